@@ -1,0 +1,227 @@
+/*
+ * kutacc_b200.h -- C ABI of the B200 build of KuTACC's gated-attention path.
+ *
+ * The entry points in part 1 keep the names, argument order, struct layouts and error behaviour of
+ * the reference's public header (include/kutacc.h); a caller compiled against that header links
+ * against this library unchanged. Each declaration cites the reference interface it replaces.
+ * Part 2 lists additions that the reference does not have (device helpers, error query, a
+ * plain-pointer projection entry); they all carry the kutacc_b200_ prefix.
+ *
+ * Tensors: a kutacc_tensor_h is a pointer to a strided descriptor {dim, data pointer, sizes,
+ * strides, dtype} (reference: src/tensor/tensor.h:21-51). The library never owns tensor data.
+ * data pointers may be CUDA device pointers (no copies are made) or host pointers (the library
+ * stages them through device memory on every call). Strides are in elements for compute
+ * operators and in bytes for kutacc_af2_all_gather, as in the reference.
+ *
+ * Errors: operators return void. A failed check prints one line
+ *   "KUTACC_CHECK fail in <func> at <file>:<line> , <message>"
+ * on stderr and sets a sticky process-wide flag; while the flag is set every operator returns
+ * without touching memory (reference: src/utils/check.h:50-56, src/utils/check.cpp:16).
+ */
+#ifndef KUTACC_B200_H
+#define KUTACC_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+#include <vector>
+extern "C" {
+#endif
+
+#define KUTACC_B200_API __attribute__((visibility("default")))
+
+/* ------------------------------------------------------------------------------------------- */
+/* Part 1: the reference's own interface for this path                                         */
+/* ------------------------------------------------------------------------------------------- */
+
+#ifndef KUTACC_OK
+#define KUTACC_OK 0
+#define KUTACC_ERROR (-1)
+#endif
+
+#ifndef KUTACC_H /* the reference header, if included first, already defines these types */
+
+/* replaces include/kutacc.h:32-39 */
+typedef struct kutacc_version {
+    const char *product_name;
+    const char *product_version;
+    const char *component_name;
+    const char *component_version;
+    const char *component_abi_version;
+    const char *component_appendinfo;
+} kutacc_version_t;
+
+/* replaces include/kutacc.h:49 */
+typedef void *kutacc_tensor_h;
+
+/* replaces include/kutacc.h:77-89. Weight matrices are stored W[out][in]; gating_b and output_b
+ * are fp32 vectors of nchannels entries. For global attention key_w and value_w are
+ * [head_size, nchannels]. */
+typedef struct kutacc_af2_attention_weights {
+    int64_t nchannels;
+    int64_t nheads;
+    int64_t head_size;
+    kutacc_tensor_h query_w;
+    kutacc_tensor_h key_w;
+    kutacc_tensor_h value_w;
+    kutacc_tensor_h gating_w;
+    kutacc_tensor_h gating_b;
+    kutacc_tensor_h output_w;
+    kutacc_tensor_h output_b;
+} kutacc_af2_attention_weights_t;
+
+/* replaces include/kutacc.h:95-104. q, k, v, gate, avg are caller-owned scratch tensors. The
+ * reference fills them with its intermediate projections; this library keeps intermediates in its
+ * own device workspace and leaves them untouched (handles may be null). */
+typedef struct kutacc_af2_attention_inputs {
+    int64_t batch;
+    int64_t seq_len;
+    kutacc_tensor_h q;
+    kutacc_tensor_h k;
+    kutacc_tensor_h v;
+    kutacc_tensor_h gate;
+    kutacc_tensor_h avg;
+} kutacc_af2_attention_inputs_t;
+
+#endif /* KUTACC_H */
+
+/* replaces include/kutacc.h:47 (src/version/version.cpp:28-35) */
+KUTACC_B200_API int kutacc_get_version(kutacc_version_t *version);
+
+/* replaces include/kutacc.h:51-52 (src/comm/kupl.cpp:25-27): process-wide rank bookkeeping */
+KUTACC_B200_API extern int64_t world_size;
+KUTACC_B200_API extern int64_t rank;
+
+/* replaces include/kutacc.h:55-56 (src/comm/kupl.cpp:50-68). One process per GPU. Builds an NCCL
+ * communicator over the ranks; the NCCL unique id is exchanged through a file whose name comes
+ * from the environment variable SHMID (as the reference's test runner sets it) or
+ * KUTACC_RENDEZVOUS. buffer_size is accepted and recorded; NCCL needs no staging window. */
+KUTACC_B200_API void kutacc_comm_init(int64_t world_size_, int64_t rank_, int64_t buffer_size_);
+KUTACC_B200_API void kutacc_comm_fini(void);
+
+/* replaces include/kutacc.h:74 (src/comm/all_gather.cpp:21-100). data is [chunk(m), n, len] or
+ * [m, chunk(n), len], out is [m, n, len]; len and all strides are BYTES; the sharded axis is
+ * dim 1 when data.sizes[0] == out.sizes[0], else dim 0; block(x) = ceil(x / world_size),
+ * chunk(x) = min(block(x), x - rank * block(x)). */
+KUTACC_B200_API void kutacc_af2_all_gather(kutacc_tensor_h data, kutacc_tensor_h out);
+
+/* replaces include/kutacc.h:297-300 (src/attention/gating_attention.cpp:160-200).
+ *   input            [batch*seq_len, nchannels]
+ *   bias             [batch, seq_len] additive mask bias (row stride = strides[0])
+ *   nonbatched_bias  [nheads, seq_len, seq_len] pair bias, unit key stride; "absent" is a valid
+ *                    handle whose sizes[0] == 0
+ *   out              [batch, seq_len, nchannels] (row stride = strides[1])
+ *   block_size       query tile of the reference's CPU loop; validated (> 0), otherwise a hint
+ * dtype of input/bias/nonbatched_bias/weights/out: all bf16, or all fp32 (extension). */
+KUTACC_B200_API void kutacc_af2_gating_attention(kutacc_tensor_h input, kutacc_af2_attention_inputs_t *q_based_ptr,
+                                                 kutacc_tensor_h bias, kutacc_tensor_h nonbatched_bias,
+                                                 kutacc_af2_attention_weights_t *weight_ptr, kutacc_tensor_h out,
+                                                 int64_t block_size);
+
+/* replaces include/kutacc.h:305-307 (src/attention/global_attention.cpp:167-205).
+ *   q_data [batch, seq_len, 64] bf16 contiguous, q_mask [batch, seq_len, 1] bf16,
+ *   out [batch, seq_len, 64]. nchannels must be 64, as in the reference. */
+KUTACC_B200_API void kutacc_af2_global_attention(kutacc_af2_attention_inputs_t *q_based_ptr, kutacc_tensor_h q_data,
+                                                 kutacc_tensor_h q_mask, kutacc_af2_attention_weights_t *weight_ptr,
+                                                 kutacc_tensor_h out);
+
+/* replaces include/kutacc.h:399-400 (src/linear/linear.cpp:21-50):
+ * result[m,n] = act[m,k] . weight[n,k]^T + beta * result + bias_data[n]; result is contiguous. */
+KUTACC_B200_API void kutacc_af2_linear(kutacc_tensor_h act, kutacc_tensor_h weight, float *bias_data,
+                                       kutacc_tensor_h result, int64_t beta);
+
+/* replaces include/kutacc.h:407-408 (src/linear/mm.cpp:94-110). The packed image of an [n,k]
+ * weight is the dense row-major [n,k] matrix (n*k elements, the size the reference reports). Takes
+ * the element type as uint16_t bit patterns so that the header is plain C. */
+KUTACC_B200_API void kutacc_af2_linear_weight_prepack(const uint16_t *weight, uint16_t *result, int64_t n, int64_t k,
+                                                      int64_t ldb, int64_t num_threads);
+
+/* replaces include/kutacc.h:418 (src/utils/blas.cpp:93-98): 'A' -> m*k, 'B' -> k*n elements */
+KUTACC_B200_API size_t kutacc_af2_gemm_pack_get_size(char identifier, char transa, char transb, int m, int n, int k);
+
+/* ------------------------------------------------------------------------------------------- */
+/* Part 2: additions (no counterpart in the reference)                                          */
+/* ------------------------------------------------------------------------------------------- */
+
+/* dtype tags: 0 and 1 are the reference's (include/kutacc.h:467-471); 2 is new */
+#define KUTACC_B200_DTYPE_INT64 0
+#define KUTACC_B200_DTYPE_BF16 1
+#define KUTACC_B200_DTYPE_FP32 2
+
+/* Plain-C construction of a tensor descriptor (the reference only offers the C++ class
+ * kutacc::TensorWrapper). The descriptor copies sizes and strides; data is not owned. */
+KUTACC_B200_API kutacc_tensor_h kutacc_b200_tensor_create(void *data, int64_t dim, const int64_t *sizes,
+                                                          const int64_t *strides, int dtype);
+KUTACC_B200_API void kutacc_b200_tensor_destroy(kutacc_tensor_h t);
+
+/* Sticky error flag: 1 if a check has failed since the last clear. The message of the most recent
+ * failure is copied into buf (truncated to cap-1 characters). */
+KUTACC_B200_API int kutacc_b200_error_set(void);
+KUTACC_B200_API int kutacc_b200_last_error(char *buf, size_t cap);
+KUTACC_B200_API void kutacc_b200_clear_error(void);
+
+/* Device selection (default: current CUDA device) and stream (default: the legacy default
+ * stream). Operators are synchronous unless kutacc_b200_set_async(1) was called, in which case
+ * calls with device-resident tensors only enqueue work on the stream. */
+KUTACC_B200_API void kutacc_b200_set_stream(void *cuda_stream);
+KUTACC_B200_API void kutacc_b200_set_async(int enabled);
+KUTACC_B200_API void kutacc_b200_synchronize(void);
+
+/* Device memory helpers for callers without a CUDA runtime of their own. */
+KUTACC_B200_API void *kutacc_b200_device_malloc(size_t bytes);
+KUTACC_B200_API void kutacc_b200_device_free(void *p);
+KUTACC_B200_API void kutacc_b200_memcpy_h2d(void *dst, const void *src, size_t bytes);
+KUTACC_B200_API void kutacc_b200_memcpy_d2h(void *dst, const void *src, size_t bytes);
+
+/* Bytes of device workspace currently held by the library (grow-only pool), and release. */
+KUTACC_B200_API size_t kutacc_b200_workspace_bytes(void);
+KUTACC_B200_API void kutacc_b200_release_workspace(void);
+
+/* Number of kernels the library has launched since load (all operators). */
+KUTACC_B200_API uint64_t kutacc_b200_launch_count(void);
+
+/* Per-kernel timing for benchmarks: while enabled, every kernel launch is bracketed by CUDA
+ * events. kutacc_b200_profile_read synchronises, writes up to cap durations (ms) in launch order
+ * and their names joined by ';' into names, clears the record and returns the count. */
+KUTACC_B200_API void kutacc_b200_set_profile(int enabled);
+KUTACC_B200_API int kutacc_b200_profile_read(char *names, size_t names_cap, float *ms, int cap);
+
+/* Communicator set-up for callers that can already broadcast 128 bytes between ranks (for
+ * example through torch.distributed): rank 0 asks for an id, every rank passes the same id. */
+KUTACC_B200_API void kutacc_b200_comm_unique_id(void *id128);
+KUTACC_B200_API void kutacc_b200_comm_init_with_id(int64_t world_size_, int64_t rank_, const void *id128);
+
+/* Pair-bias projection written directly in the layout the attention operator consumes:
+ * nb[h, q, k] = z[q, k, :] . wb[h, :]   with z [rows, n_k, c_z], wb [nheads, c_z], nb
+ * [nheads, rows, n_k] (row stride of head h = nb_head_stride elements). Same arithmetic as
+ * kutacc_af2_linear on z viewed [rows*n_k, c_z] followed by the caller's permute. dtype bf16/fp32. */
+KUTACC_B200_API void kutacc_b200_pair_bias(kutacc_tensor_h z, kutacc_tensor_h wb, kutacc_tensor_h nb);
+
+#ifdef __cplusplus
+} /* extern "C" */
+
+#ifndef KUTACC_H
+namespace kutacc {
+/* replaces include/kutacc.h:467-471; kFP32 is an addition (the reference tags fp32 buffers kBF16
+ * or passes raw float pointers). */
+typedef enum TensorDataType { kInt64 = 0, kBF16 = 1, kFP32 = 2, kNumTypes } DType;
+
+/* replaces include/kutacc.h:484-497 (src/tensor/tensor.cpp:20-30,89-92): owns the descriptor, not
+ * the data. Same constructor signature, so the mangled symbols match the reference's. */
+struct KUTACC_B200_API TensorWrapper {
+private:
+    kutacc_tensor_h tensor_;
+
+public:
+    TensorWrapper(void *data_ptr, std::vector<int64_t> &&sizes, std::vector<int64_t> &&strides, int64_t dim,
+                  DType dtype);
+    TensorWrapper();
+    kutacc_tensor_h get_tensor() { return tensor_; }
+    ~TensorWrapper();
+};
+}  // namespace kutacc
+#endif /* KUTACC_H */
+#endif /* __cplusplus */
+
+#endif /* KUTACC_B200_H */

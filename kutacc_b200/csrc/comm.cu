@@ -1,0 +1,305 @@
+// Rank bookkeeping and the byte-typed all-gather on NCCL.
+// Replaces src/comm/kupl.cpp:25-68 and src/comm/all_gather.cpp:21-100 of the reference, where the
+// transport is a shared-memory window plus MPI barriers; here it is ncclAllGather over NVLink into
+// this GPU's own memory. NCCL is resolved with dlopen at kutacc_comm_init, so single-GPU users do
+// not need the library at all.
+#include <cuda_runtime.h>
+#include <dlfcn.h>
+#include <nccl.h>
+#include <sys/stat.h>
+#include <unistd.h>
+
+#include <algorithm>
+#include <chrono>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <string>
+#include <thread>
+
+#include "common.h"
+
+extern "C" {
+KUTACC_B200_API int64_t world_size = 1;
+KUTACC_B200_API int64_t rank = 0;
+}
+int64_t buffer_size = 0;  // declared by the reference header, not exported (include/kutacc.h:53)
+
+namespace kutacc {
+
+namespace {
+
+struct NcclApi {
+    void *handle = nullptr;
+    ncclResult_t (*GetUniqueId)(ncclUniqueId *) = nullptr;
+    ncclResult_t (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int) = nullptr;
+    ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+    ncclResult_t (*AllGather)(const void *, void *, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+    const char *(*GetErrorString)(ncclResult_t) = nullptr;
+};
+NcclApi g_nccl;
+ncclComm_t g_comm = nullptr;
+std::string g_id_file;
+
+bool load_nccl()
+{
+    if (g_nccl.handle) return true;
+    const char *names[] = {"libnccl.so.2", "libnccl.so"};
+    for (const char *n : names) {
+        g_nccl.handle = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
+        if (g_nccl.handle) break;
+    }
+    KUTACC_CHECK(g_nccl.handle != nullptr, "cannot load libnccl.so.2: ", dlerror());
+    if (!g_nccl.handle) return false;
+#define KUTACC_SYM(field, name) \
+    g_nccl.field = reinterpret_cast<decltype(g_nccl.field)>(dlsym(g_nccl.handle, name))
+    KUTACC_SYM(GetUniqueId, "ncclGetUniqueId");
+    KUTACC_SYM(CommInitRank, "ncclCommInitRank");
+    KUTACC_SYM(CommDestroy, "ncclCommDestroy");
+    KUTACC_SYM(AllGather, "ncclAllGather");
+    KUTACC_SYM(GetErrorString, "ncclGetErrorString");
+#undef KUTACC_SYM
+    const bool ok = g_nccl.GetUniqueId && g_nccl.CommInitRank && g_nccl.CommDestroy && g_nccl.AllGather &&
+                    g_nccl.GetErrorString;
+    KUTACC_CHECK(ok, "libnccl lacks a required symbol");
+    return ok;
+}
+
+#define KUTACC_NCCL(call)                                                                                   \
+    do {                                                                                                    \
+        ncclResult_t r__ = (call);                                                                          \
+        KUTACC_CHECK(r__ == ncclSuccess, "NCCL error: ", g_nccl.GetErrorString(r__), " (", #call, ")");    \
+    } while (0)
+
+std::string rendezvous_path()
+{
+    const char *name = std::getenv("KUTACC_RENDEZVOUS");
+    if (!name || !*name) name = std::getenv("SHMID");
+    std::string base;
+    if (name && *name) {
+        base = name;
+    } else {
+        const char *port = std::getenv("MASTER_PORT");
+        base = std::string("kutacc_nccl_") + (port ? port : "default");
+    }
+    if (base.find('/') != std::string::npos) return base;
+    return "/dev/shm/" + base + ".ncclid";
+}
+
+struct IdRecord {
+    ncclUniqueId id;
+    int64_t stamp;  // seconds since the epoch when rank 0 wrote the file
+    int64_t world;
+};
+
+// rank 0 publishes the id through a file (write + rename), the others poll for a fresh record
+bool exchange_id(int64_t nranks, int64_t me, ncclUniqueId &id)
+{
+    using clock = std::chrono::system_clock;
+    const int64_t now = std::chrono::duration_cast<std::chrono::seconds>(clock::now().time_since_epoch()).count();
+    g_id_file = rendezvous_path();
+    if (me == 0) {
+        KUTACC_NCCL(g_nccl.GetUniqueId(&id));
+        if (kutacc_check_err_set) return false;
+        IdRecord rec;
+        rec.id = id;
+        rec.stamp = now;
+        rec.world = nranks;
+        const std::string tmp = g_id_file + ".tmp";
+        std::remove(g_id_file.c_str());
+        FILE *f = std::fopen(tmp.c_str(), "wb");
+        KUTACC_CHECK(f != nullptr, "cannot write rendezvous file ", tmp);
+        if (!f) return false;
+        const size_t w = std::fwrite(&rec, sizeof(rec), 1, f);
+        std::fclose(f);
+        KUTACC_CHECK(w == 1 && std::rename(tmp.c_str(), g_id_file.c_str()) == 0, "cannot publish rendezvous file ",
+                     g_id_file);
+        return !kutacc_check_err_set;
+    }
+    const char *to = std::getenv("KUTACC_RENDEZVOUS_TIMEOUT_S");
+    const double timeout_s = to ? std::atof(to) : 120.0;
+    const auto t0 = std::chrono::steady_clock::now();
+    for (;;) {
+        FILE *f = std::fopen(g_id_file.c_str(), "rb");
+        if (f) {
+            IdRecord rec;
+            const size_t r = std::fread(&rec, sizeof(rec), 1, f);
+            std::fclose(f);
+            // a record older than this process's start (minus slack) belongs to an earlier job
+            if (r == 1 && rec.world == nranks && rec.stamp >= now - 300) {
+                id = rec.id;
+                return true;
+            }
+        }
+        const double waited = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+        if (waited > timeout_s) {
+            KUTACC_CHECK(false, "rank ", me, ": no fresh rendezvous record at ", g_id_file, " after ", waited, " s");
+            return false;
+        }
+        std::this_thread::sleep_for(std::chrono::milliseconds(20));
+    }
+}
+
+// strided byte gather/scatter between a [a, o, len] view and a dense buffer
+__global__ void copy_rows_kernel(const uint8_t *__restrict__ src, int64_t s_a, int64_t s_o, uint8_t *__restrict__ dst,
+                                 int64_t d_a, int64_t d_o, int64_t na, int64_t no, int64_t len)
+{
+    const int64_t total = na * no;
+    for (int64_t row = blockIdx.x; row < total; row += gridDim.x) {
+        const int64_t a = row / no, o = row % no;
+        const uint8_t *s = src + a * s_a + o * s_o;
+        uint8_t *d = dst + a * d_a + o * d_o;
+        if (((((uintptr_t)s) | ((uintptr_t)d) | (uintptr_t)len) & 15u) == 0) {
+            for (int64_t i = threadIdx.x; i < len / 16; i += blockDim.x)
+                reinterpret_cast<uint4 *>(d)[i] = reinterpret_cast<const uint4 *>(s)[i];
+        } else {
+            for (int64_t i = threadIdx.x; i < len; i += blockDim.x) d[i] = s[i];
+        }
+    }
+}
+
+void copy_rows(cudaStream_t stream, const void *src, int64_t s_a, int64_t s_o, void *dst, int64_t d_a, int64_t d_o,
+               int64_t na, int64_t no, int64_t len)
+{
+    if (na <= 0 || no <= 0 || len <= 0) return;
+    const unsigned grid = (unsigned)std::min<int64_t>(na * no, 148 * 8);
+    const unsigned block = len >= 4096 ? 256 : (len >= 512 ? 128 : 32);
+    copy_rows_kernel<<<grid, block, 0, stream>>>((const uint8_t *)src, s_a, s_o, (uint8_t *)dst, d_a, d_o, na, no, len);
+    count_launch();
+}
+
+}  // namespace
+
+static void init_common(int64_t nranks, int64_t me, int64_t bufsz, const ncclUniqueId *given)
+{
+    KUTACC_CHECK(nranks > 0 && me >= 0 && me < nranks && bufsz >= 0, "kutacc_comm_init: invalid arguments ", nranks,
+                 " ", me, " ", bufsz);
+    if (kutacc_check_err_set) return;
+    world_size = nranks;
+    rank = me;
+    buffer_size = bufsz;
+    if (nranks == 1) return;
+    if (const char *dev = std::getenv("KUTACC_DEVICE")) KUTACC_CUDA(cudaSetDevice(std::atoi(dev)));
+    if (!load_nccl()) return;
+    ncclUniqueId id;
+    if (given) {
+        id = *given;
+    } else if (!exchange_id(nranks, me, id)) {
+        return;
+    }
+    KUTACC_NCCL(g_nccl.CommInitRank(&g_comm, (int)nranks, id, (int)me));
+}
+
+}  // namespace kutacc
+
+extern "C" {
+
+void kutacc_comm_init(int64_t world_size_, int64_t rank_, int64_t buffer_size_)
+{
+    kutacc::init_common(world_size_, rank_, buffer_size_, nullptr);
+}
+
+// Variant for callers that already have a way to broadcast 128 bytes between ranks.
+KUTACC_B200_API void kutacc_b200_comm_unique_id(void *id128)
+{
+    using namespace kutacc;
+    KUTACC_CHECK(id128 != nullptr, "kutacc_b200_comm_unique_id: nullptr");
+    if (kutacc_check_err_set || !load_nccl()) return;
+    ncclUniqueId id;
+    KUTACC_NCCL(g_nccl.GetUniqueId(&id));
+    std::memcpy(id128, &id, sizeof(id));
+}
+KUTACC_B200_API void kutacc_b200_comm_init_with_id(int64_t world_size_, int64_t rank_, const void *id128)
+{
+    using namespace kutacc;
+    KUTACC_CHECK(id128 != nullptr, "kutacc_b200_comm_init_with_id: nullptr");
+    if (kutacc_check_err_set) return;
+    ncclUniqueId id;
+    std::memcpy(&id, id128, sizeof(id));
+    init_common(world_size_, rank_, 0, &id);
+}
+
+void kutacc_comm_fini(void)
+{
+    using namespace kutacc;
+    if (g_comm) {
+        cudaStreamSynchronize((cudaStream_t)runtime().stream);
+        KUTACC_NCCL(g_nccl.CommDestroy(g_comm));
+        g_comm = nullptr;
+    }
+    if (rank == 0 && !g_id_file.empty()) std::remove(g_id_file.c_str());
+    g_id_file.clear();
+    world_size = 1;
+    rank = 0;
+}
+
+void kutacc_af2_all_gather(kutacc_tensor_h data_h, kutacc_tensor_h out_h)
+{
+    using namespace kutacc;
+    if (data_h == nullptr || out_h == nullptr) {  // all_gather.cpp:88-92
+        KUTACC_CHECK(data_h != nullptr, "all_gather: data is null");
+        KUTACC_CHECK(out_h != nullptr, "all_gather: out is null");
+        return;
+    }
+    if (kutacc_check_err_set) return;
+    Tensor &data = *as_tensor(data_h), &out = *as_tensor(out_h);
+    KUTACC_CHECK(data.dim() == 3 && out.dim() == 3 && data.data_ptr() && out.data_ptr(),
+                 "all_gather: [m, n, len] byte tensors expected");
+    if (kutacc_check_err_set) return;
+    const int64_t m = out.sizes()[0], n = out.sizes()[1], len = data.sizes()[2];
+    KUTACC_CHECK(data.strides()[2] == 1, data.strides()[2]);  // all_gather.cpp:37-38
+    KUTACC_CHECK(out.strides()[2] == 1, out.strides()[2]);
+    KUTACC_CHECK(m > 0 && n > 0 && len > 0 && out.sizes()[2] == len, "all_gather: shape invalid");
+    if (kutacc_check_err_set) return;
+    // sharded axis: dim 1 when the leading sizes agree (all_gather.cpp:27-33); a = sharded, o = whole
+    const bool dim1 = data.sizes()[0] == m;
+    const int64_t full = dim1 ? n : m, other = dim1 ? m : n;
+    const int64_t ds_a = dim1 ? data.strides()[1] : data.strides()[0], ds_o = dim1 ? data.strides()[0] : data.strides()[1];
+    const int64_t os_a = dim1 ? out.strides()[1] : out.strides()[0], os_o = dim1 ? out.strides()[0] : out.strides()[1];
+    const int64_t block = (full + world_size - 1) / world_size;
+    const int64_t mine = std::max<int64_t>(0, std::min(block, full - rank * block));
+    KUTACC_CHECK((dim1 ? data.sizes()[1] : data.sizes()[0]) >= mine && (dim1 ? data.sizes()[0] : data.sizes()[1]) == other,
+                 "all_gather: data shape does not match this rank's chunk");
+    if (kutacc_check_err_set) return;
+
+    auto span = [&](const Tensor &t) {
+        return (size_t)((t.sizes()[0] - 1) * t.strides()[0] + (t.sizes()[1] - 1) * t.strides()[1] + len);
+    };
+    const size_t data_bytes = mine > 0 ? span(data) : 0, out_bytes = span(out);
+    const size_t slot = (size_t)block * other * len;  // dense bytes per rank
+
+    Runtime &rt = runtime();
+    cudaStream_t stream = (cudaStream_t)rt.stream;
+    if (!rt.reserve_stage(staged_bytes_needed(data.data_ptr(), data_bytes) + staged_bytes_needed(out.data_ptr(), out_bytes)))
+        return;
+    DeviceArg d_in = data_bytes ? resolve_in(data.data_ptr(), data_bytes) : DeviceArg{};
+    // a staged (host) output is rebuilt whole on the device and copied back
+    DeviceArg d_out = resolve_out(out.data_ptr(), out_bytes);
+    if (kutacc_check_err_set) return;
+
+    const bool dense_dim0 = !dim1 && ds_o == len && ds_a == other * len && os_o == len && os_a == other * len;
+    if (world_size == 1 || g_comm == nullptr) {
+        KUTACC_CHECK(world_size == 1, "all_gather: kutacc_comm_init has not built a communicator");
+        if (kutacc_check_err_set) return;
+        copy_rows(stream, d_in.dev, ds_a, ds_o, d_out.dev, os_a, os_o, mine, other, len);
+    } else if (dense_dim0 && full % world_size == 0) {
+        // every rank's rows are one contiguous slab of out: gather in place
+        KUTACC_NCCL(g_nccl.AllGather(d_in.dev, d_out.dev, slot, ncclUint8, g_comm, stream));
+    } else {
+        if (!rt.reserve_workspace((size_t)(world_size + 1) * (slot + 256))) return;
+        uint8_t *send = (uint8_t *)rt.take_workspace(slot);
+        uint8_t *recv = (uint8_t *)rt.take_workspace((size_t)world_size * slot);
+        if (kutacc_check_err_set) return;
+        copy_rows(stream, d_in.dev, ds_a, ds_o, send, other * len, len, mine, other, len);
+        KUTACC_NCCL(g_nccl.AllGather(send, recv, slot, ncclUint8, g_comm, stream));
+        for (int64_t r = 0; r < world_size; ++r) {
+            const int64_t have = std::max<int64_t>(0, std::min(block, full - r * block));
+            copy_rows(stream, recv + (size_t)r * slot, other * len, len, (uint8_t *)d_out.dev + r * block * os_a, os_a,
+                      os_o, have, other, len);
+        }
+    }
+    finish_out(d_out);
+    end_of_call();
+}
+
+}  // extern "C"

@@ -1,0 +1,152 @@
+// kutacc_af2_gating_attention: validation, device resolution of the arguments, kernel sequence.
+// Replaces src/attention/gating_attention.cpp:33-200 of the reference.
+#include <cuda_runtime.h>
+
+#include <climits>
+#include <cmath>
+
+#include "common.h"
+#include "kernels.h"
+
+namespace kutacc {
+
+namespace {
+bool aligned16(const void *p) { return ((uintptr_t)p & 15u) == 0; }
+}  // namespace
+
+static void gating_attention_impl(Tensor &input, int64_t batch, int64_t seq_len, Tensor &bias, Tensor &nonbatched_bias,
+                                  const Tensor &query_w, const Tensor &key_w, const Tensor &value_w,
+                                  const Tensor &gating_w, const Tensor &gating_b, const Tensor &output_w,
+                                  const Tensor &output_b, Tensor &out, int64_t block_size, int64_t head_size,
+                                  int64_t nheads, int64_t nchannels)
+{
+    // same scalar validation, in the same place, as gating_attention.cpp:39-45 and :69
+    KUTACC_CHECK(batch > 0 && seq_len > 0 && block_size > 0 && head_size > 0 && nheads > 0 && nchannels > 0 &&
+                     batch <= INT32_MAX / seq_len && seq_len <= INT32_MAX && nchannels <= INT32_MAX &&
+                     head_size <= INT32_MAX && block_size <= INT64_MAX / seq_len,
+                 "input param <= 0 or overflow");
+    if (kutacc_check_err_set) return;
+    const int64_t nblocks = (seq_len + block_size - 1) / block_size;
+    KUTACC_CHECK(batch <= INT64_MAX / nheads / nblocks, "parallel end overflow");
+    KUTACC_CHECK(nheads * head_size == nchannels, "nchannels != nheads * head_size: ", nchannels, " ", nheads, " ",
+                 head_size);
+    if (kutacc_check_err_set) return;
+
+    const DType dt = input.dtype();
+    KUTACC_CHECK(dt == kBF16 || dt == kFP32, "gating_attention dtype invalid: [", (int)dt, "]");
+    KUTACC_CHECK(input.data_ptr() && bias.data_ptr() && out.data_ptr() && query_w.data_ptr() && key_w.data_ptr() &&
+                     value_w.data_ptr() && gating_w.data_ptr() && gating_b.data_ptr() && output_w.data_ptr() &&
+                     output_b.data_ptr(),
+                 "gating_attention: null data pointer");
+    KUTACC_CHECK(bias.dim() >= 1 && out.dim() >= 2, "gating_attention: bias/out rank invalid");
+    if (kutacc_check_err_set) return;
+
+    const bool has_nb = nonbatched_bias.dim() > 0 && nonbatched_bias.sizes()[0] != 0;  // :103
+    if (has_nb) {
+        KUTACC_CHECK(nonbatched_bias.dim() >= 3 && nonbatched_bias.data_ptr() != nullptr,
+                     "gating_attention: nonbatched_bias must be [nheads, seq_len, seq_len]");
+        if (kutacc_check_err_set) return;
+    }
+
+    const int64_t B = batch, S = seq_len, H = nheads, D = head_size, C = nchannels, M = B * S;
+    const size_t es = dtype_size(dt);
+    const int64_t bias_s0 = bias.dim() >= 2 ? bias.strides()[0] : 0;
+    const int64_t nb_s0 = has_nb ? nonbatched_bias.strides()[0] : 0, nb_s1 = has_nb ? nonbatched_bias.strides()[1] : 0;
+    const int64_t out_rs = out.dim() >= 3 ? out.strides()[1] : out.strides()[0];
+    KUTACC_CHECK(out_rs >= C, "gating_attention: out row stride ", out_rs, " < nchannels ", C);
+    if (kutacc_check_err_set) return;
+
+    const size_t x_bytes = (size_t)M * C * es, w_bytes = (size_t)C * C * es, b_bytes = (size_t)C * sizeof(float);
+    const size_t bias_bytes = (size_t)((B - 1) * bias_s0 + S) * es;
+    const size_t nb_bytes = has_nb ? (size_t)((H - 1) * nb_s0 + (S - 1) * nb_s1 + S) * es : 0;
+    const size_t out_bytes = (size_t)((M - 1) * out_rs + C) * es;
+
+    Runtime &rt = runtime();
+    cudaStream_t stream = (cudaStream_t)rt.stream;
+
+    size_t stage = staged_bytes_needed(input.data_ptr(), x_bytes) + staged_bytes_needed(bias.data_ptr(), bias_bytes) +
+                   staged_bytes_needed(out.data_ptr(), out_bytes) + staged_bytes_needed(gating_b.data_ptr(), b_bytes) +
+                   staged_bytes_needed(output_b.data_ptr(), b_bytes);
+    if (has_nb) stage += staged_bytes_needed(nonbatched_bias.data_ptr(), nb_bytes);
+    for (const Tensor *w : {&query_w, &key_w, &value_w, &gating_w, &output_w})
+        stage += staged_bytes_needed(w->data_ptr(), w_bytes);
+    if (!rt.reserve_stage(stage)) return;
+    if (!rt.reserve_workspace(5 * (x_bytes + 256))) return;
+
+    DeviceArg d_x = resolve_in(input.data_ptr(), x_bytes);
+    DeviceArg d_bias = resolve_in(bias.data_ptr(), bias_bytes);
+    DeviceArg d_nb = has_nb ? resolve_in(nonbatched_bias.data_ptr(), nb_bytes) : DeviceArg{};
+    DeviceArg d_wq = resolve_in(query_w.data_ptr(), w_bytes), d_wk = resolve_in(key_w.data_ptr(), w_bytes),
+              d_wv = resolve_in(value_w.data_ptr(), w_bytes), d_wg = resolve_in(gating_w.data_ptr(), w_bytes),
+              d_wo = resolve_in(output_w.data_ptr(), w_bytes);
+    DeviceArg d_bg = resolve_in(gating_b.data_ptr(), b_bytes), d_bo = resolve_in(output_b.data_ptr(), b_bytes);
+    DeviceArg d_out = resolve_out(out.data_ptr(), out_bytes);
+    void *wq_ = rt.take_workspace(x_bytes), *wk_ = rt.take_workspace(x_bytes), *wv_ = rt.take_workspace(x_bytes),
+         *wg_ = rt.take_workspace(x_bytes), *wavg = rt.take_workspace(x_bytes);
+    if (kutacc_check_err_set) return;
+
+    const float scale = (float)(1 / std::sqrt((double)head_size));  // gating_attention.cpp:68
+
+    const bool fast = dt == kBF16 && (C % 64 == 0) && (D == 16 || D == 32 || D == 64) && B <= 65535 && H <= 65535 &&
+                      aligned16(d_x.dev) && aligned16(d_wq.dev) && aligned16(d_wk.dev) && aligned16(d_wv.dev) &&
+                      aligned16(d_wg.dev) && aligned16(d_wo.dev) && (out_rs % 2 == 0) &&
+                      (((uintptr_t)d_out.dev & 3u) == 0) &&
+                      (!has_nb || ((nb_s0 % 8 == 0) && (nb_s1 % 8 == 0) && aligned16(d_nb.dev)));
+    bool ok;
+    if (fast) {
+        const float q_scale = scale * 1.4426950408889634f;  // the attention kernel works in base 2
+        ok = dev::launch_proj_qkvg_bf16(stream, d_x.dev, d_wq.dev, d_wk.dev, d_wv.dev, d_wg.dev,
+                                        (const float *)d_bg.dev, wq_, wk_, wv_, wg_, (int)B, (int)S, (int)H, (int)D,
+                                        q_scale);
+        ok = ok && dev::launch_attn_core_bf16(stream, wq_, wk_, wv_, wg_, d_bias.dev, bias_s0,
+                                              has_nb ? d_nb.dev : nullptr, nb_s0, nb_s1, wavg, (int)B, (int)S, (int)H,
+                                              (int)D);
+        ok = ok && dev::launch_linear_bias_bf16(stream, wavg, C, d_wo.dev, (const float *)d_bo.dev, d_out.dev, out_rs,
+                                                M, (int)C, (int)C);
+    } else {
+        const dev::ElemType et = dt == kFP32 ? dev::kElemF32 : dev::kElemBF16;
+        ok = dev::launch_gemm_generic(stream, et, d_x.dev, C, d_wq.dev, C, nullptr, 0.f, wq_, C, M, C, C);
+        ok = ok && dev::launch_gemm_generic(stream, et, d_x.dev, C, d_wk.dev, C, nullptr, 0.f, wk_, C, M, C, C);
+        ok = ok && dev::launch_gemm_generic(stream, et, d_x.dev, C, d_wv.dev, C, nullptr, 0.f, wv_, C, M, C, C);
+        ok = ok && dev::launch_gemm_generic(stream, et, d_x.dev, C, d_wg.dev, C, (const float *)d_bg.dev, 0.f, wg_, C,
+                                            M, C, C);
+        ok = ok && dev::launch_attn_generic(stream, et, wq_, wk_, wv_, wg_, d_bias.dev, bias_s0,
+                                            has_nb ? d_nb.dev : nullptr, nb_s0, nb_s1, wavg, (int)B, (int)S, (int)H,
+                                            (int)D, scale);
+        ok = ok && dev::launch_gemm_generic(stream, et, wavg, C, d_wo.dev, C, (const float *)d_bo.dev, 0.f, d_out.dev,
+                                            out_rs, M, C, C);
+    }
+    KUTACC_CHECK(ok, "gating_attention: no device kernel for this shape (B=", B, " S=", S, " H=", H, " D=", D, ")");
+    finish_out(d_out);
+    end_of_call();
+}
+
+}  // namespace kutacc
+
+extern "C" void kutacc_af2_gating_attention(kutacc_tensor_h input, kutacc_af2_attention_inputs_t *q_based_ptr,
+                                            kutacc_tensor_h bias, kutacc_tensor_h nonbatched_bias,
+                                            kutacc_af2_attention_weights_t *weight_ptr, kutacc_tensor_h out,
+                                            int64_t block_size)
+{
+    using namespace kutacc;
+    // handle / struct nulls first (gating_attention.cpp:165-170) ...
+    KUTACC_CHECK(input != nullptr && q_based_ptr != nullptr && bias != nullptr && nonbatched_bias != nullptr &&
+                     weight_ptr != nullptr && out != nullptr,
+                 "kutacc_af2_gating_attention: input args nullptr error");
+    if (kutacc_check_err_set) return;
+    // ... then the scalars, before any handle is dereferenced: the reference's robustness tests
+    // pass pointers to stack floats as handles together with one bad integer.
+    const int64_t batch = q_based_ptr->batch, seq_len = q_based_ptr->seq_len;
+    const int64_t head_size = weight_ptr->head_size, nheads = weight_ptr->nheads, nchannels = weight_ptr->nchannels;
+    KUTACC_CHECK(batch > 0 && seq_len > 0 && block_size > 0 && head_size > 0 && nheads > 0 && nchannels > 0,
+                 "input param <= 0 or overflow");
+    KUTACC_CHECK(weight_ptr->query_w && weight_ptr->key_w && weight_ptr->value_w && weight_ptr->gating_w &&
+                     weight_ptr->gating_b && weight_ptr->output_w && weight_ptr->output_b,
+                 "kutacc_af2_gating_attention: weight handle nullptr error");
+    if (kutacc_check_err_set) return;
+    gating_attention_impl(*as_tensor(input), batch, seq_len, *as_tensor(bias), *as_tensor(nonbatched_bias),
+                          *as_tensor(weight_ptr->query_w), *as_tensor(weight_ptr->key_w),
+                          *as_tensor(weight_ptr->value_w), *as_tensor(weight_ptr->gating_w),
+                          *as_tensor(weight_ptr->gating_b), *as_tensor(weight_ptr->output_w),
+                          *as_tensor(weight_ptr->output_b), *as_tensor(out), block_size, head_size, nheads, nchannels);
+}

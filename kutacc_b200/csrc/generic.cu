@@ -1,0 +1,378 @@
+// Shape-agnostic kernels: any channel count, head size and sequence length, bf16 or fp32 storage,
+// fp32 arithmetic on the CUDA cores. They cover what the tensor-core kernels do not (fp32 tensors,
+// head sizes other than 16/32/64, channel counts that are not multiples of 64, unaligned pair-bias
+// strides) so that every shape the reference accepts has a device path.
+//
+// Same math as src/attention/gating_attention.cpp:47-157 with the rounding points of the storage
+// type (none for fp32).
+#include "common.h"
+#include "kernels.h"
+#include "ptx_utils.cuh"
+
+#include <algorithm>
+
+namespace kutacc {
+namespace dev {
+
+namespace {
+
+template <typename T>
+__device__ __forceinline__ float ld(const T *p);
+template <>
+__device__ __forceinline__ float ld<float>(const float *p)
+{
+    return *p;
+}
+template <>
+__device__ __forceinline__ float ld<__nv_bfloat16>(const __nv_bfloat16 *p)
+{
+    return __bfloat162float(*p);
+}
+template <typename T>
+__device__ __forceinline__ void st(T *p, float v);
+template <>
+__device__ __forceinline__ void st<float>(float *p, float v)
+{
+    *p = v;
+}
+template <>
+__device__ __forceinline__ void st<__nv_bfloat16>(__nv_bfloat16 *p, float v)
+{
+    *p = __float2bfloat16_rn(v);
+}
+template <typename T>
+__device__ __forceinline__ float round_store(float v);
+template <>
+__device__ __forceinline__ float round_store<float>(float v)
+{
+    return v;
+}
+template <>
+__device__ __forceinline__ float round_store<__nv_bfloat16>(float v)
+{
+    return __bfloat162float(__float2bfloat16_rn(v));
+}
+
+// ---- GEMM: 64 x 64 tile, 16-wide K slabs, 4 x 4 outputs per thread ------------------------------
+constexpr int GT = 64, GK = 16;
+
+template <typename T>
+__global__ void __launch_bounds__(256) gemm_generic_kernel(const T *__restrict__ a, int64_t lda,
+                                                           const T *__restrict__ w, int64_t ldw,
+                                                           const float *__restrict__ bias, float beta, T *c,
+                                                           int64_t ldc, int64_t M, int64_t N, int64_t K)
+{
+    __shared__ float sa[GK][GT + 1];
+    __shared__ float sw[GK][GT + 1];
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    const int64_t m0 = (int64_t)blockIdx.x * GT, n0 = (int64_t)blockIdx.y * GT;
+    float acc[4][4] = {};
+    for (int64_t k0 = 0; k0 < K; k0 += GK) {
+        for (int i = threadIdx.x; i < GT * GK; i += 256) {
+            const int r = i / GK, kk = i % GK;
+            const int64_t gm = m0 + r, gn = n0 + r, gk = k0 + kk;
+            sa[kk][r] = (gm < M && gk < K) ? ld(a + gm * lda + gk) : 0.f;
+            sw[kk][r] = (gn < N && gk < K) ? ld(w + gn * ldw + gk) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < GK; ++kk) {
+            float av[4], wv[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                av[i] = sa[kk][ty * 4 + i];
+                wv[i] = sw[kk][tx * 4 + i];
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], wv[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int64_t m = m0 + ty * 4 + i;
+        if (m >= M) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int64_t n = n0 + tx * 4 + j;
+            if (n >= N) continue;
+            float v = acc[i][j];
+            if (beta != 0.f) v += beta * ld(c + m * ldc + n);
+            if (bias) v += bias[n];
+            st(c + m * ldc + n, v);
+        }
+    }
+}
+
+// ---- attention: one warp per (b, h, query) --------------------------------------------------------
+// Lanes split the keys for the logits (each lane a dot product over D) and split the head
+// channels for P.V. Online softmax across 32-key chunks.
+template <typename T, int DMAX>
+__global__ void __launch_bounds__(128) attn_generic_kernel(const T *__restrict__ q, const T *__restrict__ k,
+                                                           const T *__restrict__ v, const T *__restrict__ gate,
+                                                           const T *__restrict__ bias, int64_t bias_stride0,
+                                                           const T *__restrict__ nb, int64_t nb_stride_h,
+                                                           int64_t nb_stride_q, T *__restrict__ avg, int B, int S,
+                                                           int H, int D, float scale)
+{
+    const int lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= (int64_t)B * H * S) return;
+    const int i = (int)(row % S);
+    const int h = (int)((row / S) % H);
+    const int b = (int)(row / ((int64_t)S * H));
+    const int C = H * D;
+    const T *qi = q + ((int64_t)b * S + i) * C + h * D;
+    const T *kb = k + (int64_t)b * S * C + h * D;
+    const T *vb = v + (int64_t)b * S * C + h * D;
+    const T *brow = bias + (int64_t)b * bias_stride0;
+    const T *nbrow = nb ? nb + (int64_t)h * nb_stride_h + (int64_t)i * nb_stride_q : nullptr;
+
+    constexpr int ND = DMAX / 32;  // output channels per lane
+    float qreg[DMAX];
+#pragma unroll
+    for (int d = 0; d < DMAX; ++d) qreg[d] = d < D ? ld(qi + d) : 0.f;
+    float o[ND];
+#pragma unroll
+    for (int j = 0; j < ND; ++j) o[j] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;
+
+    for (int j0 = 0; j0 < S; j0 += 32) {
+        const int j = j0 + lane;
+        float x = -INFINITY;
+        if (j < S) {
+            const T *kj = kb + (int64_t)j * C;
+            float acc = 0.f;
+#pragma unroll
+            for (int d = 0; d < DMAX; ++d)
+                if (d < D) acc = fmaf(qreg[d], ld(kj + d), acc);
+            acc = round_store<T>(acc);                       // logits are stored in the tensor type
+            x = acc * scale + ld(brow + j);
+            if (nbrow) x = x + ld(nbrow + j);
+        }
+        float mx = x;
+#pragma unroll
+        for (int s = 16; s > 0; s >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, s));
+        const float m_new = fmaxf(m_run, mx);
+        const float corr = __expf(m_run - m_new);
+        const float pj = (j < S) ? __expf(x - m_new) : 0.f;
+        float ps = pj;
+#pragma unroll
+        for (int s = 16; s > 0; s >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, s);
+        l_run = l_run * corr + ps;
+        m_run = m_new;
+#pragma unroll
+        for (int jj = 0; jj < ND; ++jj) o[jj] *= corr;
+        const int lim = min(32, S - j0);
+        for (int kk = 0; kk < lim; ++kk) {
+            const float pk = __shfl_sync(0xffffffffu, pj, kk);
+            const T *vj = vb + (int64_t)(j0 + kk) * C;
+#pragma unroll
+            for (int jj = 0; jj < ND; ++jj) {
+                const int d = jj * 32 + lane;
+                if (d < D) o[jj] = fmaf(pk, ld(vj + d), o[jj]);
+            }
+        }
+    }
+    const float inv = 1.0f / l_run;
+    const T *gi = gate + ((int64_t)b * S + i) * C + h * D;
+    T *ai = avg + ((int64_t)b * S + i) * C + h * D;
+#pragma unroll
+    for (int jj = 0; jj < ND; ++jj) {
+        const int d = jj * 32 + lane;
+        if (d < D) {
+            const float wa = round_store<T>(o[jj] * inv);
+            const float sg = 1.0f / (1.0f + __expf(-ld(gi + d)));
+            st(ai + d, wa * sg);
+        }
+    }
+}
+
+// ---- pair-bias projection -------------------------------------------------------------------------
+// One warp per (row, key) pair reads z[r, k, :] with 16-byte loads where possible and reduces the
+// H dot products with shuffles; writes nb[h, r, k]. Bandwidth bound: reads R*Nk*Cz elements once.
+template <typename T, int HMAX>
+__global__ void __launch_bounds__(256) pair_bias_kernel(const T *__restrict__ z, const T *__restrict__ wb,
+                                                        T *__restrict__ nb, int64_t nb_head_stride, int64_t pos_stride,
+                                                        int64_t R, int64_t Nk, int Cz, int H)
+{
+    extern __shared__ float swb[];  // [H][Cz]
+    for (int i = threadIdx.x; i < H * Cz; i += blockDim.x) swb[i] = ld(wb + i);
+    __syncthreads();
+    const int lane = threadIdx.x & 31;
+    const int64_t nwarps = (int64_t)gridDim.x * (blockDim.x >> 5);
+    for (int64_t pos = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); pos < R * Nk; pos += nwarps) {
+        const T *zr = z + pos * Cz;
+        float acc[HMAX];
+#pragma unroll
+        for (int hh = 0; hh < HMAX; ++hh) acc[hh] = 0.f;
+        for (int c = lane; c < Cz; c += 32) {
+            const float zv = ld(zr + c);
+#pragma unroll
+            for (int hh = 0; hh < HMAX; ++hh)
+                if (hh < H) acc[hh] = fmaf(zv, swb[hh * Cz + c], acc[hh]);
+        }
+#pragma unroll
+        for (int hh = 0; hh < HMAX; ++hh) {
+#pragma unroll
+            for (int s = 16; s > 0; s >>= 1) acc[hh] += __shfl_xor_sync(0xffffffffu, acc[hh], s);
+        }
+        if (lane == 0) {
+            const int64_t r = pos / Nk, kk = pos % Nk;
+#pragma unroll
+            for (int hh = 0; hh < HMAX; ++hh)
+                if (hh < H) st(nb + hh * nb_head_stride + (r * Nk + kk) * pos_stride, acc[hh]);
+        }
+    }
+}
+
+// bf16 fast variant: Cz/8 lanes share one (row, key) position, each lane fetches 8 channels with one
+// 128-bit load; partial dot products are combined with xor shuffles inside the lane group.
+template <int HMAX>
+__global__ void __launch_bounds__(256) pair_bias_vec_kernel(const __nv_bfloat16 *__restrict__ z,
+                                                            const __nv_bfloat16 *__restrict__ wb,
+                                                            __nv_bfloat16 *__restrict__ nb, int64_t nb_head_stride,
+                                                            int64_t pos_stride, int64_t R, int64_t Nk, int Cz, int H,
+                                                            int lanes_per_pos)
+{
+    const int sub = threadIdx.x % lanes_per_pos;
+    // this lane's 8 channels of every head's weight row stay in registers for the whole kernel
+    float wreg[HMAX][8];
+#pragma unroll
+    for (int hh = 0; hh < HMAX; ++hh)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) wreg[hh][i] = hh < H ? __bfloat162float(wb[hh * Cz + sub * 8 + i]) : 0.f;
+    const int64_t pos_per_block = blockDim.x / lanes_per_pos;
+    const int64_t total = R * Nk;
+    // the loop bound depends on the block only, so whole warps stay together for the shuffles
+    for (int64_t base = (int64_t)blockIdx.x * pos_per_block; base < total; base += (int64_t)gridDim.x * pos_per_block) {
+        const int64_t pos = base + threadIdx.x / lanes_per_pos;
+        const bool live = pos < total;
+        float acc[HMAX];
+#pragma unroll
+        for (int hh = 0; hh < HMAX; ++hh) acc[hh] = 0.f;
+        if (live) {
+            const uint4 raw = __ldg(reinterpret_cast<const uint4 *>(z + pos * Cz) + sub);
+            const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+            float zv[8];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                zv[2 * i] = bf16lo_to_f32(w[i]);
+                zv[2 * i + 1] = bf16hi_to_f32(w[i]);
+            }
+#pragma unroll
+            for (int hh = 0; hh < HMAX; ++hh) {
+                if (hh < H) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) acc[hh] = fmaf(zv[i], wreg[hh][i], acc[hh]);
+                }
+            }
+        }
+#pragma unroll
+        for (int hh = 0; hh < HMAX; ++hh) {
+            for (int s = lanes_per_pos >> 1; s > 0; s >>= 1) acc[hh] += __shfl_xor_sync(0xffffffffu, acc[hh], s);
+        }
+        if (live && sub == 0) {
+#pragma unroll
+            for (int hh = 0; hh < HMAX; ++hh)
+                if (hh < H) nb[hh * nb_head_stride + pos * pos_stride] = __float2bfloat16_rn(acc[hh]);
+        }
+    }
+}
+
+}  // namespace
+
+bool launch_gemm_generic(cudaStream_t stream, ElemType t, const void *a, int64_t lda, const void *w, int64_t ldw,
+                         const float *bias, float beta, void *c, int64_t ldc, int64_t M, int64_t N, int64_t K)
+{
+    dim3 grid((unsigned)((M + GT - 1) / GT), (unsigned)((N + GT - 1) / GT));
+    if (grid.y > 65535) return false;
+    KernelTimer timer__("gemm_generic");
+    if (t == kElemF32)
+        gemm_generic_kernel<float><<<grid, 256, 0, stream>>>((const float *)a, lda, (const float *)w, ldw, bias, beta,
+                                                            (float *)c, ldc, M, N, K);
+    else
+        gemm_generic_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16 *)a, lda,
+                                                                    (const __nv_bfloat16 *)w, ldw, bias, beta,
+                                                                    (__nv_bfloat16 *)c, ldc, M, N, K);
+    count_launch();
+    return true;
+}
+
+template <typename T>
+static bool launch_attn_generic_t(cudaStream_t stream, const void *q, const void *k, const void *v, const void *gate,
+                                  const void *bias, int64_t bias_stride0, const void *nb, int64_t nb_stride_h,
+                                  int64_t nb_stride_q, void *avg, int B, int S, int H, int D, float scale)
+{
+    const int64_t rows = (int64_t)B * H * S;
+    const unsigned grid = (unsigned)((rows + 3) / 4);
+    KernelTimer timer__("attn_generic");
+#define KUTACC_ATTN_GENERIC(DMAX)                                                                                  \
+    attn_generic_kernel<T, DMAX><<<grid, 128, 0, stream>>>((const T *)q, (const T *)k, (const T *)v, (const T *)gate, \
+                                                           (const T *)bias, bias_stride0, (const T *)nb, nb_stride_h, \
+                                                           nb_stride_q, (T *)avg, B, S, H, D, scale)
+    if (D <= 32)
+        KUTACC_ATTN_GENERIC(32);
+    else if (D <= 64)
+        KUTACC_ATTN_GENERIC(64);
+    else if (D <= 128)
+        KUTACC_ATTN_GENERIC(128);
+    else
+        return false;
+#undef KUTACC_ATTN_GENERIC
+    count_launch();
+    return true;
+}
+
+bool launch_attn_generic(cudaStream_t stream, ElemType t, const void *q, const void *k, const void *v,
+                         const void *gate, const void *bias, int64_t bias_stride0, const void *nb,
+                         int64_t nb_stride_h, int64_t nb_stride_q, void *avg, int B, int S, int H, int D, float scale)
+{
+    if (t == kElemF32)
+        return launch_attn_generic_t<float>(stream, q, k, v, gate, bias, bias_stride0, nb, nb_stride_h, nb_stride_q,
+                                            avg, B, S, H, D, scale);
+    return launch_attn_generic_t<__nv_bfloat16>(stream, q, k, v, gate, bias, bias_stride0, nb, nb_stride_h,
+                                                nb_stride_q, avg, B, S, H, D, scale);
+}
+
+bool launch_pair_bias(cudaStream_t stream, ElemType t, const void *z, const void *wb, void *nb,
+                      int64_t nb_head_stride, int64_t pos_stride, int64_t R, int64_t Nk, int Cz, int H)
+{
+    if (H > 16 || (size_t)H * Cz * 4 > 48 * 1024) return false;
+    KernelTimer timer__("pair_bias");
+    const int64_t pos = R * Nk;
+    const unsigned grid = (unsigned)std::min<int64_t>((pos + 7) / 8, 148 * 16);
+    const size_t smem = (size_t)H * Cz * 4;
+    const int lanes = Cz / 8;
+    const bool pow2 = lanes > 0 && (lanes & (lanes - 1)) == 0 && lanes <= 32 && Cz % 8 == 0;
+    if (t == kElemBF16 && pow2 && H <= 8 && ((uintptr_t)z % 16) == 0) {
+        const int64_t ppb = 256 / lanes;
+        const unsigned gridv = (unsigned)std::min<int64_t>((pos + ppb - 1) / ppb, 148 * 32);
+        pair_bias_vec_kernel<8><<<gridv, 256, 0, stream>>>((const __nv_bfloat16 *)z, (const __nv_bfloat16 *)wb,
+                                                              (__nv_bfloat16 *)nb, nb_head_stride, pos_stride, R, Nk, Cz, H, lanes);
+        count_launch();
+        return true;
+    }
+    if (t == kElemF32) {
+        if (H <= 8)
+            pair_bias_kernel<float, 8><<<grid, 256, smem, stream>>>((const float *)z, (const float *)wb, (float *)nb,
+                                                                    nb_head_stride, pos_stride, R, Nk, Cz, H);
+        else
+            pair_bias_kernel<float, 16><<<grid, 256, smem, stream>>>((const float *)z, (const float *)wb, (float *)nb,
+                                                                     nb_head_stride, pos_stride, R, Nk, Cz, H);
+    } else {
+        if (H <= 8)
+            pair_bias_kernel<__nv_bfloat16, 8><<<grid, 256, smem, stream>>>(
+                (const __nv_bfloat16 *)z, (const __nv_bfloat16 *)wb, (__nv_bfloat16 *)nb, nb_head_stride, pos_stride, R, Nk, Cz, H);
+        else
+            pair_bias_kernel<__nv_bfloat16, 16><<<grid, 256, smem, stream>>>(
+                (const __nv_bfloat16 *)z, (const __nv_bfloat16 *)wb, (__nv_bfloat16 *)nb, nb_head_stride, pos_stride, R, Nk, Cz, H);
+    }
+    count_launch();
+    return true;
+}
+
+}  // namespace dev
+}  // namespace kutacc

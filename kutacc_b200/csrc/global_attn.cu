@@ -1,0 +1,436 @@
+// Extra-MSA global column attention (nchannels = 64), bandwidth-bound.
+//
+// Reference path: src/attention/global_attention.cpp:30-164 makes five passes over the [B, S, 64]
+// activations (pool, K, V, gate, output) and materialises k, v and gate. Here each batch column is
+// handled by three kernels that stream the activations with 128-bit loads and keep every
+// intermediate on chip:
+//   pool : partial masked sums of x over a slice of the rows                      (:44-75)
+//   core : q = q_avg.Wq^T; per row k = x.Wk^T, v = x.Wv^T, logits for all heads, online softmax,
+//          partial weighted sums of v                                              (:76-89, :96-133)
+//   out  : gate = x.Wg^T + bg; out = (sigmoid(gate) * wa).Wo^T + bo on tensor cores (:90-94, :134-163)
+// The batch is processed in groups whose activations fit in L2, so that the second and third read
+// of x are L2 hits and HBM sees one read of x and one write of out.
+//
+// bf16 rounding points of the reference that are kept: q_avg, q, k, v, logits, wa, gate, gated
+// gate, out. Probabilities are kept in fp32 (the reference rounds them to bf16 after normalising).
+#include "common.h"
+#include "kernels.h"
+#include "ptx_utils.cuh"
+
+#include <algorithm>
+
+namespace kutacc {
+namespace dev {
+
+namespace {
+
+constexpr int GC = 64;            // channels
+constexpr int POOL_THREADS = 256;
+constexpr int CORE_THREADS = 256;
+constexpr int OUT_ROWS = 128;     // rows per CTA of the output kernel (8 warps x 16 rows)
+
+__device__ __forceinline__ float rbf(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+// scratch layout per batch column b (all fp32):
+//   pool  : [nsplit][GC + 1]   partial sums and partial mask sum
+//   core  : [nsplit][H][2 + D] running max, running sum, partial weighted v
+struct Scratch {
+    float *pool;
+    float *core;
+    int nsplit;
+};
+
+// ---- pool ----------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(POOL_THREADS) global_pool_kernel(const __nv_bfloat16 *__restrict__ x,
+                                                                   const __nv_bfloat16 *__restrict__ mask,
+                                                                   Scratch sc, int b0, int S, int rows_per_split)
+{
+    const int b = b0 + blockIdx.y, split = blockIdx.x;
+    const int s_begin = split * rows_per_split, s_end = min(S, s_begin + rows_per_split);
+    const int sub = threadIdx.x & 7, rgrp = threadIdx.x >> 3;  // 8 lanes x 8 channels per row, 32 rows in flight
+    float acc[8] = {};
+    float msum = 0.f;
+    const __nv_bfloat16 *xb = x + (int64_t)b * S * GC;
+    const __nv_bfloat16 *mb = mask + (int64_t)b * S;
+    for (int s = s_begin + rgrp; s < s_end; s += POOL_THREADS / 8) {
+        const float mv = __bfloat162float(mb[s]);
+        const uint4 raw = __ldg(reinterpret_cast<const uint4 *>(xb + (int64_t)s * GC) + sub);
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            acc[2 * i] = fmaf(bf16lo_to_f32(w[i]), mv, acc[2 * i]);
+            acc[2 * i + 1] = fmaf(bf16hi_to_f32(w[i]), mv, acc[2 * i + 1]);
+        }
+        if (sub == 0) msum += mv;
+    }
+    __shared__ float red[POOL_THREADS / 8][GC + 1];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) red[rgrp][sub * 8 + i] = acc[i];
+    if (sub == 0) red[rgrp][GC] = msum;
+    __syncthreads();
+    if (threadIdx.x <= GC) {
+        float t = 0.f;
+        for (int r = 0; r < POOL_THREADS / 8; ++r) t += red[r][threadIdx.x];
+        sc.pool[((int64_t)b * sc.nsplit + split) * (GC + 1) + threadIdx.x] = t;
+    }
+}
+
+// ---- core ----------------------------------------------------------------------------------------
+template <int H, int D>
+__global__ void __launch_bounds__(CORE_THREADS) global_core_kernel(const __nv_bfloat16 *__restrict__ x,
+                                                                   const __nv_bfloat16 *__restrict__ mask,
+                                                                   const __nv_bfloat16 *__restrict__ wq,
+                                                                   const __nv_bfloat16 *__restrict__ wk,
+                                                                   const __nv_bfloat16 *__restrict__ wv, Scratch sc,
+                                                                   int b0, int S, int rows_per_split)
+{
+    static_assert(H * D == GC, "global attention is specialised to 64 channels");
+    __shared__ float s_qa[GC];
+    __shared__ float s_q[GC];
+    __shared__ float s_wk[D][GC];
+    __shared__ float s_wv[D][GC];
+    __shared__ float s_m[CORE_THREADS / 32][H];
+    __shared__ float s_part[CORE_THREADS / 32][H][1 + D];
+
+    const int b = b0 + blockIdx.y, split = blockIdx.x;
+    const int tid = threadIdx.x;
+    for (int i = tid; i < D * GC; i += CORE_THREADS) {
+        s_wk[i / GC][i % GC] = __bfloat162float(wk[i]);
+        s_wv[i / GC][i % GC] = __bfloat162float(wv[i]);
+    }
+    if (tid < GC) {
+        float t = 0.f, ms = 0.f;
+        for (int sp = 0; sp < sc.nsplit; ++sp) {
+            const float *pp = sc.pool + ((int64_t)b * sc.nsplit + sp) * (GC + 1);
+            t += pp[tid];
+            ms += pp[GC];
+        }
+        s_qa[tid] = rbf(t * (1.0f / (ms + 1e-10f)));
+    }
+    __syncthreads();
+    if (tid < GC) {
+        float t = 0.f;
+        for (int c = 0; c < GC; ++c) t = fmaf(s_qa[c], __bfloat162float(wq[tid * GC + c]), t);
+        s_q[tid] = rbf(t);
+    }
+    __syncthreads();
+
+    const float scale = 1.0f / sqrtf((float)D);
+    float m_run[H], l_run[H], acc[H][D];
+#pragma unroll
+    for (int h = 0; h < H; ++h) {
+        m_run[h] = -INFINITY;
+        l_run[h] = 0.f;
+#pragma unroll
+        for (int d = 0; d < D; ++d) acc[h][d] = 0.f;
+    }
+    const int s_begin = split * rows_per_split, s_end = min(S, s_begin + rows_per_split);
+    const __nv_bfloat16 *xb = x + (int64_t)b * S * GC;
+    const __nv_bfloat16 *mb = mask + (int64_t)b * S;
+    for (int s = s_begin + tid; s < s_end; s += CORE_THREADS) {
+        float kk[D], vv[D];
+#pragma unroll
+        for (int d = 0; d < D; ++d) kk[d] = vv[d] = 0.f;
+        const uint4 *xr = reinterpret_cast<const uint4 *>(xb + (int64_t)s * GC);
+#pragma unroll
+        for (int ch = 0; ch < GC / 8; ++ch) {
+            const uint4 raw = __ldg(xr + ch);
+            const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float x0 = bf16lo_to_f32(w[i]), x1 = bf16hi_to_f32(w[i]);
+                const int c = ch * 8 + 2 * i;
+#pragma unroll
+                for (int d = 0; d < D; ++d) {
+                    kk[d] = fmaf(x0, s_wk[d][c], kk[d]);
+                    kk[d] = fmaf(x1, s_wk[d][c + 1], kk[d]);
+                    vv[d] = fmaf(x0, s_wv[d][c], vv[d]);
+                    vv[d] = fmaf(x1, s_wv[d][c + 1], vv[d]);
+                }
+            }
+        }
+#pragma unroll
+        for (int d = 0; d < D; ++d) {
+            kk[d] = rbf(kk[d]);
+            vv[d] = rbf(vv[d]);
+        }
+        const float mbias = fmaf(__bfloat162float(mb[s]), 1e9f, -1e9f);
+#pragma unroll
+        for (int h = 0; h < H; ++h) {
+            float l = 0.f;
+#pragma unroll
+            for (int d = 0; d < D; ++d) l = fmaf(s_q[h * D + d], kk[d], l);
+            const float xv = rbf(l) * scale + mbias;
+            if (xv > m_run[h]) {
+                const float corr = __expf(m_run[h] - xv);
+                l_run[h] *= corr;
+#pragma unroll
+                for (int d = 0; d < D; ++d) acc[h][d] *= corr;
+                m_run[h] = xv;
+            }
+            const float pv = __expf(xv - m_run[h]);
+            l_run[h] += pv;
+#pragma unroll
+            for (int d = 0; d < D; ++d) acc[h][d] = fmaf(pv, vv[d], acc[h][d]);
+        }
+    }
+
+    // merge the per-thread softmax states: block max per head, then rescaled sums
+    const int warp = tid >> 5, lane = tid & 31;
+#pragma unroll
+    for (int h = 0; h < H; ++h) {
+        float mx = m_run[h];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        if (lane == 0) s_m[warp][h] = mx;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int h = 0; h < H; ++h) {
+        float mx = s_m[0][h];
+        for (int w = 1; w < CORE_THREADS / 32; ++w) mx = fmaxf(mx, s_m[w][h]);
+        const float f = (m_run[h] == -INFINITY) ? 0.f : __expf(m_run[h] - mx);
+        float lv = l_run[h] * f;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) lv += __shfl_xor_sync(0xffffffffu, lv, o);
+        if (lane == 0) s_part[warp][h][0] = lv;
+#pragma unroll
+        for (int d = 0; d < D; ++d) {
+            float av = acc[h][d] * f;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) av += __shfl_xor_sync(0xffffffffu, av, o);
+            if (lane == 0) s_part[warp][h][1 + d] = av;
+        }
+    }
+    __syncthreads();
+    float *dst = sc.core + ((int64_t)b * sc.nsplit + split) * H * (2 + D);
+    for (int i = tid; i < H * (1 + D); i += CORE_THREADS) {
+        const int h = i / (1 + D), j = i % (1 + D);
+        float t = 0.f;
+        for (int w = 0; w < CORE_THREADS / 32; ++w) t += s_part[w][h][j];
+        dst[h * (2 + D) + 1 + j] = t;
+        if (j == 0) {
+            float mx = s_m[0][h];
+            for (int w = 1; w < CORE_THREADS / 32; ++w) mx = fmaxf(mx, s_m[w][h]);
+            dst[h * (2 + D)] = mx;
+        }
+    }
+}
+
+// ---- out -----------------------------------------------------------------------------------------
+struct OutSmem {
+    __nv_bfloat16 x[OUT_ROWS * GC];   // activations tile, later reused to stage the output tile
+    __nv_bfloat16 wg[GC * GC];
+    __nv_bfloat16 wo[GC * GC];
+    float wa[GC];
+    float bg[GC];
+    float bo[GC];
+};
+
+template <int H, int D>
+__global__ void __launch_bounds__(256) global_out_kernel(const __nv_bfloat16 *__restrict__ x,
+                                                         const __nv_bfloat16 *__restrict__ wg,
+                                                         const float *__restrict__ bg,
+                                                         const __nv_bfloat16 *__restrict__ wo,
+                                                         const float *__restrict__ bo, __nv_bfloat16 *__restrict__ out,
+                                                         int64_t out_row_stride, Scratch sc, int b0, int S)
+{
+    __shared__ __align__(128) OutSmem sm;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int b = b0 + blockIdx.y;
+    const int s0 = blockIdx.x * OUT_ROWS;
+    const __nv_bfloat16 *xb = x + ((int64_t)b * S + s0) * GC;
+
+    for (int idx = tid; idx < OUT_ROWS * 8; idx += 256) {
+        const int r = idx >> 3, c = idx & 7;
+        const bool ok = s0 + r < S;
+        cp_async16(smem_u32(&sm.x[r * GC + swz8(r, c) * 8]), xb + (int64_t)(ok ? r : 0) * GC + c * 8, ok ? 16 : 0);
+    }
+    for (int idx = tid; idx < GC * 8; idx += 256) {
+        const int r = idx >> 3, c = idx & 7;
+        cp_async16(smem_u32(&sm.wg[r * GC + swz8(r, c) * 8]), wg + r * GC + c * 8, 16);
+        cp_async16(smem_u32(&sm.wo[r * GC + swz8(r, c) * 8]), wo + r * GC + c * 8, 16);
+    }
+    cp_async_commit();
+    if (tid < GC) {
+        // combine the split softmax states of this column into wa (bf16-rounded, as the reference stores it)
+        const int h = tid / D, d = tid % D;
+        float mx = -INFINITY;
+        for (int sp = 0; sp < sc.nsplit; ++sp)
+            mx = fmaxf(mx, sc.core[(((int64_t)b * sc.nsplit + sp) * H + h) * (2 + D)]);
+        float l = 0.f, a = 0.f;
+        for (int sp = 0; sp < sc.nsplit; ++sp) {
+            const float *pp = sc.core + (((int64_t)b * sc.nsplit + sp) * H + h) * (2 + D);
+            const float f = (pp[0] == -INFINITY) ? 0.f : __expf(pp[0] - mx);
+            l += pp[1] * f;
+            a += pp[2 + d] * f;
+        }
+        sm.wa[tid] = rbf(a / l);
+        sm.bg[tid] = bg[tid];
+        sm.bo[tid] = bo[tid];
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+
+    const int g = lane >> 2, t = lane & 3;
+    // gate = x . Wg^T : 16 rows x 64 per warp
+    float acc[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[i][e] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) {
+        uint32_t a[4];
+        {
+            const int r = warp * 16 + (lane & 15), c = ks * 2 + (lane >> 4);
+            ldmatrix_x4(a[0], a[1], a[2], a[3], smem_u32(&sm.x[r * GC + swz8(r, c) * 8]));
+        }
+#pragma unroll
+        for (int np = 0; np < 4; ++np) {
+            uint32_t b0r, b1r, b2r, b3r;
+            const int r = np * 16 + (lane & 7) + ((lane >> 4) << 3), c = ks * 2 + ((lane >> 3) & 1);
+            ldmatrix_x4(b0r, b1r, b2r, b3r, smem_u32(&sm.wg[r * GC + swz8(r, c) * 8]));
+            mma_bf16_16816(acc[np * 2], a, b0r, b1r);
+            mma_bf16_16816(acc[np * 2 + 1], a, b2r, b3r);
+        }
+    }
+    // gated = bf16(sigmoid(bf16(gate + bg)) * wa), packed as the A operand of the output product
+    uint32_t pf[4][4];
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+        const int c = nt * 8 + 2 * t;
+        float v[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int cc = c + (e & 1);
+            const float gate = rbf(acc[nt][e] + sm.bg[cc]);
+            v[e] = (1.0f / (1.0f + __expf(-gate))) * sm.wa[cc];
+        }
+        pf[nt >> 1][(nt & 1) * 2 + 0] = pack_bf16x2(v[0], v[1]);
+        pf[nt >> 1][(nt & 1) * 2 + 1] = pack_bf16x2(v[2], v[3]);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[i][e] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) {
+#pragma unroll
+        for (int np = 0; np < 4; ++np) {
+            uint32_t b0r, b1r, b2r, b3r;
+            const int r = np * 16 + (lane & 7) + ((lane >> 4) << 3), c = ks * 2 + ((lane >> 3) & 1);
+            ldmatrix_x4(b0r, b1r, b2r, b3r, smem_u32(&sm.wo[r * GC + swz8(r, c) * 8]));
+            mma_bf16_16816(acc[np * 2], pf[ks], b0r, b1r);
+            mma_bf16_16816(acc[np * 2 + 1], pf[ks], b2r, b3r);
+        }
+    }
+    // stage the 16 x 64 result of this warp in its own rows of the x tile, then store 16-byte rows
+    __syncwarp();
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+        const int c = nt * 8 + 2 * t;
+        const int r0 = warp * 16 + g, r1 = r0 + 8;
+        *reinterpret_cast<uint32_t *>(&sm.x[r0 * GC + swz8(r0, nt) * 8 + 2 * t]) =
+            pack_bf16x2(acc[nt][0] + sm.bo[c], acc[nt][1] + sm.bo[c + 1]);
+        *reinterpret_cast<uint32_t *>(&sm.x[r1 * GC + swz8(r1, nt) * 8 + 2 * t]) =
+            pack_bf16x2(acc[nt][2] + sm.bo[c], acc[nt][3] + sm.bo[c + 1]);
+    }
+    __syncwarp();
+    __nv_bfloat16 *ob = out + ((int64_t)b * S + s0) * out_row_stride;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int idx = lane + i * 32;
+        const int r = warp * 16 + (idx >> 3), c = idx & 7;
+        if (s0 + r < S) {
+            const uint4 val = *reinterpret_cast<const uint4 *>(&sm.x[r * GC + swz8(r, c) * 8]);
+            *reinterpret_cast<uint4 *>(ob + (int64_t)r * out_row_stride + c * 8) = val;
+        }
+    }
+}
+
+struct Plan {
+    int group;      // batch columns per L2-resident group
+    int nsplit;     // row slices per column in pool/core
+    int rows_per_split;
+};
+
+Plan make_plan(int B, int S)
+{
+    Plan p;
+    const int64_t col_bytes = (int64_t)S * GC * 2;
+    const int64_t l2_budget = (int64_t)32 << 20;
+    p.group = (int)std::max<int64_t>(1, std::min<int64_t>(B, l2_budget / std::max<int64_t>(col_bytes, 1)));
+    int ns = (148 * 4 + p.group - 1) / p.group;
+    ns = std::max(1, std::min(ns, 32));
+    ns = std::min(ns, std::max(1, S / 256));
+    p.nsplit = ns;
+    p.rows_per_split = (S + ns - 1) / ns;
+    return p;
+}
+
+template <int H, int D>
+void run_global(cudaStream_t stream, const void *x, const void *mask, const void *wq, const void *wk, const void *wv,
+                const void *wg, const float *bg, const void *wo, const float *bo, void *out, int64_t out_row_stride,
+                void *scratch, int B, int S)
+{
+    const Plan pl = make_plan(B, S);
+    Scratch sc;
+    sc.nsplit = pl.nsplit;
+    sc.pool = (float *)scratch;
+    sc.core = sc.pool + (int64_t)B * pl.nsplit * (GC + 1);
+    for (int b0 = 0; b0 < B; b0 += pl.group) {
+        const int nb = std::min(pl.group, B - b0);
+        dim3 g1((unsigned)pl.nsplit, (unsigned)nb);
+        {
+            KernelTimer timer__("global_pool");
+        global_pool_kernel<<<g1, POOL_THREADS, 0, stream>>>((const __nv_bfloat16 *)x, (const __nv_bfloat16 *)mask, sc,
+                                                            b0, S, pl.rows_per_split);
+        }
+        {
+            KernelTimer timer__("global_core");
+        global_core_kernel<H, D><<<g1, CORE_THREADS, 0, stream>>>(
+            (const __nv_bfloat16 *)x, (const __nv_bfloat16 *)mask, (const __nv_bfloat16 *)wq,
+            (const __nv_bfloat16 *)wk, (const __nv_bfloat16 *)wv, sc, b0, S, pl.rows_per_split);
+        }
+        dim3 g3((unsigned)((S + OUT_ROWS - 1) / OUT_ROWS), (unsigned)nb);
+        {
+            KernelTimer timer__("global_out");
+        global_out_kernel<H, D><<<g3, 256, 0, stream>>>((const __nv_bfloat16 *)x, (const __nv_bfloat16 *)wg, bg,
+                                                        (const __nv_bfloat16 *)wo, bo, (__nv_bfloat16 *)out,
+                                                        out_row_stride, sc, b0, S);
+        }
+        count_launch(3);
+    }
+}
+
+}  // namespace
+
+size_t global_attention_scratch_bytes(int B, int S, int H, int D)
+{
+    const Plan pl = make_plan(B, S);
+    return ((size_t)B * pl.nsplit * (GC + 1) + (size_t)B * pl.nsplit * H * (2 + D)) * sizeof(float);
+}
+
+bool launch_global_attention_bf16(cudaStream_t stream, const void *x, const void *mask, const void *wq,
+                                  const void *wk, const void *wv, const void *wg, const float *bg, const void *wo,
+                                  const float *bo, void *out, int64_t out_row_stride, void *scratch, int B, int S,
+                                  int H, int D)
+{
+    if (H * D != GC || (out_row_stride % 8) != 0 || B > 65535) return false;
+#define KUTACC_GLOBAL_CASE(HH, DD)                                                                              \
+    if (H == HH && D == DD) {                                                                                   \
+        run_global<HH, DD>(stream, x, mask, wq, wk, wv, wg, bg, wo, bo, out, out_row_stride, scratch, B, S);   \
+        return true;                                                                                            \
+    }
+    KUTACC_GLOBAL_CASE(8, 8)
+    KUTACC_GLOBAL_CASE(4, 16)
+    KUTACC_GLOBAL_CASE(16, 4)
+    KUTACC_GLOBAL_CASE(2, 32)
+    KUTACC_GLOBAL_CASE(1, 64)
+#undef KUTACC_GLOBAL_CASE
+    return false;
+}
+
+}  // namespace dev
+}  // namespace kutacc

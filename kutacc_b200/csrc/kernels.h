@@ -1,0 +1,59 @@
+// Launchers of the device kernels. Plain pointers and integers only: the operator entry points
+// translate tensor descriptors into these calls. Every launcher enqueues on `stream` and returns
+// false (after reporting through KUTACC_CHECK) when the shape is outside what it supports.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace kutacc {
+namespace dev {
+
+enum ElemType { kElemBF16 = 0, kElemF32 = 1 };
+
+// ---- projections ---------------------------------------------------------------------------------
+// Fused Q/K/V/gate projection of x [M = B*S, C] with four [C, C] weights (W[out][in]).
+//   q, k, v : [B, H, S, D] (q pre-multiplied by q_scale), gate : [B, S, C] with bg added.
+// bf16 in / bf16 out, fp32 accumulate. Needs C % 64 == 0.
+bool launch_proj_qkvg_bf16(cudaStream_t stream, const void *x, const void *wq, const void *wk, const void *wv,
+                           const void *wg, const float *bg, void *q, void *k, void *v, void *gate, int B, int S,
+                           int H, int D, float q_scale);
+
+// out[m, :] = a[m, :] . w^T + bias, a [M, K] (row stride lda), w [N, K], out row stride ldo.
+// bf16 in / bf16 out, fp32 accumulate. Needs K % 64 == 0 and N % 64 == 0.
+bool launch_linear_bias_bf16(cudaStream_t stream, const void *a, int64_t lda, const void *w, const float *bias,
+                             void *out, int64_t ldo, int64_t M, int N, int K);
+
+// ---- fused attention core ------------------------------------------------------------------------
+// avg[b, s, h*D + d] = sigmoid(gate[b, s, h*D + d]) * softmax_k(q.k + bias[b,k] + nb[h,s,k]) . v
+// q already carries the 1/sqrt(D) scale. bf16; D in {16, 32, 64}. nb may be null.
+bool launch_attn_core_bf16(cudaStream_t stream, const void *q, const void *k, const void *v, const void *gate,
+                           const void *bias, int64_t bias_stride0, const void *nb, int64_t nb_stride_h,
+                           int64_t nb_stride_q, void *avg, int B, int S, int H, int D);
+
+// ---- generic (any shape, bf16 or fp32 storage, fp32 math) ------------------------------------------
+// c[m, n] = sum_k a[m, k] * w[n, k] (+ bias[n]) (+ beta * c[m, n]); a row stride lda, w row stride
+// ldw, c row stride ldc.
+bool launch_gemm_generic(cudaStream_t stream, ElemType t, const void *a, int64_t lda, const void *w, int64_t ldw,
+                         const float *bias, float beta, void *c, int64_t ldc, int64_t M, int64_t N, int64_t K);
+// Attention core on [B, S, C]-shaped q/k/v/gate (head h at channel offset h*D); scale applied here.
+bool launch_attn_generic(cudaStream_t stream, ElemType t, const void *q, const void *k, const void *v,
+                         const void *gate, const void *bias, int64_t bias_stride0, const void *nb,
+                         int64_t nb_stride_h, int64_t nb_stride_q, void *avg, int B, int S, int H, int D,
+                         float scale);
+
+// ---- pair-bias projection --------------------------------------------------------------------------
+// y[h * head_stride + (r * Nk + k) * pos_stride] = z[r, k, :] . wb[h, :], z [R, Nk, Cz] contiguous.
+// (head_stride = R*Nk, pos_stride = 1) writes [H, R, Nk]; (1, H) writes [R*Nk, H]. H <= 16.
+bool launch_pair_bias(cudaStream_t stream, ElemType t, const void *z, const void *wb, void *nb,
+                      int64_t nb_head_stride, int64_t pos_stride, int64_t R, int64_t Nk, int Cz, int H);
+
+// ---- global attention (bf16, C = 64) ---------------------------------------------------------------
+// scratch: qk [B, H, 64] fp32-sized slots and wa [B, 64]; see global_attention.cu
+size_t global_attention_scratch_bytes(int B, int S, int H, int D);
+bool launch_global_attention_bf16(cudaStream_t stream, const void *x, const void *mask, const void *wq,
+                                  const void *wk, const void *wv, const void *wg, const float *bg, const void *wo,
+                                  const float *bo, void *out, int64_t out_row_stride, void *scratch, int B, int S,
+                                  int H, int D);
+
+}  // namespace dev
+}  // namespace kutacc

@@ -1,0 +1,138 @@
+// kutacc_af2_linear, weight prepack, pack size query, and the fused pair-bias projection.
+// Replaces src/linear/linear.cpp:21-50, src/linear/mm.cpp:94-110, src/utils/blas.cpp:93-98.
+#include <cuda_runtime.h>
+
+#include <cstring>
+
+#include "common.h"
+#include "kernels.h"
+
+extern "C" void kutacc_af2_linear(kutacc_tensor_h act_h, kutacc_tensor_h weight_h, float *bias_data,
+                                  kutacc_tensor_h result_h, int64_t beta)
+{
+    using namespace kutacc;
+    KUTACC_CHECK(act_h != nullptr && weight_h != nullptr && result_h != nullptr, "kutacc_af2_linear: nullptr error");
+    if (kutacc_check_err_set) return;
+    Tensor &act = *as_tensor(act_h), &weight = *as_tensor(weight_h), &result = *as_tensor(result_h);
+    KUTACC_CHECK(act.dim() >= 1 && weight.dim() >= 1 && act.data_ptr() && weight.data_ptr() && result.data_ptr(),
+                 "kutacc_af2_linear: empty tensor");
+    if (kutacc_check_err_set) return;
+    // shapes as linear.cpp:23-25: m = numel / last, n = rows of weight, k = last dim of act
+    const int64_t k = act.sizes().back();
+    KUTACC_CHECK(k > 0 && weight.sizes().back() == k, "shape invalid, act k: [", k, "], weight k: [",
+                 weight.sizes().back(), "]");
+    if (kutacc_check_err_set) return;
+    const int64_t m = act.numel() / k, n = weight.numel() / k;
+    const int64_t lda = act.dim() >= 2 ? act.strides()[(size_t)act.dim() - 2] : k;
+    const int64_t ldw = weight.dim() >= 2 ? weight.strides()[(size_t)weight.dim() - 2] : k;
+    const DType dt = act.dtype();
+    KUTACC_CHECK(dt == kBF16 || dt == kFP32, "addmm dtype invalid, a: [", (int)dt, "]");
+    KUTACC_CHECK(m > 0 && n > 0 && lda >= k && ldw >= k, "kutacc_af2_linear: shape/stride invalid m=", m, " n=", n,
+                 " lda=", lda, " ldw=", ldw);
+    if (kutacc_check_err_set) return;
+    const size_t es = dtype_size(dt);
+    const size_t a_bytes = (size_t)((m - 1) * lda + k) * es, w_bytes = (size_t)((n - 1) * ldw + k) * es,
+                 r_bytes = (size_t)m * n * es, b_bytes = bias_data ? (size_t)n * 4 : 0;
+
+    Runtime &rt = runtime();
+    cudaStream_t stream = (cudaStream_t)rt.stream;
+    const size_t stage = staged_bytes_needed(act.data_ptr(), a_bytes) + staged_bytes_needed(weight.data_ptr(), w_bytes) +
+                         staged_bytes_needed(result.data_ptr(), r_bytes) + staged_bytes_needed(bias_data, b_bytes);
+    if (!rt.reserve_stage(stage)) return;
+    DeviceArg d_a = resolve_in(act.data_ptr(), a_bytes), d_w = resolve_in(weight.data_ptr(), w_bytes);
+    DeviceArg d_b = bias_data ? resolve_in(bias_data, b_bytes) : DeviceArg{};
+    // beta != 0 reads the old result (linear.cpp:32)
+    DeviceArg d_r = beta != 0 ? resolve_in(result.data_ptr(), r_bytes) : resolve_out(result.data_ptr(), r_bytes);
+    if (d_r.staged && beta != 0) d_r.host = result.data_ptr();
+    if (kutacc_check_err_set) return;
+
+    const dev::ElemType et = dt == kFP32 ? dev::kElemF32 : dev::kElemBF16;
+    bool ok = false;
+    const bool a16 = (((uintptr_t)d_a.dev | (uintptr_t)d_w.dev) & 15u) == 0;
+    if (dt == kBF16 && beta == 0 && a16 && k % 64 == 0 && n % 64 == 0 && lda % 8 == 0 && ldw == k) {
+        ok = dev::launch_linear_bias_bf16(stream, d_a.dev, lda, d_w.dev, (const float *)d_b.dev, d_r.dev, n, m, (int)n,
+                                          (int)k);
+    } else if (beta == 0 && bias_data == nullptr && n <= 16 && lda == k && ldw == k && k <= INT32_MAX) {
+        // skinny projection (the pair-bias shape): bandwidth-bound kernel, result [m, n]
+        ok = dev::launch_pair_bias(stream, et, d_a.dev, d_w.dev, d_r.dev, 1, n, m, 1, (int)k, (int)n);
+    }
+    if (!ok) {
+        float betaf = (float)beta;
+        if (dt == kBF16) {  // beta passes through bf16 in the reference (linear.cpp:32)
+            uint32_t u;
+            std::memcpy(&u, &betaf, 4);
+            u = (u + 0x7fffu + ((u >> 16) & 1u)) & 0xffff0000u;
+            std::memcpy(&betaf, &u, 4);
+        }
+        ok = dev::launch_gemm_generic(stream, et, d_a.dev, lda, d_w.dev, ldw, (const float *)d_b.dev, betaf, d_r.dev, n,
+                                      m, n, k);
+    }
+    KUTACC_CHECK(ok, "kutacc_af2_linear: no device kernel for m=", m, " n=", n, " k=", k);
+    finish_out(d_r);
+    end_of_call();
+}
+
+// The packed image is the dense row-major [n, k] matrix; rows are copied block by block as the
+// reference does (mm.cpp:97-106). Host or device pointers; num_threads is ignored.
+extern "C" void kutacc_af2_linear_weight_prepack(const uint16_t *weight, uint16_t *result, int64_t n, int64_t k,
+                                                 int64_t ldb, int64_t num_threads)
+{
+    using namespace kutacc;
+    (void)num_threads;
+    KUTACC_CHECK(weight != nullptr && result != nullptr && n > 0 && k > 0 && ldb >= k,
+                 "kutacc_af2_linear_weight_prepack: invalid argument");
+    if (kutacc_check_err_set) return;
+    const bool dsrc = is_device_pointer(weight), ddst = is_device_pointer(result);
+    if (!dsrc && !ddst) {
+        for (int64_t r = 0; r < n; ++r) std::memcpy(result + r * k, weight + r * ldb, (size_t)k * 2);
+        return;
+    }
+    KUTACC_CUDA(cudaMemcpy2DAsync(result, (size_t)k * 2, weight, (size_t)ldb * 2, (size_t)k * 2, (size_t)n,
+                                  cudaMemcpyDefault, (cudaStream_t)runtime().stream));
+    end_of_call();
+}
+
+extern "C" size_t kutacc_af2_gemm_pack_get_size(char identifier, char transa, char transb, int m, int n, int k)
+{
+    (void)transa;
+    (void)transb;
+    if (m < 0 || n < 0 || k < 0) return 0;
+    if (identifier == 'A' || identifier == 'a') return (size_t)m * (size_t)k;
+    return (size_t)k * (size_t)n;
+}
+
+// nb[h, r, c] = z[r, c, :] . wb[h, :]
+extern "C" void kutacc_b200_pair_bias(kutacc_tensor_h z_h, kutacc_tensor_h wb_h, kutacc_tensor_h nb_h)
+{
+    using namespace kutacc;
+    KUTACC_CHECK(z_h != nullptr && wb_h != nullptr && nb_h != nullptr, "kutacc_b200_pair_bias: nullptr error");
+    if (kutacc_check_err_set) return;
+    Tensor &z = *as_tensor(z_h), &wb = *as_tensor(wb_h), &nb = *as_tensor(nb_h);
+    KUTACC_CHECK(z.dim() == 3 && wb.dim() == 2 && nb.dim() == 3 && z.data_ptr() && wb.data_ptr() && nb.data_ptr(),
+                 "kutacc_b200_pair_bias: z [rows, keys, c_z], wb [nheads, c_z], nb [nheads, rows, keys] expected");
+    if (kutacc_check_err_set) return;
+    const int64_t R = z.sizes()[0], Nk = z.sizes()[1], Cz = z.sizes()[2], H = wb.sizes()[0];
+    const DType dt = z.dtype();
+    KUTACC_CHECK((dt == kBF16 || dt == kFP32) && wb.sizes()[1] == Cz && nb.sizes()[0] == H && nb.sizes()[1] == R &&
+                     nb.sizes()[2] == Nk && z.strides()[2] == 1 && z.strides()[1] == Cz && z.strides()[0] == Nk * Cz &&
+                     nb.strides()[2] == 1 && nb.strides()[1] == Nk && wb.strides()[1] == 1 && wb.strides()[0] == Cz &&
+                     R > 0 && Nk > 0 && Cz > 0 && H > 0 && H <= 16 && Cz <= 4096,
+                 "kutacc_b200_pair_bias: shape/stride invalid");
+    if (kutacc_check_err_set) return;
+    const size_t es = dtype_size(dt);
+    const int64_t hs = nb.strides()[0];
+    const size_t z_bytes = (size_t)R * Nk * Cz * es, w_bytes = (size_t)H * Cz * es,
+                 nb_bytes = (size_t)((H - 1) * hs + R * Nk) * es;
+    Runtime &rt = runtime();
+    const size_t stage = staged_bytes_needed(z.data_ptr(), z_bytes) + staged_bytes_needed(wb.data_ptr(), w_bytes) +
+                         staged_bytes_needed(nb.data_ptr(), nb_bytes);
+    if (!rt.reserve_stage(stage)) return;
+    DeviceArg d_z = resolve_in(z.data_ptr(), z_bytes), d_w = resolve_in(wb.data_ptr(), w_bytes),
+              d_n = resolve_out(nb.data_ptr(), nb_bytes);
+    if (kutacc_check_err_set) return;
+    const bool ok = dev::launch_pair_bias((cudaStream_t)rt.stream, dt == kFP32 ? dev::kElemF32 : dev::kElemBF16,
+                                          d_z.dev, d_w.dev, d_n.dev, hs, 1, R, Nk, (int)Cz, (int)H);
+    KUTACC_CHECK(ok, "kutacc_b200_pair_bias: no device kernel for nheads=", H, " c_z=", Cz);
+    finish_out(d_n);
+    end_of_call();
+}

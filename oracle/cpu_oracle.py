@@ -1,0 +1,141 @@
+"""ctypes front end of the CPU oracle (test infrastructure).
+
+Arrays are numpy: bf16 data travels as uint16 bit patterns, fp32 as float32. Only tests, the
+smoke check and the benchmark's CPU-baseline leg import this module.
+"""
+import ctypes as C
+import os
+
+import numpy as np
+
+from . import build as _build
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        path = _build.LIB if os.path.exists(_build.LIB) else _build.build()
+        _lib = C.CDLL(path)
+        _lib.orc_fexpa_exp.restype = C.c_float
+        _lib.orc_fexpa_exp.argtypes = [C.c_float]
+        _lib.orc_num_threads.restype = C.c_int
+    return _lib
+
+
+def _p(a):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+def num_threads() -> int:
+    return int(lib().orc_num_threads())
+
+
+def f32_to_bf16(a: np.ndarray) -> np.ndarray:
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    out = np.empty(a.shape, dtype=np.uint16)
+    lib().orc_f32_to_bf16(_p(a), _p(out), C.c_int64(a.size))
+    return out
+
+
+def bf16_to_f32(a: np.ndarray) -> np.ndarray:
+    a = np.ascontiguousarray(a, dtype=np.uint16)
+    out = np.empty(a.shape, dtype=np.float32)
+    lib().orc_bf16_to_f32(_p(a), _p(out), C.c_int64(a.size))
+    return out
+
+
+def fexpa_exp(x: float) -> float:
+    return float(lib().orc_fexpa_exp(C.c_float(x)))
+
+
+def gating_attention_bf16(x, wq, wk, wv, wg, bg, wo, bo, bias, nb, B, S, H, D, block_size=128, dumps=False):
+    """Faithful mode. x [B*S,C] u16, w* [C,C] u16, bg/bo [C] f32, bias [B,S] u16, nb [H,S,S] u16 or None."""
+    Cn = H * D
+    x = np.ascontiguousarray(x, dtype=np.uint16)
+    out = np.empty((B, S, Cn), dtype=np.uint16)
+    bias = np.ascontiguousarray(bias, dtype=np.uint16)
+    if nb is not None:
+        nb = np.ascontiguousarray(nb, dtype=np.uint16)
+    d = {}
+    if dumps:
+        for name in ("q", "k", "g", "avg"):
+            d[name] = np.empty((B, S, H, D), dtype=np.uint16)
+        d["v"] = np.empty((H, D, B, S), dtype=np.uint16)
+    lib().orc_gating_attention_bf16(
+        _p(x), _p(wq), _p(wk), _p(wv), _p(wg), _p(bg), _p(wo), _p(bo),
+        _p(bias), C.c_int64(S), _p(nb), C.c_int64(S * S), C.c_int64(S),
+        C.c_int64(B), C.c_int64(S), C.c_int64(H), C.c_int64(D), C.c_int64(block_size), _p(out),
+        _p(d.get("q")), _p(d.get("k")), _p(d.get("v")), _p(d.get("g")), _p(d.get("avg")))
+    return (out, d) if dumps else out
+
+
+def gating_attention_exact(x, wq, wk, wv, wg, bg, wo, bo, bias, nb, B, S, H, D):
+    """Exact mode: every array float32; double accumulation inside."""
+    Cn = H * D
+    f = lambda a: None if a is None else np.ascontiguousarray(a, dtype=np.float32)
+    x, wq, wk, wv, wg, bg, wo, bo, bias, nb = map(f, (x, wq, wk, wv, wg, bg, wo, bo, bias, nb))
+    out = np.empty((B, S, Cn), dtype=np.float32)
+    lib().orc_gating_attention_exact(
+        _p(x), _p(wq), _p(wk), _p(wv), _p(wg), _p(bg), _p(wo), _p(bo),
+        _p(bias), C.c_int64(S), _p(nb), C.c_int64(S * S), C.c_int64(S),
+        C.c_int64(B), C.c_int64(S), C.c_int64(H), C.c_int64(D), _p(out))
+    return out
+
+
+def global_attention_bf16(x, mask, wq, wk, wv, wg, bg, wo, bo, B, S, H, D):
+    Cn = H * D
+    out = np.empty((B, S, Cn), dtype=np.uint16)
+    x = np.ascontiguousarray(x, dtype=np.uint16)
+    mask = np.ascontiguousarray(mask, dtype=np.uint16)
+    lib().orc_global_attention_bf16(_p(x), _p(mask), _p(wq), _p(wk), _p(wv), _p(wg), _p(bg), _p(wo), _p(bo),
+                                    C.c_int64(B), C.c_int64(S), C.c_int64(H), C.c_int64(D), _p(out))
+    return out
+
+
+def global_attention_exact(x, mask, wq, wk, wv, wg, bg, wo, bo, B, S, H, D):
+    Cn = H * D
+    f = lambda a: np.ascontiguousarray(a, dtype=np.float32)
+    x, mask, wq, wk, wv, wg, bg, wo, bo = map(f, (x, mask, wq, wk, wv, wg, bg, wo, bo))
+    out = np.empty((B, S, Cn), dtype=np.float32)
+    lib().orc_global_attention_exact(_p(x), _p(mask), _p(wq), _p(wk), _p(wv), _p(wg), _p(bg), _p(wo), _p(bo),
+                                     C.c_int64(B), C.c_int64(S), C.c_int64(H), C.c_int64(D), _p(out))
+    return out
+
+
+def linear_bf16(act, w, bias, beta=0, result=None):
+    """act [M,K] u16, w [N,K] u16, bias [N] f32 or None; returns [M,N] u16."""
+    act = np.ascontiguousarray(act, dtype=np.uint16)
+    w = np.ascontiguousarray(w, dtype=np.uint16)
+    M, K = act.shape
+    N = w.shape[0]
+    res = np.zeros((M, N), dtype=np.uint16) if result is None else np.ascontiguousarray(result, dtype=np.uint16).copy()
+    lib().orc_linear_bf16(_p(act), C.c_int64(K), _p(w), C.c_int64(K), _p(bias), C.c_int64(M), C.c_int64(N),
+                          C.c_int64(K), C.c_int64(beta), _p(res))
+    return res
+
+
+def linear_exact(act, w, bias, beta=0, result=None):
+    act = np.ascontiguousarray(act, dtype=np.float32)
+    w = np.ascontiguousarray(w, dtype=np.float32)
+    M, K = act.shape
+    N = w.shape[0]
+    res = np.zeros((M, N), dtype=np.float32) if result is None else np.ascontiguousarray(result, dtype=np.float32).copy()
+    lib().orc_linear_exact(_p(act), C.c_int64(K), _p(w), C.c_int64(K), _p(bias), C.c_int64(M), C.c_int64(N),
+                           C.c_int64(K), C.c_int64(beta), _p(res))
+    return res
+
+
+def all_gather_bytes(shards, out_shape, data_size0):
+    """shards: list of contiguous uint8 arrays [a,b,len] (one per rank); returns gathered [m,n,len]."""
+    world = len(shards)
+    m, n, ln = out_shape
+    out = np.zeros((m, n, ln), dtype=np.uint8)
+    shards = [np.ascontiguousarray(s, dtype=np.uint8) for s in shards]
+    ptrs = (C.c_void_p * world)(*[s.ctypes.data for s in shards])
+    ds0 = (C.c_int64 * world)(*[s.shape[1] * ln for s in shards])
+    ds1 = ln
+    lib().orc_all_gather_bytes(ptrs, C.c_int64(world), C.c_int64(data_size0), ds0, C.c_int64(ds1),
+                               _p(out), C.c_int64(m), C.c_int64(n), C.c_int64(ln), C.c_int64(n * ln), C.c_int64(ln))
+    return out

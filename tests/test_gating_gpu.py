@@ -1,0 +1,132 @@
+"""Parity of kutacc_af2_gating_attention (CUDA, through the C ABI) with the CPU oracle."""
+import numpy as np
+import pytest
+import torch
+
+from kutacc_b200 import api, runner
+from kutacc_b200 import workloads as W
+from tests import helpers
+
+pytestmark = pytest.mark.gpu
+
+
+def _run(w, device=True):
+    case = runner.DeviceCase(w) if device else runner.HostCase(w)
+    out = case.run()
+    torch.cuda.synchronize()
+    return runner.out_to_f32(out)
+
+
+# (B, S, H, D, with_nb): tensor-core path shapes, including ragged sequence lengths
+FAST_SHAPES = [
+    (2, 64, 2, 32, True), (3, 70, 2, 32, True), (2, 129, 4, 32, False), (1, 200, 4, 16, True),
+    (2, 96, 1, 64, True), (5, 33, 2, 32, False), (2, 384, 4, 32, True), (1, 8, 2, 32, True),
+]
+
+
+@pytest.mark.parametrize("B,S,H,D,with_nb", FAST_SHAPES)
+def test_bf16_tensor_core_path_matches_faithful_oracle(kutacc_lib, B, S, H, D, with_nb):
+    w = W.random_gating_case(seed=100 + S, B=B, S=S, H=H, D=D, with_nb=with_nb, full_mask_rows=1 if B > 1 else 0)
+    before = api.launch_count()
+    got = _run(w)
+    assert api.launch_count() - before == 3            # projection, attention core, output projection
+    ref = helpers.oracle_faithful(w)
+    assert helpers.rel_err(got, ref) <= helpers.BF16_TOL
+    assert helpers.rel_err(got, helpers.oracle_exact(w)) <= helpers.BF16_TOL
+    assert np.isfinite(got).all()
+
+
+# shapes outside the tensor-core kernels: odd head size / channel count, unaligned pair-bias rows
+GENERIC_SHAPES = [(2, 37, 3, 8, True), (1, 50, 2, 12, False), (2, 45, 2, 32, True), (1, 40, 1, 80, True)]
+
+
+@pytest.mark.parametrize("B,S,H,D,with_nb", GENERIC_SHAPES)
+def test_bf16_generic_path_matches_faithful_oracle(kutacc_lib, B, S, H, D, with_nb):
+    w = W.random_gating_case(seed=200 + S, B=B, S=S, H=H, D=D, with_nb=with_nb, full_mask_rows=0)
+    got = _run(w)
+    assert helpers.rel_err(got, helpers.oracle_faithful(w)) <= helpers.BF16_TOL
+
+
+@pytest.mark.parametrize("B,S,H,D,with_nb", [(2, 64, 2, 32, True), (3, 50, 4, 16, False), (1, 100, 8, 32, True)])
+def test_fp32_matches_exact_oracle(kutacc_lib, B, S, H, D, with_nb):
+    w = W.random_gating_case(seed=300 + S, B=B, S=S, H=H, D=D, dtype="fp32", with_nb=with_nb, full_mask_rows=1)
+    got = _run(w)
+    assert helpers.rel_err(got, helpers.oracle_exact(w)) <= helpers.FP32_TOL
+
+
+def test_fully_masked_row_is_uniform(kutacc_lib):
+    # every key of batch row 0 carries -1e9: the softmax must be uniform, not NaN or zero
+    w = W.random_gating_case(seed=5, B=2, S=128, H=2, D=32, with_nb=True, full_mask_rows=1)
+    got = _run(w)
+    ref = helpers.oracle_faithful(w)
+    assert np.isfinite(got).all()
+    assert helpers.rel_err(got[0], ref[0]) <= helpers.BF16_TOL
+
+
+def test_host_pointers_give_the_same_bits_as_device_pointers(kutacc_lib):
+    w = W.random_gating_case(seed=7, B=3, S=96, H=4, D=32, with_nb=True)
+    dev = _run(w, device=True)
+    host = _run(w, device=False)
+    assert np.array_equal(dev, host)
+
+
+def test_strided_out_and_bias(kutacc_lib):
+    # out row stride (strides[1]) and bias row stride (strides[0]) are honoured
+    w = W.random_gating_case(seed=9, B=2, S=64, H=2, D=32, with_nb=False)
+    case = runner.DeviceCase(w)
+    dense = runner.out_to_f32(case.run()).copy()
+    pad = torch.full((w.B, w.S, w.C + 16), 7.0, dtype=torch.bfloat16, device="cuda:0")
+    bias_pad = torch.zeros((w.B, w.S + 8), dtype=torch.bfloat16, device="cuda:0")
+    bias_pad[:, :w.S] = case.bias
+    api.gating_attention(case.t_x, case.inputs, api.tensor(bias_pad, sizes=[w.B, w.S], strides=[w.S + 8, 1]), case.t_nb,
+                         case.weights, api.tensor(pad, sizes=[w.B, w.S, w.C], strides=[w.S * (w.C + 16), w.C + 16, 1]))
+    torch.cuda.synchronize()
+    got = pad.float().cpu().numpy()
+    assert np.array_equal(got[:, :, :w.C], dense)
+    assert (got[:, :, w.C:] == 7.0).all()              # padding untouched
+
+
+@pytest.mark.parametrize("name,rows", [("triangle_start_384", 24), ("msa_col_512", 12), ("triangle_end_1024", 4)])
+def test_benchmark_shapes_subsampled_rows(kutacc_lib, name, rows):
+    # the benchmark shapes at full sequence length on the first `rows` batch rows
+    w = W.make(name, rows=rows)
+    got = _run(w)
+    assert helpers.rel_err(got, helpers.oracle_faithful(w)) <= helpers.BF16_TOL
+
+
+def test_msa_row_fp32_shape_subsampled(kutacc_lib):
+    w = W.make("msa_row_fp32", rows=6)
+    got = _run(w)
+    assert helpers.rel_err(got, helpers.oracle_exact(w)) <= helpers.FP32_TOL
+
+
+def test_full_size_properties_triangle_start(kutacc_lib):
+    """Size-independent checks at the full benchmark size (the oracle is too slow for all of it):
+    rows are independent problems, and the output bias enters linearly."""
+    w = W.make("triangle_start_384")
+    case = runner.DeviceCase(w)
+    full = runner.out_to_f32(case.run()).copy()
+    assert np.isfinite(full).all()
+    # (1) a sub-batch gives bit-identical rows
+    sub = W.make("triangle_start_384", rows=16)
+    assert np.array_equal(runner.out_to_f32(runner.DeviceCase(sub).run()), full[:16])
+    # (2) oracle on a few rows spread over the batch, including a fully masked one
+    masked = np.where(w.arrays["mask"].sum(1) == 0)[0]
+    rows = sorted(set([0, 191, 383] + masked[:1].tolist()))
+    pick = W.Workload(name="pick", kind="gating", dtype="bf16", B=len(rows), S=w.S, H=w.H, D=w.D, seed=0, has_nb=True)
+    pick.arrays = dict(w.arrays)
+    pick.arrays["x"] = w.arrays["x"][rows]
+    pick.arrays["bias"] = w.arrays["bias"][rows]
+    assert helpers.rel_err(full[rows], helpers.oracle_faithful(pick)) <= helpers.BF16_TOL
+    # (3) shifting the output bias shifts the output by the same amount (up to bf16 rounding)
+    case.bo += 0.5
+    shifted = runner.out_to_f32(case.run())
+    assert np.abs((shifted - full) - 0.5).max() <= 2.0 ** -6 * max(1.0, np.abs(full).max())
+
+
+def test_repeat_calls_are_deterministic(kutacc_lib):
+    w = W.random_gating_case(seed=13, B=4, S=160, H=4, D=32, with_nb=True)
+    case = runner.DeviceCase(w)
+    a = runner.out_to_f32(case.run()).copy()
+    b = runner.out_to_f32(case.run()).copy()
+    assert np.array_equal(a, b)

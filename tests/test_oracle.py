@@ -1,0 +1,172 @@
+"""The CPU oracle against golden vectors, textbook float64 formulas and known properties."""
+import os
+
+import numpy as np
+import pytest
+
+from kutacc_b200 import workloads as W
+from oracle import cpu_oracle as O
+from tests import helpers
+
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def test_bf16_conversion_matches_torch():
+    import torch
+    rng = np.random.default_rng(0)
+    a = np.concatenate([rng.standard_normal(4096).astype(np.float32) * 10.0 ** rng.integers(-6, 6, 4096),
+                        np.array([0.0, -0.0, 1.0, 1.00390625, 1.01171875, 3.3895314e38, np.inf, -np.inf], np.float32)])
+    ours = O.f32_to_bf16(a)
+    ref = torch.from_numpy(a).to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)
+    assert np.array_equal(ours, ref)
+    assert np.array_equal(W.bf16_bits(a), ref)                    # the numpy twin used by the workloads
+    assert np.array_equal(O.bf16_to_f32(ours), W.as_f32(ours))
+
+
+def test_fexpa_exp_properties():
+    # exact at multiples of ln2/64 that land on table entry 0: powers of two
+    assert O.fexpa_exp(0.0) == 1.0
+    assert O.fexpa_exp(-1e9) == 0.0            # very negative saturates to +0 (softmax of masked keys)
+    assert O.fexpa_exp(-1e4) == 0.0
+    xs = np.linspace(-20.0, 5.0, 2001)
+    ys = np.array([O.fexpa_exp(float(x)) for x in xs])
+    rel = np.abs(ys - np.exp(xs)) / np.exp(xs)
+    assert rel.max() <= 2 ** (1 / 128) - 1 + 1e-4      # quantised to 1/64 octave
+    assert np.all(np.diff(ys) >= 0)                    # monotone
+    # the table: result is 2^(n/64) for integer n
+    n = np.round(np.log2(ys[ys > 0]) * 64)
+    assert np.allclose(np.log2(ys[ys > 0]) * 64, n, atol=1e-3)
+
+
+def _textbook_gating(w):
+    A = w.arrays
+    B, S, H, D, C = w.B, w.S, w.H, w.D, w.C
+    x = A["x"].astype(np.float64)
+    q = (x @ A["wq"].T.astype(np.float64)).reshape(B, S, H, D)
+    k = (x @ A["wk"].T.astype(np.float64)).reshape(B, S, H, D)
+    v = (x @ A["wv"].T.astype(np.float64)).reshape(B, S, H, D)
+    g = (x @ A["wg"].T.astype(np.float64) + A["bg"]).reshape(B, S, H, D)
+    lg = np.einsum("bqhd,bkhd->bhqk", q, k) / np.sqrt(D)
+    lg = (lg.astype(np.float32) + A["bias"][:, None, None, :]).astype(np.float32)
+    if w.has_nb:
+        lg = lg + A["nb"][None]
+    lg = lg.astype(np.float64)
+    p = np.exp(lg - lg.max(-1, keepdims=True))
+    p /= p.sum(-1, keepdims=True)
+    o = np.einsum("bhqk,bkhd->bqhd", p, v) / (1 + np.exp(-g))
+    return o.reshape(B, S, C) @ A["wo"].T.astype(np.float64) + A["bo"]
+
+
+@pytest.mark.parametrize("with_nb", [True, False])
+def test_gating_exact_matches_textbook(with_nb):
+    w = W.random_gating_case(seed=3, B=3, S=70, H=2, D=32, with_nb=with_nb, full_mask_rows=1)
+    ex = helpers.oracle_exact(w)
+    ref = _textbook_gating(w)
+    assert helpers.rel_err(ex, ref) < 1e-6
+
+
+def test_gating_faithful_close_to_exact_and_masked_row_uniform():
+    w = W.random_gating_case(seed=4, B=2, S=64, H=2, D=32, with_nb=True, full_mask_rows=1)
+    fa = helpers.oracle_faithful(w, block_size=16)
+    ex = helpers.oracle_exact(w)
+    # FEXPA (0.54 % per exp) and the bf16 round trips bound the distance between the two modes
+    assert helpers.rel_err(fa, ex) < 1e-2
+    # block_size only tiles the query loop: results do not depend on it
+    fb = helpers.oracle_faithful(w, block_size=64)
+    assert np.array_equal(fa, fb)
+
+
+def test_fully_masked_row_is_uniform_average():
+    # all keys of batch row 0 carry -1e9: fp32 absorbs the logits, softmax is uniform (1/S each)
+    w = W.random_gating_case(seed=5, B=1, S=32, H=1, D=16, with_nb=False, full_mask_rows=1)
+    A = w.arrays
+    A["bg"][:] = 50.0            # sigmoid -> 1
+    A["wo"] = np.eye(w.C, dtype=np.float32)
+    A["bo"][:] = 0.0
+    ex = helpers.oracle_exact(w)
+    v = A["x"].reshape(w.S, w.C).astype(np.float64) @ A["wv"].T.astype(np.float64)
+    assert np.allclose(ex[0], np.broadcast_to(v.mean(0), (w.S, w.C)), atol=1e-5)
+
+
+def _textbook_global(w):
+    A = w.arrays
+    B, S, H, D, C = w.B, w.S, w.H, w.D, w.C
+    x = A["x"].astype(np.float64)
+    m = A["mask"].astype(np.float64)
+    qa = (m[..., None] * x).sum(1) / (m.sum(1, keepdims=True) + 1e-10)
+    q = (qa @ A["wq"].T.astype(np.float64)).reshape(B, H, D)
+    k = x @ A["wk"].T.astype(np.float64)
+    v = x @ A["wv"].T.astype(np.float64)
+    lg = np.einsum("bhd,bsd->bhs", q, k) / np.sqrt(D)
+    lg = lg.astype(np.float32) + (A["mask"] * np.float32(1e9) - np.float32(1e9))[:, None, :]
+    lg = lg.astype(np.float64)
+    p = np.exp(lg - lg.max(-1, keepdims=True))
+    p /= p.sum(-1, keepdims=True)
+    wa = np.einsum("bhs,bsd->bhd", p, v).reshape(B, 1, C)
+    g = 1 / (1 + np.exp(-(x @ A["wg"].T.astype(np.float64) + A["bg"])))
+    return (g * wa) @ A["wo"].T.astype(np.float64) + A["bo"]
+
+
+def test_global_exact_matches_textbook_and_faithful_is_close():
+    w = W.random_global_case(seed=6, B=3, S=96, zero_mask_rows=1)
+    ex = helpers.oracle_exact(w)
+    assert helpers.rel_err(ex, _textbook_global(w)) < 1e-6
+    assert helpers.rel_err(helpers.oracle_faithful(w), ex) < 1e-2
+
+
+def test_linear_modes_agree():
+    rng = np.random.default_rng(7)
+    a = W.as_f32(W.bf16_bits(rng.standard_normal((37, 48)).astype(np.float32)))
+    w = W.as_f32(W.bf16_bits(rng.standard_normal((5, 48)).astype(np.float32) / 7))
+    bias = rng.standard_normal(5).astype(np.float32)
+    fa = W.as_f32(O.linear_bf16(W.bf16_bits(a), W.bf16_bits(w), bias))
+    ex = O.linear_exact(a, w, bias)
+    assert np.allclose(ex, a.astype(np.float64) @ w.T.astype(np.float64) + bias, atol=1e-5)
+    assert helpers.rel_err(fa, ex) < 5e-3
+    prev = W.bf16_bits(rng.standard_normal((37, 5)).astype(np.float32))
+    fb = W.as_f32(O.linear_bf16(W.bf16_bits(a), W.bf16_bits(w), None, beta=1, result=prev))
+    assert helpers.rel_err(fb, a @ w.T + W.as_f32(prev)) < 5e-3
+
+
+def test_all_gather_reference_grid():
+    """Golden vector of the reference's own collective test (all_gather_test.cpp:29-67)."""
+    g = np.load(os.path.join(GOLD, "all_gather_grid.npz"))
+    out = O.all_gather_bytes([g["shard0"], g["shard1"]], (8, 5, 1), data_size0=4)
+    assert np.array_equal(out, g["expect"])
+    # the closed form the reference test spells out: 0..19 then 32..51
+    assert out.reshape(-1).tolist() == list(range(20)) + list(range(32, 52))
+
+
+def test_all_gather_ragged_and_dim1():
+    rng = np.random.default_rng(8)
+    full = rng.integers(0, 255, (7, 6, 3), dtype=np.uint8)
+    world = 3                                    # block = 3: ranks own 3, 3, 1 rows
+    shards = [full[r * 3:min(7, r * 3 + 3)] for r in range(world)]
+    assert np.array_equal(O.all_gather_bytes(shards, (7, 6, 3), data_size0=shards[0].shape[0]), full)
+    # sharded on dim 1: data.sizes[0] == out.sizes[0]
+    shards1 = [np.ascontiguousarray(full[:, r * 2:r * 2 + 2]) for r in range(world)]
+    assert np.array_equal(O.all_gather_bytes(shards1, (7, 6, 3), data_size0=7), full)
+
+
+def test_oracle_regression_vectors():
+    g = np.load(os.path.join(GOLD, "gating_small.npz"))
+    w = W.random_gating_case(seed=11, B=2, S=40, H=2, D=16, full_mask_rows=1)
+    assert np.array_equal(W.bf16_bits(helpers.oracle_faithful(w, block_size=16)), g["faithful"])
+    assert np.allclose(helpers.oracle_exact(w), g["exact"], rtol=0, atol=1e-6)
+    g = np.load(os.path.join(GOLD, "global_small.npz"))
+    w = W.random_global_case(seed=12, B=2, S=48, zero_mask_rows=1)
+    assert np.array_equal(W.bf16_bits(helpers.oracle_faithful(w)), g["faithful"])
+    assert np.allclose(helpers.oracle_exact(w), g["exact"], rtol=0, atol=1e-6)
+
+
+def test_workload_shapes_and_flops():
+    # algorithmic work of the five benchmark shapes (2 FLOPs per multiply-add)
+    expect = {"msa_row_fp32": 30.199, "triangle_start_384": 53.301, "msa_col_512": 231.928,
+              "extra_msa_global": 36.997, "triangle_end_1024": 722.628}
+    for name, gf in expect.items():
+        kind, dtype, B, S, H, D, c_z, seed = W.spec(name)
+        w = W.Workload(name=name, kind=kind, dtype=dtype, B=B, S=S, H=H, D=D, seed=seed, c_z=c_z, has_nb=c_z > 0)
+        assert abs(w.flops() / 1e9 - gf) < 0.01, (name, w.flops() / 1e9)
+    w = W.make("triangle_start_384", rows=4)
+    assert w.arrays["x"].shape == (4, 384, 128) and w.arrays["nb"].shape == (4, 384, 384)
+    assert w.arrays["bias"].shape == (4, 384)
