@@ -1,0 +1,332 @@
+#!/usr/bin/env python
+"""Benchmark of the gated-attention hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
+
+A "step" is one call of kutacc_af2_gating_attention (or kutacc_af2_global_attention) on one batch of
+seeded synthetic input of the named shape. Rank 0 prints one JSON line:
+
+  value / ms_per_step  whole-job TFLOP/s (algorithmic FLOPs, 2 per multiply-add) with inputs resident
+                       in HBM, timed with CUDA events on the launching stream, max over ranks
+  e2e                  the same call with every tensor in pinned HOST memory: the library's own
+                       host->device and device->host copies are inside the timed region
+  roofline             the dominant kernel of the call, timed live with CUDA events
+  cpu_baseline         the CPU restatement of the reference on the host cores (rank 0, N = 1 only)
+
+With N > 1 (launched by torch.distributed.run, one rank per GPU) every rank processes its own batch
+of rows of the same shape: rows are independent problems, nothing is exchanged (weak scaling).
+
+--impl reference times the CPU restatement of the reference's algorithm on the host cores (the
+reference's own ARM SVE sources do not compile on this x86 host) on a bounded sample of the same
+workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+
+DEFAULT_WORKLOAD = "triangle_start_384"
+METRIC = "gated_attention_tflops"
+UNIT = "TFLOP/s"
+
+# DRAM bytes (read + write) of one launch of the dominant kernel from an ncu capture, per workload;
+# None until a capture exists for the current kernel. See profiles/.
+NCU_TRAFFIC = {}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"],
+                "bf16_tflops_sustained": p.get("bf16_tflops_sustained"), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU while a region runs (read-only NVML)."""
+
+    def __init__(self, index: int, period_s: float = 0.02):
+        self.index, self.period = index, period_s
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _loop(self):
+        nv = self.nv
+        names = {
+            "hw_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8),
+            "hw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40),
+            "sw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20),
+            "sw_power_cap": getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4),
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for k, bit in names.items():
+                    if r & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._thread:
+            self._thread.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": 0}
+        return {"sm_mhz": statistics.median(self.samples), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def dominant_kernel(workload):
+    """(kernel name in the library's profile record, bound, algorithmic work per call, unit)."""
+    if workload.kind == "gating":
+        # Q.K^T and P.V: 4*B*S^2*C FLOPs, all inside the fused attention core
+        return "attn_core", "tensor", 4.0 * workload.B * workload.S * workload.S * workload.C, "TFLOP/s"
+    # global attention: the output kernel streams x once more and writes out: bandwidth bound
+    return "global_out", "hbm", 2.0 * workload.B * workload.S * workload.C * 2, "GB/s"
+
+
+def cpu_baseline(name: str, budget_s: float = 12.0):
+    """CPU restatement of the reference on a bounded sample (a subset of the batch rows)."""
+    from kutacc_b200 import workloads as W
+    from oracle import cpu_oracle as O
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from tests import helpers
+    kind, dtype, B, S, H, D, c_z, seed = W.spec(name)
+    rows = min(B, 8)
+    w = W.make(name, rows=rows)
+    run = (lambda ww: helpers.oracle_exact(ww)) if dtype == "fp32" else (lambda ww: helpers.oracle_faithful(ww))
+    t0 = time.perf_counter()
+    run(w)
+    t_probe = time.perf_counter() - t0
+    # grow the sample so that one pass takes a few seconds, then repeat within the budget
+    rows2 = int(min(B, max(rows, rows * 3.0 / max(t_probe, 1e-3))))
+    if rows2 != rows:
+        w = W.make(name, rows=rows2)
+    times = []
+    t_start = time.perf_counter()
+    while len(times) < 5 and (time.perf_counter() - t_start < budget_s or not times):
+        t0 = time.perf_counter()
+        run(w)
+        times.append(time.perf_counter() - t0)
+    t = min(times)
+    return {"value": w.flops() / t / 1e12, "unit": UNIT, "cores": O.num_threads(), "kind": "port",
+            "sample": f"{w.B} of {B} batch rows of {name} (full sequence length {S}), best of {len(times)} runs, "
+                      f"{t * 1e3:.1f} ms per pass",
+            "ms_full_call_est": t * 1e3 * B / w.B}
+
+
+def run_reference_arm(args):
+    """The reference's CPU implementation, as restated in oracle/ (the ARM sources do not compile here)."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    from kutacc_b200 import workloads as W
+    from oracle import cpu_oracle as O
+    from tests import helpers
+    name = args.workload
+    kind, dtype, B, S, H, D, c_z, seed = W.spec(name)
+    run = (lambda ww: helpers.oracle_exact(ww)) if dtype == "fp32" else (lambda ww: helpers.oracle_faithful(ww))
+    probe = W.make(name, rows=min(B, 4))
+    t0 = time.perf_counter()
+    run(probe)
+    t_row = (time.perf_counter() - t0) / probe.B
+    total_steps = args.steps + args.warmup
+    rows = int(max(1, min(B, 150.0 / max(total_steps, 1) / max(t_row, 1e-6))))
+    w = W.make(name, rows=rows)
+    for _ in range(args.warmup):
+        run(w)
+    times = []
+    for _ in range(args.steps):
+        t0 = time.perf_counter()
+        run(w)
+        times.append(time.perf_counter() - t0)
+    t = sum(times) / len(times)
+    val = w.flops() / t / 1e12
+    sample = f"{rows} of {B} batch rows of {name} per step (full sequence length {S})"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": dtype, "data": "synthetic (seeded numpy, AlphaFold2 model shapes)",
+        "config": {"workload": name, "B": B, "S": S, "H": H, "D": D, "C": H * D, "sample_rows": rows,
+                   "note": "CPU restatement of the reference algorithm (oracle/), host cores only"},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": O.num_threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    if args.impl == "reference":
+        return run_reference_arm(args)
+
+    import torch
+    import torch.distributed as dist
+    from kutacc_b200 import api, build, runner
+    from kutacc_b200 import workloads as W
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = f"cuda:{local_rank}"
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device(dev))
+    if not os.path.exists(api.LIB_PATH):
+        build.build()
+    api.lib()
+
+    w = W.make(args.workload)
+    case = runner.DeviceCase(w, device=dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)      # larger than the 126 MB L2
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        case.run()
+    barrier()
+    launches0 = api.launch_count()
+    api.set_profile(True)
+    api.profile_read()
+    step_ms = []
+    with ClockSampler(local_rank) as clocks:
+        for _ in range(args.steps):
+            flush.zero_()                                             # evict L2 between timed steps
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            case.run()
+            e1.record()
+            e1.synchronize()
+            step_ms.append(e0.elapsed_time(e1))
+        barrier()
+    prof = api.profile_read()
+    api.set_profile(False)
+    launches = api.launch_count() - launches0
+    total_ms = float(sum(step_ms))
+    if world > 1:
+        t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms = float(t.item())
+    ms_per_step = total_ms / args.steps
+    flops_job = w.flops() * world
+    value = flops_job / (ms_per_step * 1e-3) / 1e12
+
+    # dominant kernel, timed live inside the same steps
+    kname, bound, work, runit = dominant_kernel(w)
+    per_kernel = {}
+    for n, ms in prof:
+        per_kernel.setdefault(n, []).append(ms)
+    kshare = {n: sum(v) / max(sum(sum(x) for x in per_kernel.values()), 1e-9) for n, v in per_kernel.items()}
+    peaks = measured_peaks()
+    roofline = None
+    if kname in per_kernel:
+        launches_per_step = len(per_kernel[kname]) / args.steps
+        k_ms = sum(per_kernel[kname]) / args.steps                    # all launches of that kernel in one step
+        achieved = work / (k_ms * 1e-3) / (1e12 if bound == "tensor" else 1e9)
+        peak = peaks["bf16_tflops"] if bound == "tensor" else peaks["hbm_gbs"]
+        roofline = {"kernel": kname, "bound": bound, "achieved": achieved, "peak": peak, "unit": runit,
+                    "frac": achieved / peak, "traffic": NCU_TRAFFIC.get(args.workload),
+                    "peak_source": f"{peaks['source']} ({'burst bf16' if bound == 'tensor' else 'copy'})",
+                    "kernel_ms_per_step": k_ms, "launches_per_step": launches_per_step,
+                    "time_share": {n: round(s, 4) for n, s in kshare.items()}}
+
+    # end to end: every tensor in pinned host memory, copies inside the library call
+    e2e = None
+    if not args.no_e2e:
+        host = runner.HostCase(w)
+        for _ in range(2):
+            host.run()
+        barrier()
+        e_ms = []
+        for _ in range(max(3, min(args.steps, 10))):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            host.run()
+            e1.record()
+            e1.synchronize()
+            e_ms.append(e0.elapsed_time(e1))
+        em = float(sum(e_ms) / len(e_ms))
+        if world > 1:
+            t = torch.tensor([em], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            em = float(t.item())
+        e2e = {"value": flops_job / (em * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": host.h2d_bytes(),
+               "d2h_bytes_per_step": host.d2h_bytes(), "ms_per_step": em}
+        checksum = float(host.out.float().abs().mean())               # read the result on the host
+        e2e["result_mean_abs"] = checksum
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cpu = cpu_baseline(args.workload)
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": w.dtype, "data": "synthetic (seeded numpy, AlphaFold2 model shapes)",
+            "config": {"workload": args.workload, "B_per_gpu": w.B, "S": w.S, "H": w.H, "D": w.D, "C": w.C,
+                       "pair_bias": w.has_nb, "gflop_per_call": w.flops() / 1e9,
+                       "l2": "flushed between timed steps (256 MiB memset)",
+                       "parallelism": f"rows sharded over {world} GPU(s), no collective"},
+            "frac_of_bf16_peak": value / world / peaks["bf16_tflops"],
+            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches),
+            "clocks": clocks.summary(),
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

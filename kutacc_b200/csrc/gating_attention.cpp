@@ -71,7 +71,8 @@ static void gating_attention_impl(Tensor &input, int64_t batch, int64_t seq_len,
     for (const Tensor *w : {&query_w, &key_w, &value_w, &gating_w, &output_w})
         stage += staged_bytes_needed(w->data_ptr(), w_bytes);
     if (!rt.reserve_stage(stage)) return;
-    if (!rt.reserve_workspace(5 * (x_bytes + 256))) return;
+    const size_t nb_pad_bytes = has_nb ? (size_t)H * S * ((S + 7) / 8 * 8) * 2 : 0;
+    if (!rt.reserve_workspace(5 * (x_bytes + 256) + nb_pad_bytes + 256)) return;
 
     DeviceArg d_x = resolve_in(input.data_ptr(), x_bytes);
     DeviceArg d_bias = resolve_in(bias.data_ptr(), bias_bytes);
@@ -83,6 +84,7 @@ static void gating_attention_impl(Tensor &input, int64_t batch, int64_t seq_len,
     DeviceArg d_out = resolve_out(out.data_ptr(), out_bytes);
     void *wq_ = rt.take_workspace(x_bytes), *wk_ = rt.take_workspace(x_bytes), *wv_ = rt.take_workspace(x_bytes),
          *wg_ = rt.take_workspace(x_bytes), *wavg = rt.take_workspace(x_bytes);
+    void *nb_pad = nb_pad_bytes ? rt.take_workspace(nb_pad_bytes) : nullptr;
     if (kutacc_check_err_set) return;
 
     const float scale = (float)(1 / std::sqrt((double)head_size));  // gating_attention.cpp:68
@@ -90,17 +92,30 @@ static void gating_attention_impl(Tensor &input, int64_t batch, int64_t seq_len,
     const bool fast = dt == kBF16 && (C % 64 == 0) && (D == 16 || D == 32 || D == 64) && B <= 65535 && H <= 65535 &&
                       aligned16(d_x.dev) && aligned16(d_wq.dev) && aligned16(d_wk.dev) && aligned16(d_wv.dev) &&
                       aligned16(d_wg.dev) && aligned16(d_wo.dev) && (out_rs % 2 == 0) &&
-                      (((uintptr_t)d_out.dev & 3u) == 0) &&
-                      (!has_nb || ((nb_s0 % 8 == 0) && (nb_s1 % 8 == 0) && aligned16(d_nb.dev)));
+                      (((uintptr_t)d_out.dev & 3u) == 0);
     bool ok;
     if (fast) {
-        const float q_scale = scale * 1.4426950408889634f;  // the attention kernel works in base 2
+        // The TMA loads of the pair bias need 16-byte aligned rows. A pair bias whose strides are not
+        // multiples of 8 elements is first copied into the workspace with padded rows.
+        const void *nb_dev = has_nb ? d_nb.dev : nullptr;
+        int64_t nb_sh = nb_s0, nb_sq = nb_s1;
+        if (has_nb && ((nb_s0 % 8) || (nb_s1 % 8) || !aligned16(d_nb.dev))) {
+            const int64_t s_pad = (S + 7) / 8 * 8;
+            KUTACC_CUDA(cudaMemcpy2DAsync(nb_pad, (size_t)s_pad * 2, d_nb.dev, (size_t)nb_s1 * 2, (size_t)S * 2,
+                                          (size_t)(nb_s0 == S * nb_s1 ? H * S : S), cudaMemcpyDeviceToDevice, stream));
+            for (int64_t hh = 1; nb_s0 != S * nb_s1 && hh < H; ++hh)
+                KUTACC_CUDA(cudaMemcpy2DAsync((char *)nb_pad + (size_t)hh * S * s_pad * 2, (size_t)s_pad * 2,
+                                              (const char *)d_nb.dev + (size_t)hh * nb_s0 * 2, (size_t)nb_s1 * 2,
+                                              (size_t)S * 2, (size_t)S, cudaMemcpyDeviceToDevice, stream));
+            nb_dev = nb_pad;
+            nb_sq = s_pad;
+            nb_sh = S * s_pad;
+        }
         ok = dev::launch_proj_qkvg_bf16(stream, d_x.dev, d_wq.dev, d_wk.dev, d_wv.dev, d_wg.dev,
                                         (const float *)d_bg.dev, wq_, wk_, wv_, wg_, (int)B, (int)S, (int)H, (int)D,
-                                        q_scale);
-        ok = ok && dev::launch_attn_core_bf16(stream, wq_, wk_, wv_, wg_, d_bias.dev, bias_s0,
-                                              has_nb ? d_nb.dev : nullptr, nb_s0, nb_s1, wavg, (int)B, (int)S, (int)H,
-                                              (int)D);
+                                        1.0f);
+        ok = ok && dev::launch_attn_core_bf16(stream, wq_, wk_, wv_, wg_, d_bias.dev, bias_s0, nb_dev, nb_sh, nb_sq,
+                                              wavg, (int)B, (int)S, (int)H, (int)D, scale);
         ok = ok && dev::launch_linear_bias_bf16(stream, wavg, C, d_wo.dev, (const float *)d_bo.dev, d_out.dev, out_rs,
                                                 M, (int)C, (int)C);
     } else {

@@ -24,11 +24,12 @@ bool launch_linear_bias_bf16(cudaStream_t stream, const void *a, int64_t lda, co
                              void *out, int64_t ldo, int64_t M, int N, int K);
 
 // ---- fused attention core ------------------------------------------------------------------------
-// avg[b, s, h*D + d] = sigmoid(gate[b, s, h*D + d]) * softmax_k(q.k + bias[b,k] + nb[h,s,k]) . v
-// q already carries the 1/sqrt(D) scale. bf16; D in {16, 32, 64}. nb may be null.
+// avg[b, s, h*D + d] = sigmoid(gate[b, s, h*D + d]) * softmax_k(bf16(q.k)*scale + bias[b,k] + nb[h,s,k]) . v
+// q, k, v are [B, H, S, D]. bf16; D in {16, 32, 64}. nb may be null; its strides must be multiples
+// of 8 elements and its base 16-byte aligned (TMA).
 bool launch_attn_core_bf16(cudaStream_t stream, const void *q, const void *k, const void *v, const void *gate,
                            const void *bias, int64_t bias_stride0, const void *nb, int64_t nb_stride_h,
-                           int64_t nb_stride_q, void *avg, int B, int S, int H, int D);
+                           int64_t nb_stride_q, void *avg, int B, int S, int H, int D, float scale);
 
 // ---- generic (any shape, bf16 or fp32 storage, fp32 math) ------------------------------------------
 // c[m, n] = sum_k a[m, k] * w[n, k] (+ bias[n]) (+ beta * c[m, n]); a row stride lda, w row stride

@@ -6,6 +6,7 @@
 #include <vector>
 
 #include "common.h"
+#include "tma_utils.cuh"
 
 namespace kutacc {
 
@@ -154,7 +155,15 @@ void end_of_call()
 {
     cudaError_t e = cudaGetLastError();
     KUTACC_CHECK(e == cudaSuccess, "kernel launch failed: ", cudaGetErrorString(e));
-    if (!runtime().async) KUTACC_CUDA(cudaStreamSynchronize((cudaStream_t)runtime().stream));
+    if (!runtime().async) {
+        KUTACC_CUDA(cudaStreamSynchronize((cudaStream_t)runtime().stream));
+        dev::KernelErrorWord &ew = dev::kernel_error_word();
+        if (ew.host && *ew.host != 0) {
+            const int code = *ew.host;
+            *ew.host = 0;
+            KUTACC_CHECK(false, "a device-side wait ran out of time (site ", code, "); the result is invalid");
+        }
+    }
 }
 
 }  // namespace kutacc

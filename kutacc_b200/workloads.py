@@ -108,7 +108,16 @@ def make(name: str, rows: Optional[int] = None, seq: Optional[int] = None) -> Wo
     A = w.arrays
 
     x = rng.standard_normal((Bgen, S, C), dtype=np.float32)
-    if name in ("triangle_start_384", "triangle_end_1024"):
+    pair_input = name in ("triangle_start_384", "triangle_end_1024")
+    if not pair_input:
+        # consume the draws of the rows that were left out, so that every later array (weights, mask)
+        # is the same whatever `rows` is
+        left = (B - Bgen) * S * C
+        while left > 0:
+            n = min(left, 1 << 24)
+            rng.standard_normal(n, dtype=np.float32)
+            left -= n
+    if pair_input:
         # the activations are the pair representation itself: x[i, j, :] = z[i, j, :]; the pair bias
         # of query row q and key k is z[q, k, :] . Wb, so z needs all S rows even when rows < S
         zfull = x if Bgen == S else np.concatenate(
