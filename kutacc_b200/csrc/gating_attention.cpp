@@ -111,13 +111,18 @@ static void gating_attention_impl(Tensor &input, int64_t batch, int64_t seq_len,
             nb_sq = s_pad;
             nb_sh = S * s_pad;
         }
-        ok = dev::launch_proj_qkvg_bf16(stream, d_x.dev, d_wq.dev, d_wk.dev, d_wv.dev, d_wg.dev,
+        // tensor-memory GEMM where the shape allows it, warp-level MMA otherwise
+        ok = dev::tcgen05_proj_qkvg_bf16(stream, d_x.dev, d_wq.dev, d_wk.dev, d_wv.dev, d_wg.dev,
+                                         (const float *)d_bg.dev, wq_, wk_, wv_, wg_, (int)B, (int)S, (int)H, (int)D) ||
+             dev::launch_proj_qkvg_bf16(stream, d_x.dev, d_wq.dev, d_wk.dev, d_wv.dev, d_wg.dev,
                                         (const float *)d_bg.dev, wq_, wk_, wv_, wg_, (int)B, (int)S, (int)H, (int)D,
                                         1.0f);
         ok = ok && dev::launch_attn_core_bf16(stream, wq_, wk_, wv_, wg_, d_bias.dev, bias_s0, nb_dev, nb_sh, nb_sq,
                                               wavg, (int)B, (int)S, (int)H, (int)D, scale);
-        ok = ok && dev::launch_linear_bias_bf16(stream, wavg, C, d_wo.dev, (const float *)d_bo.dev, d_out.dev, out_rs,
-                                                M, (int)C, (int)C);
+        ok = ok && (dev::tcgen05_linear_bias_bf16(stream, wavg, d_wo.dev, (const float *)d_bo.dev, d_out.dev, out_rs,
+                                                  (int)B, (int)S, (int)C, (int)C) ||
+                    dev::launch_linear_bias_bf16(stream, wavg, C, d_wo.dev, (const float *)d_bo.dev, d_out.dev, out_rs,
+                                                 M, (int)C, (int)C));
     } else {
         const dev::ElemType et = dt == kFP32 ? dev::kElemF32 : dev::kElemBF16;
         ok = dev::launch_gemm_generic(stream, et, d_x.dev, C, d_wq.dev, C, nullptr, 0.f, wq_, C, M, C, C);

@@ -1,0 +1,408 @@
+// Projection GEMMs on the fifth-generation tensor cores: tcgen05.mma with TMEM accumulators, operands
+// staged in shared memory by TMA, results written back by TMA stores.
+//
+//   C[b, s, n] = sum_k X[b, s, k] * W[n, k] (+ bias[n])         X [B, S, K] bf16, W [N, K] bf16 (W[out][in])
+//
+// A persistent CTA (one per SM) walks 128 x 128 output tiles; a row tile never crosses a batch row, so
+// every TMA box lies inside one [S, *] slab and rows past S are zero-filled on load and clipped on
+// store. Warp roles:
+//   warp 0      producer: TMA loads of 128 x 64 slabs of X and W (128-byte swizzle) into a 5-stage ring
+//   warp 1      MMA issuer: one elected lane issues tcgen05.mma (M = 128, N = 128, K = 16) four times per
+//               slab into one of four 128-column TMEM accumulators and commits to mbarriers
+//   warps 2-5   epilogue: tcgen05.ld of the warp's 32 TMEM lanes, bias add, bf16 rounding, a swizzled
+//               32 x 32 staging tile in shared memory, TMA store into the destination layout
+// The four accumulators let the epilogue of tile i overlap the MMAs of tiles i+1 .. i+3.
+//
+// For the fused Q/K/V/gate projection the four weights are four tensor maps and the destination maps
+// scatter straight into the attention kernel's [B, H, S, D] layout (q, k, v) and into [B, S, C] (gate,
+// with the gate bias added). The same kernel serves the output projection.
+//
+// Replaces addmm -> kutacc_core_bgemm_ex of the reference
+// (src/attention/gating_attention.cpp:47-66,152-157; src/linear/mm.cpp:46-86).
+//
+// All mbarrier waits are bounded; on a timeout the roles fall through to the common tail, the TMEM
+// allocation is released and the host-visible error word carries the site.
+#include "common.h"
+#include "kernels.h"
+#include "ptx_utils.cuh"
+#include "tma_utils.cuh"
+
+#include <algorithm>
+
+namespace kutacc {
+namespace dev {
+
+namespace {
+
+constexpr int BM = 128, BN = 128, BK = 64;
+constexpr int NSTAGE = 5;
+constexpr int ACC_STAGES = 4;
+constexpr int SLAB_BYTES = BM * BK * 2;                 // 16 KB, A and W slabs alike
+constexpr int STAGE_BYTES = 2 * SLAB_BYTES;
+constexpr int EPI_WARPS = 4;
+constexpr int STG_BYTES = 32 * 32 * 2;                  // one 32 x 32 bf16 staging tile
+constexpr int STG_PER_WARP = 2;
+constexpr int STG_OFF = NSTAGE * STAGE_BYTES;
+constexpr int BAR_OFF = STG_OFF + EPI_WARPS * STG_PER_WARP * STG_BYTES;
+constexpr int NBARS = 2 * NSTAGE + 2 * ACC_STAGES;
+constexpr int SMEM_BYTES = BAR_OFF + NBARS * 8 + 16 + 1024;
+constexpr int THREADS = 32 * (2 + EPI_WARPS);
+constexpr int TMEM_COLS = ACC_STAGES * BN;              // 512: the whole tensor memory of the SM
+
+struct alignas(64) GemmMaps {
+    CUtensorMap a;        // X  [B][S][K], box [64, 128, 1], 128-byte swizzle
+    CUtensorMap w[4];     // W  [1][N_seg][K], box [64, 128, 1], 128-byte swizzle
+    CUtensorMap out[4];   // destination per segment, box [32, 32, 1], 64-byte swizzle
+};
+
+struct GemmParams {
+    const float *bias[4];   // per segment, may be null
+    int seg_n;              // output channels per segment (multiple of 128)
+    int nseg;
+    int head_dim;           // > 0: segment output is [B*H][S][D] (coords d, s, b*H + h); 0: [B][S][N_seg]
+    int head_layout_mask;   // bit i set: segment i uses the head layout
+    int heads;
+    int K;
+    int S, B;
+    int *err;
+};
+
+// ---- tcgen05 wrappers ------------------------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols)
+{
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_dst), "r"(ncols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish()
+{
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols)
+{
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem], bf16 inputs, fp32 accumulate, shape from idesc
+__device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                            uint32_t accumulate)
+{
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// this warp's 32 lanes x 32 consecutive fp32 columns
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,"
+        "%29,%30,%31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+
+// shared-memory matrix descriptor: K-major operand, rows of 128 bytes, 128-byte swizzle, 8-row groups
+// 1024 bytes apart; `addr` is the byte address of the (1024-aligned) slab plus the K offset inside the
+// swizzle atom
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFFu) >> 4);         // start address
+    d |= (uint64_t)1 << 16;                          // leading byte offset (unused for swizzled K-major)
+    d |= (uint64_t)(1024 >> 4) << 32;                // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                          // descriptor version of sm_100
+    d |= (uint64_t)2 << 61;                          // 128-byte swizzle
+    return d;
+}
+// instruction descriptor: D fp32, A and B bf16, both K-major, N = 128, M = 128
+constexpr uint32_t kInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p)
+{
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t smem = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t bar_base = smem + BAR_OFF;
+    auto full_bar = [&](int s) { return bar_base + 8u * (uint32_t)s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (uint32_t)(NSTAGE + s); };
+    auto acc_full = [&](int a) { return bar_base + 8u * (uint32_t)(2 * NSTAGE + a); };
+    auto acc_empty = [&](int a) { return bar_base + 8u * (uint32_t)(2 * NSTAGE + ACC_STAGES + a); };
+    const uint32_t tmem_slot = bar_base + 8u * NBARS;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int s_tiles = (p.S + BM - 1) / BM;
+    const int n_tiles_seg = p.seg_n / BN;
+    const int n_tiles = n_tiles_seg * p.nseg;
+    const int num_tiles = p.B * s_tiles * n_tiles;
+    const int nk = p.K / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < NSTAGE; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < ACC_STAGES; ++a) {
+            mbar_init(acc_full(a), 1);
+            mbar_init(acc_empty(a), EPI_WARPS);
+        }
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    uint32_t tmem_base;
+    asm volatile("ld.shared.b32 %0, [%1];\n" : "=r"(tmem_base) : "r"(tmem_slot));
+
+    if (warp == 0) {
+        // ================= producer =================
+        if (lane == 0) {
+            tma_prefetch_desc(&maps.a);
+            int it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                const int m_tile = tile / n_tiles, n_tile = tile % n_tiles;
+                const int b = m_tile / s_tiles, s0 = (m_tile % s_tiles) * BM;
+                const int seg = n_tile / n_tiles_seg, n0 = (n_tile % n_tiles_seg) * BN;
+                const CUtensorMap *wmap = &maps.w[seg];
+                for (int kc = 0; kc < nk; ++kc, ++it) {
+                    const int s = it % NSTAGE;
+                    if (it >= NSTAGE && !mbar_wait(empty_bar(s), (uint32_t)((it / NSTAGE - 1) & 1), p.err, 11)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t st = smem + (uint32_t)s * STAGE_BYTES;
+                    mbar_arrive_expect_tx(full_bar(s), STAGE_BYTES);
+                    tma_load_3d(st, &maps.a, full_bar(s), kc * BK, s0, b);
+                    tma_load_3d(st + SLAB_BYTES, wmap, full_bar(s), kc * BK, n0, 0);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ================= MMA issuer =================
+        int it = 0, tcount = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
+            const int a = tcount % ACC_STAGES;
+            if (tcount >= ACC_STAGES && !mbar_wait(acc_empty(a), (uint32_t)((tcount / ACC_STAGES - 1) & 1), p.err, 12)) {
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            const uint32_t d_tmem = tmem_base + (uint32_t)(a * BN);
+            for (int kc = 0; kc < nk; ++kc, ++it) {
+                const int s = it % NSTAGE;
+                if (!mbar_wait(full_bar(s), (uint32_t)((it / NSTAGE) & 1), p.err, 13)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                if (lane == 0) {
+                    const uint32_t st = smem + (uint32_t)s * STAGE_BYTES;
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k) {
+                        const uint64_t adesc = make_smem_desc(st + k * 32);
+                        const uint64_t bdesc = make_smem_desc(st + SLAB_BYTES + k * 32);
+                        tc_mma_bf16(d_tmem, adesc, bdesc, kInstrDesc, (kc > 0 || k > 0) ? 1u : 0u);
+                    }
+                    tc_commit(empty_bar(s));                 // slab may be overwritten once these MMAs retire
+                    if (kc == nk - 1) tc_commit(acc_full(a));
+                }
+                __syncwarp();
+            }
+        }
+    } else {
+        // ================= epilogue =================
+        const int quad = warp & 3;                            // TMEM lanes 32*quad .. 32*quad+31
+        const int ew = warp - 2;
+        const uint32_t stg0 = smem + STG_OFF + (uint32_t)(ew * STG_PER_WARP) * STG_BYTES;
+        int tcount = 0, nstore = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
+            const int m_tile = tile / n_tiles, n_tile = tile % n_tiles;
+            const int b = m_tile / s_tiles, s0 = (m_tile % s_tiles) * BM;
+            const int seg = n_tile / n_tiles_seg, n0 = (n_tile % n_tiles_seg) * BN;
+            const int a = tcount % ACC_STAGES;
+            if (!mbar_wait(acc_full(a), (uint32_t)((tcount / ACC_STAGES) & 1), p.err, 14)) {
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            const float *bias = p.bias[seg];
+            const bool head_layout = (p.head_layout_mask >> seg) & 1;
+            const CUtensorMap *omap = &maps.out[seg];
+            const int row0 = s0 + quad * 32;                  // first row of this warp inside the batch row
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(a * BN + c * 32), r);
+                tmem_ld_wait();
+                const int n = n0 + c * 32;
+                uint32_t packed[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    float v0 = __uint_as_float(r[2 * j]), v1 = __uint_as_float(r[2 * j + 1]);
+                    if (bias) {
+                        v0 += __ldg(bias + n + 2 * j);
+                        v1 += __ldg(bias + n + 2 * j + 1);
+                    }
+                    packed[j] = pack_bf16x2(v0, v1);
+                }
+                // staging tile: row = lane, 64 bytes per row, 16-byte chunks swizzled as the 64-byte TMA mode
+                const uint32_t stg = stg0 + (uint32_t)(nstore % STG_PER_WARP) * STG_BYTES;
+                if (nstore >= STG_PER_WARP) {
+                    if (lane == 0) tma_store_wait_read<STG_PER_WARP - 1>();
+                    __syncwarp();
+                }
+#pragma unroll
+                for (int ch = 0; ch < 4; ++ch) {
+                    const uint32_t addr = stg + (uint32_t)(lane * 64 + ((ch ^ ((lane >> 1) & 3)) << 4));
+                    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};\n" ::"r"(addr), "r"(packed[4 * ch]),
+                                 "r"(packed[4 * ch + 1]), "r"(packed[4 * ch + 2]), "r"(packed[4 * ch + 3])
+                                 : "memory");
+                }
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) {
+                    if (head_layout) {
+                        const int hh = n / p.head_dim, d0 = n - hh * p.head_dim;
+                        tma_store_3d(omap, stg, d0, row0, b * p.heads + hh);
+                    } else {
+                        tma_store_3d(omap, stg, n, row0, b);
+                    }
+                    tma_store_commit();
+                }
+                ++nstore;
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty(a));
+        }
+        if (lane == 0) tma_store_wait<0>();
+    }
+
+    // ================= common tail =================
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+int sm_count()
+{
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        if (n <= 0) n = 148;
+    }
+    return n;
+}
+
+bool launch(cudaStream_t stream, const GemmMaps &maps, const GemmParams &p, const char *name)
+{
+    static bool configured = false;
+    if (!configured) {
+        KUTACC_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        configured = true;
+    }
+    const int s_tiles = (p.S + BM - 1) / BM;
+    const int64_t tiles = (int64_t)p.B * s_tiles * (p.seg_n / BN) * p.nseg;
+    const unsigned grid = (unsigned)std::min<int64_t>(tiles, sm_count());
+    KernelTimer timer__(name);
+    gemm_tcgen05_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(maps, p);
+    count_launch();
+    return true;
+}
+
+}  // namespace
+
+bool tcgen05_proj_qkvg_bf16(cudaStream_t stream, const void *x, const void *wq, const void *wk, const void *wv,
+                            const void *wg, const float *bg, void *q, void *k, void *v, void *gate, int B, int S,
+                            int H, int D)
+{
+    const int C = H * D;
+    if (C % 128 != 0 || (D != 32 && D != 64) || C > 256 * 64) return false;
+    KernelErrorWord &ew = kernel_error_word();
+    if (ew.device == nullptr) return false;
+    GemmMaps maps;
+    const void *w[4] = {wq, wk, wv, wg};
+    void *o[3] = {q, k, v};
+    if (!make_tensor_map_bf16_3d(&maps.a, x, C, S, B, C, (uint64_t)S * C, BK, BM, 128)) return false;
+    for (int i = 0; i < 4; ++i)
+        if (!make_tensor_map_bf16_3d(&maps.w[i], w[i], C, C, 1, C, (uint64_t)C * C, BK, BN, 128)) return false;
+    for (int i = 0; i < 3; ++i)
+        if (!make_tensor_map_bf16_3d(&maps.out[i], o[i], D, S, (uint64_t)B * H, D, (uint64_t)S * D, 32, 32, 64))
+            return false;
+    if (!make_tensor_map_bf16_3d(&maps.out[3], gate, C, S, B, C, (uint64_t)S * C, 32, 32, 64)) return false;
+    GemmParams p;
+    p.bias[0] = p.bias[1] = p.bias[2] = nullptr;
+    p.bias[3] = bg;
+    p.seg_n = C;
+    p.nseg = 4;
+    p.head_dim = D;
+    p.head_layout_mask = 0x7;
+    p.heads = H;
+    p.K = C;
+    p.S = S;
+    p.B = B;
+    p.err = ew.device;
+    return launch(stream, maps, p, "proj_qkvg");
+}
+
+bool tcgen05_linear_bias_bf16(cudaStream_t stream, const void *a, const void *w, const float *bias, void *out,
+                              int64_t out_row_stride, int B, int S, int N, int K)
+{
+    if (N % 128 != 0 || K % 64 != 0 || out_row_stride % 8 != 0 || ((uintptr_t)out & 15u) || ((uintptr_t)a & 15u) ||
+        ((uintptr_t)w & 15u))
+        return false;
+    KernelErrorWord &ew = kernel_error_word();
+    if (ew.device == nullptr) return false;
+    GemmMaps maps;
+    if (!make_tensor_map_bf16_3d(&maps.a, a, K, S, B, K, (uint64_t)S * K, BK, BM, 128)) return false;
+    if (!make_tensor_map_bf16_3d(&maps.w[0], w, K, N, 1, K, (uint64_t)N * K, BK, BN, 128)) return false;
+    if (!make_tensor_map_bf16_3d(&maps.out[0], out, N, S, B, (uint64_t)out_row_stride, (uint64_t)S * out_row_stride, 32,
+                                 32, 64))
+        return false;
+    for (int i = 1; i < 4; ++i) {
+        maps.w[i] = maps.w[0];
+        maps.out[i] = maps.out[0];
+    }
+    GemmParams p;
+    p.bias[0] = bias;
+    p.bias[1] = p.bias[2] = p.bias[3] = nullptr;
+    p.seg_n = N;
+    p.nseg = 1;
+    p.head_dim = 0;
+    p.head_layout_mask = 0;
+    p.heads = 1;
+    p.K = K;
+    p.S = S;
+    p.B = B;
+    p.err = ew.device;
+    return launch(stream, maps, p, "linear_bias");
+}
+
+}  // namespace dev
+}  // namespace kutacc

@@ -23,6 +23,14 @@ bool launch_proj_qkvg_bf16(cudaStream_t stream, const void *x, const void *wq, c
 bool launch_linear_bias_bf16(cudaStream_t stream, const void *a, int64_t lda, const void *w, const float *bias,
                              void *out, int64_t ldo, int64_t M, int N, int K);
 
+// tcgen05/TMEM/TMA versions of the two GEMMs above (C % 128 == 0, D in {32, 64}; N % 128 == 0,
+// K % 64 == 0, out row stride % 8 == 0). q is written unscaled. Return false when the shape is not covered.
+bool tcgen05_proj_qkvg_bf16(cudaStream_t stream, const void *x, const void *wq, const void *wk, const void *wv,
+                            const void *wg, const float *bg, void *q, void *k, void *v, void *gate, int B, int S,
+                            int H, int D);
+bool tcgen05_linear_bias_bf16(cudaStream_t stream, const void *a, const void *w, const float *bias, void *out,
+                              int64_t out_row_stride, int B, int S, int N, int K);
+
 // ---- fused attention core ------------------------------------------------------------------------
 // avg[b, s, h*D + d] = sigmoid(gate[b, s, h*D + d]) * softmax_k(bf16(q.k)*scale + bias[b,k] + nb[h,s,k]) . v
 // q, k, v are [B, H, S, D]. bf16; D in {16, 32, 64}. nb may be null; its strides must be multiples
