@@ -192,6 +192,24 @@ KUTACC_B200_API int kutacc_b200_profile_read(char *names, size_t names_cap, floa
 KUTACC_B200_API void kutacc_b200_comm_unique_id(void *id128);
 KUTACC_B200_API void kutacc_b200_comm_init_with_id(int64_t world_size_, int64_t rank_, const void *id128);
 
+/* Global attention for callers that must not allocate device memory inside the call (a server whose
+ * own pool already owns all of HBM, a loop that cannot take the implicit synchronisation of
+ * cudaMalloc/cudaFree, a process under a fixed memory quota). It has no counterpart in the reference.
+ * Same arithmetic as kutacc_af2_global_attention; every pointer is a device pointer owned by the caller
+ * (q_data [batch, seq_len, 64] bf16 contiguous, q_mask [batch, seq_len] bf16, weights as for the operator
+ * above, biases fp32, out [batch, seq_len, 64] bf16 with row stride out_row_stride elements); work is
+ * enqueued on cuda_stream and the call returns without synchronising. Its scratch is a 4 MiB array
+ * inside the library image, resident on every GPU that loads the library until the process exits;
+ * shapes that need more (batch * row-splits beyond about 7000) are refused with an error. The first
+ * call on a device looks up the array's device address: make it outside of stream capture. Calls share
+ * the array, so two calls that overlap on the GPU race. Returns 0, or -1 after reporting an error. */
+KUTACC_B200_API int kutacc_b200_global_attention_noalloc(const void *q_data, const void *q_mask, const void *query_w,
+                                                         const void *key_w, const void *value_w, const void *gating_w,
+                                                         const float *gating_b, const void *output_w,
+                                                         const float *output_b, void *out, int64_t out_row_stride,
+                                                         int64_t batch, int64_t seq_len, int64_t nheads,
+                                                         int64_t head_size, void *cuda_stream);
+
 /* Pair-bias projection written directly in the layout the attention operator consumes:
  * nb[h, q, k] = z[q, k, :] . wb[h, :]   with z [rows, n_k, c_z], wb [nheads, c_z], nb
  * [nheads, rows, n_k] (row stride of head h = nb_head_stride elements). Same arithmetic as

@@ -32,6 +32,7 @@ EXPORTS = [
     "kutacc_b200_device_malloc", "kutacc_b200_device_free", "kutacc_b200_memcpy_h2d", "kutacc_b200_memcpy_d2h",
     "kutacc_b200_workspace_bytes", "kutacc_b200_release_workspace", "kutacc_b200_launch_count",
     "kutacc_b200_set_profile", "kutacc_b200_profile_read", "kutacc_b200_comm_unique_id", "kutacc_b200_comm_init_with_id", "kutacc_b200_pair_bias",
+    "kutacc_b200_global_attention_noalloc",
 ]
 EXPORTED_DATA = ["world_size", "rank"]
 
@@ -119,6 +120,8 @@ def lib() -> C.CDLL:
     L.kutacc_b200_comm_unique_id.restype = None
     L.kutacc_b200_comm_init_with_id.argtypes = [i64, i64, vp]
     L.kutacc_b200_comm_init_with_id.restype = None
+    L.kutacc_b200_global_attention_noalloc.argtypes = [vp] * 10 + [i64] * 5 + [vp]
+    L.kutacc_b200_global_attention_noalloc.restype = C.c_int
     L.kutacc_b200_pair_bias.argtypes = [vp, vp, vp]
     L.kutacc_b200_pair_bias.restype = None
     _lib = L

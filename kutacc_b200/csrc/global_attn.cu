@@ -18,6 +18,7 @@
 #include "ptx_utils.cuh"
 
 #include <algorithm>
+#include <climits>
 
 namespace kutacc {
 namespace dev {
@@ -434,3 +435,83 @@ bool launch_global_attention_bf16(cudaStream_t stream, const void *x, const void
 
 }  // namespace dev
 }  // namespace kutacc
+
+// ---------------------------------------------------------------------------------------------------
+// Global attention without any allocation.
+//
+// Some hosts of this library may not allocate device memory when they call an operator: an inference
+// server that handed all of HBM to its own pool at start-up (cudaMalloc then fails or fragments the
+// pool), a latency-critical loop that cannot accept the device-wide synchronisation cudaMalloc and
+// cudaFree imply, or a process running under a fixed memory quota. For them this entry point runs the
+// same three kernels as kutacc_af2_global_attention with the split-softmax scratch placed in a
+// file-scope device array instead of the library's grow-only workspace. Inputs and outputs are plain
+// device pointers supplied by the caller; nothing is staged, and no CUDA allocation routine is called.
+//
+// The array is part of the library image: every GPU that loads the library holds
+// KUTACC_B200_NOALLOC_SCRATCH_BYTES (4 MiB) of it until the process exits. The first call on each
+// device resolves the array's device address (cudaGetSymbolAddress); make that first call outside of
+// any stream capture. All calls share the one array and it keeps whatever the previous call left, so
+// two calls that overlap on the GPU (different streams, or different host threads) race; every slot a
+// call reads is written earlier in that same call, so nothing has to be cleared between calls.
+// ---------------------------------------------------------------------------------------------------
+#define KUTACC_B200_NOALLOC_SCRATCH_BYTES (4u << 20)
+static __device__ __align__(256) unsigned char g_noalloc_scratch[KUTACC_B200_NOALLOC_SCRATCH_BYTES];
+
+namespace {
+constexpr int kMaxDevices = 64;
+void *g_noalloc_scratch_addr[kMaxDevices] = {};
+
+// In host code the array's name is only a handle for the runtime, not an address a kernel could use:
+// the device address has to be asked for, once per device, with that device current.
+void *noalloc_scratch_for_current_device()
+{
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+    if (g_noalloc_scratch_addr[dev] == nullptr) {
+        void *ptr = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+        KUTACC_CHECK(e == cudaSuccess, "cudaGetSymbolAddress(static scratch): ", cudaGetErrorString(e));
+        if (e != cudaSuccess) return nullptr;
+        g_noalloc_scratch_addr[dev] = ptr;
+    }
+    return g_noalloc_scratch_addr[dev];
+}
+}  // namespace
+
+extern "C" int kutacc_b200_global_attention_noalloc(const void *q_data, const void *q_mask, const void *query_w,
+                                                    const void *key_w, const void *value_w, const void *gating_w,
+                                                    const float *gating_b, const void *output_w,
+                                                    const float *output_b, void *out, int64_t out_row_stride,
+                                                    int64_t batch, int64_t seq_len, int64_t nheads, int64_t head_size,
+                                                    void *cuda_stream)
+{
+    using namespace kutacc;
+    if (kutacc_check_err_set) return -1;
+    KUTACC_CHECK(q_data && q_mask && query_w && key_w && value_w && gating_w && gating_b && output_w && output_b && out,
+                 "kutacc_b200_global_attention_noalloc: nullptr error");
+    KUTACC_CHECK(batch > 0 && seq_len > 0 && nheads > 0 && head_size > 0 && nheads * head_size == 64 &&
+                     batch <= 65535 && seq_len <= INT32_MAX / 64 && out_row_stride >= 64 && out_row_stride % 8 == 0,
+                 "kutacc_b200_global_attention_noalloc: invalid size (64 channels, batch <= 65535, out row stride a "
+                 "multiple of 8 required)");
+    if (kutacc_check_err_set) return -1;
+    KUTACC_CHECK((((uintptr_t)q_data | (uintptr_t)out | (uintptr_t)gating_w | (uintptr_t)output_w) & 15u) == 0,
+                 "kutacc_b200_global_attention_noalloc: q_data, out and weights must be 16-byte aligned");
+    const size_t need = dev::global_attention_scratch_bytes((int)batch, (int)seq_len, (int)nheads, (int)head_size);
+    KUTACC_CHECK(need <= KUTACC_B200_NOALLOC_SCRATCH_BYTES, "kutacc_b200_global_attention_noalloc: this shape needs ",
+                 need, " bytes of scratch, the static scratch holds ", (size_t)KUTACC_B200_NOALLOC_SCRATCH_BYTES,
+                 " (use kutacc_af2_global_attention for larger batches)");
+    if (kutacc_check_err_set) return -1;
+    void *scratch = noalloc_scratch_for_current_device();
+    if (scratch == nullptr) {
+        KUTACC_CHECK(false, "kutacc_b200_global_attention_noalloc: static scratch is not available on this device");
+        return -1;
+    }
+    cudaStream_t stream = (cudaStream_t)cuda_stream;
+    const bool ok = dev::launch_global_attention_bf16(stream, q_data, q_mask, query_w, key_w, value_w, gating_w,
+                                                      gating_b, output_w, output_b, out, out_row_stride, scratch,
+                                                      (int)batch, (int)seq_len, (int)nheads, (int)head_size);
+    KUTACC_CHECK(ok, "kutacc_b200_global_attention_noalloc: no kernel for nheads=", nheads, " head_size=", head_size);
+    const cudaError_t e = cudaGetLastError();
+    KUTACC_CHECK(e == cudaSuccess, "kernel launch failed: ", cudaGetErrorString(e));
+    return kutacc_check_err_set ? -1 : 0;
+}
