@@ -9,8 +9,9 @@
 //   warp 0      producer: TMA loads of 128 x 64 slabs of X and W (128-byte swizzle) into a 5-stage ring
 //   warp 1      MMA issuer: one elected lane issues tcgen05.mma (M = 128, N = 128, K = 16) four times per
 //               slab into one of four 128-column TMEM accumulators and commits to mbarriers
-//   warps 2-5   epilogue: tcgen05.ld of the warp's 32 TMEM lanes, bias add, bf16 rounding, a swizzled
-//               32 x 32 staging tile in shared memory, TMA store into the destination layout
+//   warps 2-9   epilogue: each warp owns 32 TMEM lanes x 64 columns of the tile: two tcgen05.ld in flight,
+//               bias add, bf16 rounding, swizzled 32 x 32 staging tiles in shared memory, TMA stores into
+//               the destination layout
 // The four accumulators let the epilogue of tile i overlap the MMAs of tiles i+1 .. i+3.
 //
 // For the fused Q/K/V/gate projection the four weights are four tensor maps and the destination maps
@@ -39,7 +40,7 @@ constexpr int NSTAGE = 5;
 constexpr int ACC_STAGES = 4;
 constexpr int SLAB_BYTES = BM * BK * 2;                 // 16 KB, A and W slabs alike
 constexpr int STAGE_BYTES = 2 * SLAB_BYTES;
-constexpr int EPI_WARPS = 4;
+constexpr int EPI_WARPS = 8;                            // two per TMEM lane quarter, 64 columns each
 constexpr int STG_BYTES = 32 * 32 * 2;                  // one 32 x 32 bf16 staging tile
 constexpr int STG_PER_WARP = 2;
 constexpr int STG_OFF = NSTAGE * STAGE_BYTES;
@@ -233,6 +234,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p)
         // ================= epilogue =================
         const int quad = warp & 3;                            // TMEM lanes 32*quad .. 32*quad+31
         const int ew = warp - 2;
+        const int half = ew >> 2;                             // which 64 columns of the 128-column tile
         const uint32_t stg0 = smem + STG_OFF + (uint32_t)(ew * STG_PER_WARP) * STG_BYTES;
         int tcount = 0, nstore = 0;
         bool ok = true;
@@ -250,24 +252,31 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p)
             const bool head_layout = (p.head_layout_mask >> seg) & 1;
             const CUtensorMap *omap = &maps.out[seg];
             const int row0 = s0 + quad * 32;                  // first row of this warp inside the batch row
-#pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                uint32_t r[32];
-                tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(a * BN + c * 32), r);
-                tmem_ld_wait();
-                const int n = n0 + c * 32;
-                uint32_t packed[16];
+            uint32_t r[2][32];
+            const uint32_t tcol = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(a * BN + half * 64);
+            tmem_ld_32x32(tcol, r[0]);
+            tmem_ld_32x32(tcol + 32, r[1]);
+            tmem_ld_wait();
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    float v0 = __uint_as_float(r[2 * j]), v1 = __uint_as_float(r[2 * j + 1]);
-                    if (bias) {
-                        v0 += __ldg(bias + n + 2 * j);
-                        v1 += __ldg(bias + n + 2 * j + 1);
+            for (int c = 0; c < 2; ++c) {
+                const int n = n0 + half * 64 + c * 32;
+                uint32_t packed[16];
+                if (bias) {
+#pragma unroll
+                    for (int j4 = 0; j4 < 8; ++j4) {
+                        const float4 bv = __ldg(reinterpret_cast<const float4 *>(bias + n) + j4);
+                        packed[2 * j4] = pack_bf16x2(__uint_as_float(r[c][4 * j4]) + bv.x,
+                                                     __uint_as_float(r[c][4 * j4 + 1]) + bv.y);
+                        packed[2 * j4 + 1] = pack_bf16x2(__uint_as_float(r[c][4 * j4 + 2]) + bv.z,
+                                                         __uint_as_float(r[c][4 * j4 + 3]) + bv.w);
                     }
-                    packed[j] = pack_bf16x2(v0, v1);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        packed[j] = pack_bf16x2(__uint_as_float(r[c][2 * j]), __uint_as_float(r[c][2 * j + 1]));
                 }
                 // staging tile: row = lane, 64 bytes per row, 16-byte chunks swizzled as the 64-byte TMA mode
-                const uint32_t stg = stg0 + (uint32_t)(nstore % STG_PER_WARP) * STG_BYTES;
+                const uint32_t stg = stg0 + (uint32_t)c * STG_BYTES;
                 if (nstore >= STG_PER_WARP) {
                     if (lane == 0) tma_store_wait_read<STG_PER_WARP - 1>();
                     __syncwarp();
@@ -343,7 +352,7 @@ bool tcgen05_proj_qkvg_bf16(cudaStream_t stream, const void *x, const void *wq, 
                             int H, int D)
 {
     const int C = H * D;
-    if (C % 128 != 0 || (D != 32 && D != 64) || C > 256 * 64) return false;
+    if (C % 128 != 0 || (D != 32 && D != 64) || C > 256 * 64 || ((uintptr_t)bg & 15u)) return false;
     KernelErrorWord &ew = kernel_error_word();
     if (ew.device == nullptr) return false;
     GemmMaps maps;
@@ -375,7 +384,7 @@ bool tcgen05_linear_bias_bf16(cudaStream_t stream, const void *a, const void *w,
                               int64_t out_row_stride, int B, int S, int N, int K)
 {
     if (N % 128 != 0 || K % 64 != 0 || out_row_stride % 8 != 0 || ((uintptr_t)out & 15u) || ((uintptr_t)a & 15u) ||
-        ((uintptr_t)w & 15u))
+        ((uintptr_t)w & 15u) || ((uintptr_t)bias & 15u))
         return false;
     KernelErrorWord &ew = kernel_error_word();
     if (ew.device == nullptr) return false;
