@@ -1,0 +1,431 @@
+// Fused gated-attention core on the fifth-generation tensor cores (head size 32).
+//
+// One CTA owns (batch row b, head h, 128 queries); two CTAs share an SM. Both matrix products run on
+// tcgen05.mma with accumulators in tensor memory, issued by one elected lane; the softmax runs
+// one-thread-per-query-row on the logits read back with tcgen05.ld, so no shuffles are needed for the row
+// max and row sum. The S x S logits never leave the SM.
+//
+//   warp 0     producer: TMA tile loads (hardware swizzle) of Q once, then per 64-key tile K [64 x 32],
+//              V^T [32 x 64] and the 128 x 64 pair-bias tile; its lanes also convert the tile's 64
+//              mask-bias values to fp32
+//   warp 1     MMA issuer: S = Q.K^T (M 128, N 64, K 32) into TMEM columns 0..63; then two products
+//              O_h += P[:, 32h..32h+31] . V^T[:, 32h..32h+31]^T (M 128, N 48, K 32), h = 0, 1, into two
+//              separate TMEM accumulators. Row 32 of the V^T operand is all ones, so column 32 of each O_h
+//              accumulates the row sum of the bf16 probabilities for free
+//   warps 2-9  softmax: two threads per query row, one per 32-key half of every tile (split-key online
+//              softmax: each half keeps its own running max and its own accumulator, merged once at the
+//              end). A thread pulls its 32 logits out of TMEM (S is free for the next tile's Q.K^T once all
+//              have done so), rounds each raw logit to bf16 as the reference's logits scratch does
+//              (src/attention/gating_attention.cpp:97-101), forms x = logit*scale + bias + pair_bias in
+//              fp32 in the reference's order (:112-117), and writes P = exp(x - max) as bf16 over the
+//              pair-bias values it has just consumed (same row, same swizzled chunks), which is the A
+//              operand of P.V^T. O_h is rescaled in TMEM only when the max grows by more than 2^8 (a stale
+//              max cancels in the final division), so the correction is rare. Epilogue: the two halves are
+//              merged through shared memory, O / rowsum, bf16 (:128-133), sigmoid gate (:134-147),
+//              64-byte row stores.
+//
+// Fully masked rows stay uniform as in the reference (fp32 absorption of the logit by the -1e9 bias).
+// All mbarrier waits are bounded; on a timeout the roles fall through to the common tail, tensor memory
+// is released, and the host-visible error word carries the site.
+#include "common.h"
+#include "kernels.h"
+#include "ptx_utils.cuh"
+#include "tcgen05_utils.cuh"
+#include "tma_utils.cuh"
+
+namespace kutacc {
+namespace dev {
+
+namespace {
+
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr int D = 32;                 // head size
+constexpr int BM = 128;               // queries per CTA
+constexpr int BN = 64;                // keys per tile
+constexpr int NST = 3;                // ring depth
+constexpr int VT_ROWS = 48;           // 32 channels + the ones row + zero padding to a multiple of 16
+constexpr int Q_BYTES = BM * D * 2;           // 8 KB, 64-byte rows, 64-byte swizzle
+constexpr int K_BYTES = BN * D * 2;           // 4 KB, 64-byte rows
+constexpr int VT_BYTES = VT_ROWS * BN * 2;    // 6 KB, 128-byte rows (TMA fills the first 32)
+constexpr int NB_BYTES = BM * BN * 2;         // 16 KB, 128-byte rows: pair bias in, probabilities out (in place)
+constexpr int MB_BYTES = 1024;                // 64 floats, padded
+constexpr int STAGE_BYTES = K_BYTES + VT_BYTES + NB_BYTES + MB_BYTES;
+constexpr int OFF_STAGE = Q_BYTES;
+constexpr int OFF_BAR = OFF_STAGE + NST * STAGE_BYTES;
+constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
+constexpr int SOFTMAX_WARPS = 8;
+constexpr int THREADS = (2 + SOFTMAX_WARPS) * 32;
+constexpr int TMEM_COLS = 256;
+constexpr int S_COL = 0, O_COL = 64, O_STRIDE = VT_ROWS;   // O_0 at 64..111, O_1 at 112..159
+constexpr int XCH_STRIDE = 36;        // floats per row of the end-of-kernel exchange buffer
+constexpr float kRescaleThreshold = 8.0f;     // log2 units
+
+struct AttnParams {
+    const __nv_bfloat16 *gate;        // [B, S, H*D]
+    const __nv_bfloat16 *bias;        // [B, S] (row stride bias_stride0)
+    __nv_bfloat16 *avg;               // [B, S, H*D]
+    int64_t bias_stride0;
+    int *err;
+    int S, H;
+    float scale;
+};
+
+template <bool HAS_NB>
+__global__ void __launch_bounds__(THREADS, 2)
+attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+               const __grid_constant__ CUtensorMap tm_vt, const __grid_constant__ CUtensorMap tm_nb,
+               const AttnParams p)
+{
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t smem = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    unsigned char *smem_gen = smem_raw + (smem - smem_u32(smem_raw));
+    const uint32_t q_base = smem;
+    auto stage_base = [&](int s) { return smem + OFF_STAGE + (uint32_t)s * STAGE_BYTES; };
+    const uint32_t bar = smem + OFF_BAR;
+    auto kv_full = [&](int s) { return bar + 8u * (uint32_t)s; };
+    auto kv_empty = [&](int s) { return bar + 8u * (uint32_t)(NST + s); };
+    // P lives in the ring stage, so "P written" is tracked per stage: a softmax warp that runs a tile ahead
+    // of a slower one then arrives on a different barrier instead of completing the slower tile's phase
+    auto p_full = [&](int s) { return bar + 8u * (uint32_t)(2 * NST + s); };
+    // pv_done completes once per tile and is only awaited on the rare rescale path, where the waiter is
+    // provably at most one phase behind. The end of the last product has its own single-phase barrier: a
+    // parity wait names "the current or the preceding phase", so a warp that runs more than one tile ahead
+    // of the slowest one must not use pv_done's parity to learn that everything has retired.
+    const uint32_t q_full = bar + 8u * (3 * NST), s_full = q_full + 8, s_free = q_full + 16, pv_done = q_full + 24,
+                   o_final = q_full + 32, tmem_slot = q_full + 40;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int S = p.S;
+    const int q0 = blockIdx.x * BM, h = blockIdx.y, b = blockIdx.z;
+    const int bh = b * p.H + h;
+    const int nkt = (S + BN - 1) / BN;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < NST; ++s) {
+            mbar_init(kv_full(s), 33);      // 32 producer lanes (mask bias) + the expect_tx arrival
+            mbar_init(kv_empty(s), 1);      // the commit that follows P.V^T (P lives in the stage)
+            mbar_init(p_full(s), SOFTMAX_WARPS);
+        }
+        mbar_init(q_full, 1);
+        mbar_init(s_full, 1);
+        mbar_init(s_free, SOFTMAX_WARPS);
+        mbar_init(pv_done, 1);
+        mbar_init(o_final, 1);
+        fence_barrier_init();
+    }
+    // static rows 32..47 of every V^T stage: row 32 = 1.0 (row-sum column of O), rows 33..47 = 0
+    for (int i = threadIdx.x; i < NST * 16 * (BN * 2 / 16); i += THREADS) {
+        const int s = i / (16 * 8), rem = i % (16 * 8), row = 32 + rem / 8, ch = rem % 8;
+        const uint32_t v = row == 32 ? 0x3F803F80u : 0u;
+        uint4 *dst = reinterpret_cast<uint4 *>(smem_gen + OFF_STAGE + s * STAGE_BYTES + K_BYTES + row * 128 + ch * 16);
+        *dst = make_uint4(v, v, v, v);
+    }
+    fence_proxy_async();
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    uint32_t tmem_base;
+    asm volatile("ld.shared.b32 %0, [%1];\n" : "=r"(tmem_base) : "r"(tmem_slot));
+
+    if (warp == 0) {
+        // ================= producer =================
+        if (lane == 0) {
+            tma_prefetch_desc(&tm_q);
+            tma_prefetch_desc(&tm_k);
+            tma_prefetch_desc(&tm_vt);
+            if (HAS_NB) tma_prefetch_desc(&tm_nb);
+            mbar_arrive_expect_tx(q_full, Q_BYTES);
+            tma_load_3d(q_base, &tm_q, q_full, 0, q0, bh);
+        }
+        const __nv_bfloat16 *__restrict__ biasg = p.bias + (int64_t)b * p.bias_stride0;
+        for (int kt = 0; kt < nkt; ++kt) {
+            const int s = kt % NST;
+            if (kt >= NST && !mbar_wait_warp(kv_empty(s), (uint32_t)((kt / NST - 1) & 1), p.err, 21)) break;
+            const uint32_t st = stage_base(s);
+            const int k0 = kt * BN;
+            float *mb = reinterpret_cast<float *>(smem_gen + OFF_STAGE + s * STAGE_BYTES + K_BYTES + VT_BYTES + NB_BYTES);
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const int key = k0 + lane + 32 * j;
+                mb[lane + 32 * j] = key < S ? __bfloat162float(biasg[key]) : -INFINITY;
+            }
+            if (lane == 0) {
+                mbar_arrive_expect_tx(kv_full(s), K_BYTES + BN * D * 2 + (HAS_NB ? NB_BYTES : 0));
+                tma_load_3d(st, &tm_k, kv_full(s), 0, k0, bh);
+                tma_load_3d(st + K_BYTES, &tm_vt, kv_full(s), k0, 0, bh);
+                if (HAS_NB) tma_load_3d(st + K_BYTES + VT_BYTES, &tm_nb, kv_full(s), k0, q0, h);
+            }
+            mbar_arrive(kv_full(s));
+        }
+    } else if (warp == 1) {
+        // ================= MMA issuer =================
+        constexpr uint32_t idesc_s = make_instr_desc_bf16(BM, BN);
+        constexpr uint32_t idesc_o = make_instr_desc_bf16(BM, VT_ROWS);
+        bool ok = mbar_wait_warp(q_full, 0, p.err, 22);
+        auto issue_qk = [&](int kt) -> bool {
+            const int s = kt % NST;
+            if (!mbar_wait_warp(kv_full(s), (uint32_t)((kt / NST) & 1), p.err, 23)) return false;
+            if (kt > 0 && !mbar_wait_warp(s_free, (uint32_t)((kt - 1) & 1), p.err, 24)) return false;
+            tc_fence_after();
+            if (lane == 0) {
+                const uint32_t kb = stage_base(s);
+#pragma unroll
+                for (int k = 0; k < D / 16; ++k)
+                    tc_mma_bf16(tmem_base + S_COL, make_smem_desc_kmajor(q_base + k * 32, 64),
+                                make_smem_desc_kmajor(kb + k * 32, 64), idesc_s, k > 0 ? 1u : 0u);
+                tc_commit(s_full);
+            }
+            __syncwarp();
+            return true;
+        };
+        if (ok) ok = issue_qk(0);
+        for (int kt = 0; kt < nkt && ok; ++kt) {
+            const int s = kt % NST;
+            if (kt + 1 < nkt) ok = issue_qk(kt + 1);     // overlaps the softmax of tile kt
+            if (!ok) break;
+            if (!mbar_wait_warp(p_full(s), (uint32_t)((kt / NST) & 1), p.err, 25)) {
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            if (lane == 0) {
+                const uint32_t vb = stage_base(s) + K_BYTES, pb = vb + VT_BYTES;
+#pragma unroll
+                for (int k = 0; k < BN / 16; ++k)        // k16 steps 0,1 -> O_0 (keys 0..31), 2,3 -> O_1 (keys 32..63)
+                    tc_mma_bf16(tmem_base + O_COL + (k >> 1) * O_STRIDE, make_smem_desc_kmajor(pb + k * 32, 128),
+                                make_smem_desc_kmajor(vb + k * 32, 128), idesc_o, (kt > 0 || (k & 1)) ? 1u : 0u);
+                tc_commit(pv_done);
+                tc_commit(kv_empty(s));
+                if (kt == nkt - 1) tc_commit(o_final);
+            }
+            __syncwarp();
+        }
+    } else {
+        // ================= softmax / epilogue =================
+        const int quad = warp & 3;                       // TMEM lanes 32*quad .. 32*quad+31
+        const int half = (warp - 2) >> 2;                // which 32 keys of every tile this thread owns
+        const int row = quad * 32 + lane;                // query row inside the tile
+        const uint32_t t_lane = tmem_base + ((uint32_t)(quad * 32) << 16);
+        const uint32_t o_col = t_lane + O_COL + half * O_STRIDE;
+        const float scale = p.scale;
+        float m2 = -INFINITY;                            // running (possibly stale) max of this half, log2 units
+        bool ok = true;
+        for (int kt = 0; kt < nkt && ok; ++kt) {
+            const int s = kt % NST;
+            if (!mbar_wait_warp(s_full, (uint32_t)(kt & 1), p.err, 26)) {
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            uint32_t sr[32];
+            tmem_ld_32x32(t_lane + S_COL + half * 32, sr);
+            tmem_ld_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(s_free);
+            if (!mbar_wait_warp(kv_full(s), (uint32_t)((kt / NST) & 1), p.err, 27)) {
+                ok = false;
+                break;
+            }
+            const uint32_t st = stage_base(s);
+            const uint32_t nb_row = st + K_BYTES + VT_BYTES + (uint32_t)row * 128;     // also this row of P
+            const uint32_t mb_base = st + K_BYTES + VT_BYTES + NB_BYTES + half * 128;
+
+            // x = bf16(logit)*scale + bias (+ pair bias); max over this thread's 32 keys
+            float tmax = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {                // 8 keys per step
+                const float4 mb0 = lds128_f32(mb_base + c * 32), mb1 = lds128_f32(mb_base + c * 32 + 16);
+                const float mbv[8] = {mb0.x, mb0.y, mb0.z, mb0.w, mb1.x, mb1.y, mb1.z, mb1.w};
+                uint32_t nbw[4] = {0, 0, 0, 0};
+                if (HAS_NB) {
+                    asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];\n"
+                                 : "=r"(nbw[0]), "=r"(nbw[1]), "=r"(nbw[2]), "=r"(nbw[3])
+                                 : "r"(nb_row + (uint32_t)(((half * 4 + c) ^ (row & 7)) << 4)));
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int i0 = c * 8 + 2 * j;
+                    // the raw logit is stored as bf16 by the reference: one cvt gives its fp32 image
+                    float x0 = fmaf(round_to_bf16_f32(__uint_as_float(sr[i0])), scale, mbv[2 * j]);
+                    float x1 = fmaf(round_to_bf16_f32(__uint_as_float(sr[i0 + 1])), scale, mbv[2 * j + 1]);
+                    if (HAS_NB) {
+                        x0 += bf16lo_to_f32(nbw[j]);
+                        x1 += bf16hi_to_f32(nbw[j]);
+                    }
+                    sr[i0] = __float_as_uint(x0);
+                    sr[i0 + 1] = __float_as_uint(x1);
+                    tmax = fmax3(tmax, x0, x1);
+                }
+            }
+            // a half whose keys all lie beyond S has no max yet: park it on a finite floor
+            const float t2 = tmax > -INFINITY ? tmax * kLog2e : -1e30f;
+            const bool grow = kt == 0 || t2 > m2 + kRescaleThreshold;
+            if (__any_sync(0xffffffffu, grow && kt > 0)) {
+                // rescale this row of O_half (and its row-sum column) to the new max; the previous tile's
+                // P.V^T must have retired first
+                if (!mbar_wait_warp(pv_done, (uint32_t)((kt - 1) & 1), p.err, 28)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const float f = grow ? ex2_approx(m2 - t2) : 1.0f;
+                uint32_t o[32];
+                tmem_ld_32x32(o_col, o);
+                uint32_t osum = tmem_ld_32x1(o_col + 32);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
+                osum = __float_as_uint(__uint_as_float(osum) * f);
+                tmem_st_32x32(o_col, o);
+                tmem_st_32x1(o_col + 32, osum);
+                tmem_st_wait();
+                tc_fence_before();
+            }
+            if (grow) m2 = t2;
+
+            // probabilities -> bf16 -> over this thread's pair-bias chunks (A operand of P.V^T)
+            const float mneg = -m2;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint32_t w[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int i0 = c * 8 + 2 * j;
+                    const float p0 = ex2_approx(fmaf(__uint_as_float(sr[i0]), kLog2e, mneg));
+                    const float p1 = ex2_approx(fmaf(__uint_as_float(sr[i0 + 1]), kLog2e, mneg));
+                    w[j] = pack_bf16x2(p0, p1);
+                }
+                asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};\n" ::"r"(nb_row + (uint32_t)(((half * 4 + c) ^ (row & 7)) << 4)),
+                             "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3])
+                             : "memory");
+            }
+            fence_proxy_async();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_full(s));
+        }
+
+        // ---- epilogue: merge the two key halves of each row, normalise, gate, store ----
+        ok = ok && mbar_wait_warp(o_final, 0, p.err, 29);
+        uint32_t o[32];
+        float lsum = 0.f;
+        if (ok) {
+            tc_fence_after();
+            tmem_ld_32x32(o_col, o);
+            lsum = __uint_as_float(tmem_ld_32x1(o_col + 32));
+            tmem_ld_wait();
+        }
+        // exchange buffer: stage 0 is idle now (every tile load has been consumed)
+        float *xch = reinterpret_cast<float *>(smem_gen + OFF_STAGE + K_BYTES + VT_BYTES) + row * XCH_STRIDE;
+        if (half == 1 && ok) {
+            xch[0] = m2;
+            xch[1] = lsum;
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                *reinterpret_cast<float4 *>(xch + 4 + 4 * i) =
+                    make_float4(__uint_as_float(o[4 * i]), __uint_as_float(o[4 * i + 1]), __uint_as_float(o[4 * i + 2]),
+                                __uint_as_float(o[4 * i + 3]));
+        }
+        asm volatile("bar.sync 1, %0;\n" ::"n"(SOFTMAX_WARPS * 32) : "memory");
+        const int qi = q0 + row;
+        if (half == 0 && ok && qi < S) {
+            const float mB = xch[0], lB = xch[1];
+            const float mm = fmaxf(m2, mB);
+            const float fA = ex2_approx(m2 - mm), fB = ex2_approx(mB - mm);
+            const float inv = 1.0f / (lsum * fA + lB * fB);
+            const float cA = fA * inv, cB = fB * inv;
+            const int Cn = p.H * D;
+            const int64_t base = ((int64_t)b * S + qi) * Cn + h * D;
+            const uint4 *gp = reinterpret_cast<const uint4 *>(p.gate + base);
+            uint4 *op = reinterpret_cast<uint4 *>(p.avg + base);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const uint4 gv = __ldg(gp + c);
+                const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
+                const float4 b0 = *reinterpret_cast<const float4 *>(xch + 4 + 8 * c);
+                const float4 b1 = *reinterpret_cast<const float4 *>(xch + 8 + 8 * c);
+                const float ob[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+                uint32_t ow[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int i0 = c * 8 + 2 * j;
+                    // the weighted average is stored as bf16 before gating in the reference (:128-133)
+                    const uint32_t wa = pack_bf16x2(__uint_as_float(o[i0]) * cA + ob[2 * j] * cB,
+                                                    __uint_as_float(o[i0 + 1]) * cA + ob[2 * j + 1] * cB);
+                    const float s0 = 1.0f / (1.0f + ex2_approx(-bf16lo_to_f32(gw[j]) * kLog2e));
+                    const float s1 = 1.0f / (1.0f + ex2_approx(-bf16hi_to_f32(gw[j]) * kLog2e));
+                    ow[j] = pack_bf16x2(bf16lo_to_f32(wa) * s0, bf16hi_to_f32(wa) * s1);
+                }
+                op[c] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+            }
+        }
+    }
+
+    // ================= common tail =================
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+template <bool HAS_NB>
+bool launch_one(cudaStream_t stream, const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tvt,
+                const CUtensorMap &tnb, const AttnParams &p, int B)
+{
+    static bool configured = false;
+    if (!configured) {
+        KUTACC_CUDA(cudaFuncSetAttribute(attn_tc_kernel<HAS_NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        configured = true;
+    }
+    dim3 grid((unsigned)((p.S + BM - 1) / BM), (unsigned)p.H, (unsigned)B);
+    KernelTimer timer__("attn_core");
+    attn_tc_kernel<HAS_NB><<<grid, THREADS, SMEM_BYTES, stream>>>(tq, tk, tvt, tnb, p);
+    count_launch();
+    return true;
+}
+
+}  // namespace
+
+bool tcgen05_attn_core_bf16(cudaStream_t stream, const void *q, const void *k, const void *vt, int64_t vt_pitch,
+                            const void *gate, const void *bias, int64_t bias_stride0, const void *nb,
+                            int64_t nb_stride_h, int64_t nb_stride_q, void *avg, int B, int S, int H, int Dh,
+                            float scale)
+{
+    if (Dh != D || B > 65535 || H > 65535 || vt_pitch % 8 != 0) return false;
+    if (nb && ((nb_stride_h % 8) || (nb_stride_q % 8) || ((uintptr_t)nb % 16))) return false;
+    if ((((uintptr_t)gate | (uintptr_t)avg) & 15u) != 0) return false;
+    KernelErrorWord &ew = kernel_error_word();
+    if (ew.device == nullptr) return false;
+    AttnParams p;
+    p.gate = (const __nv_bfloat16 *)gate;
+    p.bias = (const __nv_bfloat16 *)bias;
+    p.avg = (__nv_bfloat16 *)avg;
+    p.bias_stride0 = bias_stride0;
+    p.err = ew.device;
+    p.S = S;
+    p.H = H;
+    p.scale = scale;
+    const uint64_t Su = (uint64_t)S, BH = (uint64_t)B * H;
+    CUtensorMap tq, tk, tvt, tnb;
+    if (!make_tensor_map_bf16_3d(&tq, q, D, Su, BH, D, Su * D, D, BM, 64)) return false;
+    if (!make_tensor_map_bf16_3d(&tk, k, D, Su, BH, D, Su * D, D, BN, 64)) return false;
+    if (!make_tensor_map_bf16_3d(&tvt, vt, Su, D, BH, (uint64_t)vt_pitch, (uint64_t)D * vt_pitch, BN, D, 128)) return false;
+    if (nb) {
+        if (!make_tensor_map_bf16_3d(&tnb, nb, Su, Su, (uint64_t)H, (uint64_t)nb_stride_q, (uint64_t)nb_stride_h, BN, BM,
+                                     128))
+            return false;
+        return launch_one<true>(stream, tq, tk, tvt, tnb, p, B);
+    }
+    tnb = tk;
+    return launch_one<false>(stream, tq, tk, tvt, tnb, p, B);
+}
+
+}  // namespace dev
+}  // namespace kutacc

@@ -121,7 +121,7 @@ attn_core_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         for (int kt = 0; kt < nkt; ++kt) {
             const int s = kt % C::NST;
             if (kt >= C::NST) {
-                if (!mbar_wait(empty_bar(s), (uint32_t)((kt / C::NST - 1) & 1), p.err, 1)) return;
+                if (!mbar_wait_warp(empty_bar(s), (uint32_t)((kt / C::NST - 1) & 1), p.err, 1)) return;
             }
             const uint32_t st = smem + (uint32_t)s * C::STAGE_BYTES;
             const int k0 = kt * C::BN;
@@ -165,7 +165,7 @@ attn_core_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     }
     const uint32_t mb_off = (uint32_t)(C::NB_BYTES + 2 * C::KV_BYTES + t * 64);
 
-    if (!mbar_wait(q_bar, 0, p.err, 2)) return;
+    if (!mbar_wait_warp(q_bar, 0, p.err, 2)) return;
     uint32_t qf[C::KS][4];
 #pragma unroll
     for (int ks = 0; ks < C::KS; ++ks)
@@ -186,7 +186,7 @@ attn_core_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         for (int s = 0; s < C::NST; ++s) {
             const int kt = kt0 + s;
             if (kt >= nkt) break;
-            if (!mbar_wait(full_bar(s), (uint32_t)((kt0 / C::NST) & 1), p.err, 3)) return;
+            if (!mbar_wait_warp(full_bar(s), (uint32_t)((kt0 / C::NST) & 1), p.err, 3)) return;
             const uint32_t st = smem + (uint32_t)s * C::STAGE_BYTES;
             const uint32_t k_base = st + C::NB_BYTES, v_base = k_base + C::KV_BYTES;
 

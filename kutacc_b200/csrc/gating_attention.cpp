@@ -2,6 +2,7 @@
 // Replaces src/attention/gating_attention.cpp:33-200 of the reference.
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <climits>
 #include <cmath>
 
@@ -71,8 +72,10 @@ static void gating_attention_impl(Tensor &input, int64_t batch, int64_t seq_len,
     for (const Tensor *w : {&query_w, &key_w, &value_w, &gating_w, &output_w})
         stage += staged_bytes_needed(w->data_ptr(), w_bytes);
     if (!rt.reserve_stage(stage)) return;
-    const size_t nb_pad_bytes = has_nb ? (size_t)H * S * ((S + 7) / 8 * 8) * 2 : 0;
-    if (!rt.reserve_workspace(5 * (x_bytes + 256) + nb_pad_bytes + 256)) return;
+    const int64_t s_pad8 = (S + 7) / 8 * 8;
+    const size_t nb_pad_bytes = has_nb ? (size_t)H * S * s_pad8 * 2 : 0;
+    const size_t v_bytes = std::max(x_bytes, (size_t)B * C * s_pad8 * es);   // v may be stored key-major with padded rows
+    if (!rt.reserve_workspace(4 * (x_bytes + 256) + v_bytes + 256 + nb_pad_bytes + 256)) return;
 
     DeviceArg d_x = resolve_in(input.data_ptr(), x_bytes);
     DeviceArg d_bias = resolve_in(bias.data_ptr(), bias_bytes);
@@ -82,7 +85,7 @@ static void gating_attention_impl(Tensor &input, int64_t batch, int64_t seq_len,
               d_wo = resolve_in(output_w.data_ptr(), w_bytes);
     DeviceArg d_bg = resolve_in(gating_b.data_ptr(), b_bytes), d_bo = resolve_in(output_b.data_ptr(), b_bytes);
     DeviceArg d_out = resolve_out(out.data_ptr(), out_bytes);
-    void *wq_ = rt.take_workspace(x_bytes), *wk_ = rt.take_workspace(x_bytes), *wv_ = rt.take_workspace(x_bytes),
+    void *wq_ = rt.take_workspace(x_bytes), *wk_ = rt.take_workspace(x_bytes), *wv_ = rt.take_workspace(v_bytes),
          *wg_ = rt.take_workspace(x_bytes), *wavg = rt.take_workspace(x_bytes);
     void *nb_pad = nb_pad_bytes ? rt.take_workspace(nb_pad_bytes) : nullptr;
     if (kutacc_check_err_set) return;
@@ -100,7 +103,7 @@ static void gating_attention_impl(Tensor &input, int64_t batch, int64_t seq_len,
         const void *nb_dev = has_nb ? d_nb.dev : nullptr;
         int64_t nb_sh = nb_s0, nb_sq = nb_s1;
         if (has_nb && ((nb_s0 % 8) || (nb_s1 % 8) || !aligned16(d_nb.dev))) {
-            const int64_t s_pad = (S + 7) / 8 * 8;
+            const int64_t s_pad = s_pad8;
             KUTACC_CUDA(cudaMemcpy2DAsync(nb_pad, (size_t)s_pad * 2, d_nb.dev, (size_t)nb_s1 * 2, (size_t)S * 2,
                                           (size_t)(nb_s0 == S * nb_s1 ? H * S : S), cudaMemcpyDeviceToDevice, stream));
             for (int64_t hh = 1; nb_s0 != S * nb_s1 && hh < H; ++hh)
@@ -111,14 +114,29 @@ static void gating_attention_impl(Tensor &input, int64_t batch, int64_t seq_len,
             nb_sq = s_pad;
             nb_sh = S * s_pad;
         }
-        // tensor-memory GEMM where the shape allows it, warp-level MMA otherwise
-        ok = dev::tcgen05_proj_qkvg_bf16(stream, d_x.dev, d_wq.dev, d_wk.dev, d_wv.dev, d_wg.dev,
-                                         (const float *)d_bg.dev, wq_, wk_, wv_, wg_, (int)B, (int)S, (int)H, (int)D) ||
-             dev::launch_proj_qkvg_bf16(stream, d_x.dev, d_wq.dev, d_wk.dev, d_wv.dev, d_wg.dev,
-                                        (const float *)d_bg.dev, wq_, wk_, wv_, wg_, (int)B, (int)S, (int)H, (int)D,
-                                        1.0f);
-        ok = ok && dev::launch_attn_core_bf16(stream, wq_, wk_, wv_, wg_, d_bias.dev, bias_s0, nb_dev, nb_sh, nb_sq,
-                                              wavg, (int)B, (int)S, (int)H, (int)D, scale);
+        // Tensor-memory kernels where the shape allows it (head size 32: projection with v stored
+        // key-major plus the tcgen05 attention core), warp-level MMA kernels otherwise.
+        bool v_key_major = false;
+        ok = false;
+        if (D == 32) {
+            ok = dev::tcgen05_proj_qkvg_bf16(stream, d_x.dev, d_wq.dev, d_wk.dev, d_wv.dev, d_wg.dev,
+                                             (const float *)d_bg.dev, wq_, wk_, wv_, wg_, (int)B, (int)S, (int)H,
+                                             (int)D, true, s_pad8);
+            v_key_major = ok;
+        }
+        if (!ok)
+            ok = dev::tcgen05_proj_qkvg_bf16(stream, d_x.dev, d_wq.dev, d_wk.dev, d_wv.dev, d_wg.dev,
+                                             (const float *)d_bg.dev, wq_, wk_, wv_, wg_, (int)B, (int)S, (int)H,
+                                             (int)D, false, 0) ||
+                 dev::launch_proj_qkvg_bf16(stream, d_x.dev, d_wq.dev, d_wk.dev, d_wv.dev, d_wg.dev,
+                                            (const float *)d_bg.dev, wq_, wk_, wv_, wg_, (int)B, (int)S, (int)H,
+                                            (int)D, 1.0f);
+        if (ok && v_key_major)
+            ok = dev::tcgen05_attn_core_bf16(stream, wq_, wk_, wv_, s_pad8, wg_, d_bias.dev, bias_s0, nb_dev, nb_sh,
+                                             nb_sq, wavg, (int)B, (int)S, (int)H, (int)D, scale);
+        else
+            ok = ok && dev::launch_attn_core_bf16(stream, wq_, wk_, wv_, wg_, d_bias.dev, bias_s0, nb_dev, nb_sh,
+                                                  nb_sq, wavg, (int)B, (int)S, (int)H, (int)D, scale);
         ok = ok && (dev::tcgen05_linear_bias_bf16(stream, wavg, d_wo.dev, (const float *)d_bo.dev, d_out.dev, out_rs,
                                                   (int)B, (int)S, (int)C, (int)C) ||
                     dev::launch_linear_bias_bf16(stream, wavg, C, d_wo.dev, (const float *)d_bo.dev, d_out.dev, out_rs,

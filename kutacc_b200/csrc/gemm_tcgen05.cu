@@ -26,6 +26,7 @@
 #include "common.h"
 #include "kernels.h"
 #include "ptx_utils.cuh"
+#include "tcgen05_utils.cuh"
 #include "tma_utils.cuh"
 
 #include <algorithm>
@@ -62,60 +63,12 @@ struct GemmParams {
     int nseg;
     int head_dim;           // > 0: segment output is [B*H][S][D] (coords d, s, b*H + h); 0: [B][S][N_seg]
     int head_layout_mask;   // bit i set: segment i uses the head layout
+    int transposed_mask;    // bit i set: segment i is stored transposed, [B*H][D][S] (coords s, d, b*H + h)
     int heads;
     int K;
     int S, B;
     int *err;
 };
-
-// ---- tcgen05 wrappers ------------------------------------------------------------------------------
-__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols)
-{
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_dst), "r"(ncols)
-                 : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish()
-{
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols)
-{
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(taddr), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar)
-{
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
-}
-// D[tmem] (+)= A[smem] * B[smem], bf16 inputs, fp32 accumulate, shape from idesc
-__device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                            uint32_t accumulate)
-{
-    asm volatile(
-        "{\n"
-        ".reg .pred p;\n"
-        "setp.ne.b32 p, %4, 0;\n"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
-        "}\n" ::"r"(d_tmem),
-        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-// this warp's 32 lanes x 32 consecutive fp32 columns
-__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
-{
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,"
-        "%29,%30,%31}, [%32];\n"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
 
 // shared-memory matrix descriptor: K-major operand, rows of 128 bytes, 128-byte swizzle, 8-row groups
 // 1024 bytes apart; `addr` is the byte address of the (1024-aligned) slab plus the K offset inside the
@@ -203,7 +156,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p)
         bool ok = true;
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
             const int a = tcount % ACC_STAGES;
-            if (tcount >= ACC_STAGES && !mbar_wait(acc_empty(a), (uint32_t)((tcount / ACC_STAGES - 1) & 1), p.err, 12)) {
+            if (tcount >= ACC_STAGES && !mbar_wait_warp(acc_empty(a), (uint32_t)((tcount / ACC_STAGES - 1) & 1), p.err, 12)) {
                 ok = false;
                 break;
             }
@@ -211,7 +164,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p)
             const uint32_t d_tmem = tmem_base + (uint32_t)(a * BN);
             for (int kc = 0; kc < nk; ++kc, ++it) {
                 const int s = it % NSTAGE;
-                if (!mbar_wait(full_bar(s), (uint32_t)((it / NSTAGE) & 1), p.err, 13)) {
+                if (!mbar_wait_warp(full_bar(s), (uint32_t)((it / NSTAGE) & 1), p.err, 13)) {
                     ok = false;
                     break;
                 }
@@ -243,13 +196,14 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p)
             const int b = m_tile / s_tiles, s0 = (m_tile % s_tiles) * BM;
             const int seg = n_tile / n_tiles_seg, n0 = (n_tile % n_tiles_seg) * BN;
             const int a = tcount % ACC_STAGES;
-            if (!mbar_wait(acc_full(a), (uint32_t)((tcount / ACC_STAGES) & 1), p.err, 14)) {
+            if (!mbar_wait_warp(acc_full(a), (uint32_t)((tcount / ACC_STAGES) & 1), p.err, 14)) {
                 ok = false;
                 break;
             }
             tc_fence_after();
             const float *bias = p.bias[seg];
             const bool head_layout = (p.head_layout_mask >> seg) & 1;
+            const bool transposed = (p.transposed_mask >> seg) & 1;
             const CUtensorMap *omap = &maps.out[seg];
             const int row0 = s0 + quad * 32;                  // first row of this warp inside the batch row
             uint32_t r[2][32];
@@ -280,6 +234,28 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p)
                 if (nstore >= STG_PER_WARP) {
                     if (lane == 0) tma_store_wait_read<STG_PER_WARP - 1>();
                     __syncwarp();
+                }
+                if (transposed) {
+                    // transposed staging tile: row = channel d, column = this lane's sequence position
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) {
+                            const int d = 2 * j + e;
+                            const uint32_t addr = stg + (uint32_t)(d * 64 + (((lane >> 3) ^ ((d >> 1) & 3)) << 4) + (lane & 7) * 2);
+                            const uint16_t hv = (uint16_t)(e ? (packed[j] >> 16) : (packed[j] & 0xffffu));
+                            asm volatile("st.shared.u16 [%0], %1;\n" ::"r"(addr), "h"(hv) : "memory");
+                        }
+                    }
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0) {
+                        const int hh = n / p.head_dim, d0 = n - hh * p.head_dim;
+                        tma_store_3d(omap, stg, row0, d0, b * p.heads + hh);
+                        tma_store_commit();
+                    }
+                    ++nstore;
+                    continue;
                 }
 #pragma unroll
                 for (int ch = 0; ch < 4; ++ch) {
@@ -349,7 +325,7 @@ bool launch(cudaStream_t stream, const GemmMaps &maps, const GemmParams &p, cons
 
 bool tcgen05_proj_qkvg_bf16(cudaStream_t stream, const void *x, const void *wq, const void *wk, const void *wv,
                             const void *wg, const float *bg, void *q, void *k, void *v, void *gate, int B, int S,
-                            int H, int D)
+                            int H, int D, bool v_transposed, int64_t v_pitch)
 {
     const int C = H * D;
     if (C % 128 != 0 || (D != 32 && D != 64) || C > 256 * 64 || ((uintptr_t)bg & 15u)) return false;
@@ -361,9 +337,18 @@ bool tcgen05_proj_qkvg_bf16(cudaStream_t stream, const void *x, const void *wq, 
     if (!make_tensor_map_bf16_3d(&maps.a, x, C, S, B, C, (uint64_t)S * C, BK, BM, 128)) return false;
     for (int i = 0; i < 4; ++i)
         if (!make_tensor_map_bf16_3d(&maps.w[i], w[i], C, C, 1, C, (uint64_t)C * C, BK, BN, 128)) return false;
-    for (int i = 0; i < 3; ++i)
+    for (int i = 0; i < 3; ++i) {
+        if (i == 2 && v_transposed) {
+            // v^T: [B*H][D][S] with row pitch v_pitch (a multiple of 8 elements)
+            if (v_pitch % 8 != 0 || v_pitch < S) return false;
+            if (!make_tensor_map_bf16_3d(&maps.out[i], o[i], S, D, (uint64_t)B * H, (uint64_t)v_pitch,
+                                         (uint64_t)D * v_pitch, 32, 32, 64))
+                return false;
+            continue;
+        }
         if (!make_tensor_map_bf16_3d(&maps.out[i], o[i], D, S, (uint64_t)B * H, D, (uint64_t)S * D, 32, 32, 64))
             return false;
+    }
     if (!make_tensor_map_bf16_3d(&maps.out[3], gate, C, S, B, C, (uint64_t)S * C, 32, 32, 64)) return false;
     GemmParams p;
     p.bias[0] = p.bias[1] = p.bias[2] = nullptr;
@@ -372,6 +357,7 @@ bool tcgen05_proj_qkvg_bf16(cudaStream_t stream, const void *x, const void *wq, 
     p.nseg = 4;
     p.head_dim = D;
     p.head_layout_mask = 0x7;
+    p.transposed_mask = v_transposed ? 0x4 : 0;
     p.heads = H;
     p.K = C;
     p.S = S;
@@ -405,6 +391,7 @@ bool tcgen05_linear_bias_bf16(cudaStream_t stream, const void *a, const void *w,
     p.nseg = 1;
     p.head_dim = 0;
     p.head_layout_mask = 0;
+    p.transposed_mask = 0;
     p.heads = 1;
     p.K = K;
     p.S = S;

@@ -24,10 +24,12 @@ bool launch_linear_bias_bf16(cudaStream_t stream, const void *a, int64_t lda, co
                              void *out, int64_t ldo, int64_t M, int N, int K);
 
 // tcgen05/TMEM/TMA versions of the two GEMMs above (C % 128 == 0, D in {32, 64}; N % 128 == 0,
-// K % 64 == 0, out row stride % 8 == 0). q is written unscaled. Return false when the shape is not covered.
+// K % 64 == 0, out row stride % 8 == 0). q is written unscaled. With v_transposed, v is written as
+// [B, H, D, S] with row pitch v_pitch (what the tcgen05 attention core consumes) instead of [B, H, S, D].
+// Return false when the shape is not covered.
 bool tcgen05_proj_qkvg_bf16(cudaStream_t stream, const void *x, const void *wq, const void *wk, const void *wv,
                             const void *wg, const float *bg, void *q, void *k, void *v, void *gate, int B, int S,
-                            int H, int D);
+                            int H, int D, bool v_transposed, int64_t v_pitch);
 bool tcgen05_linear_bias_bf16(cudaStream_t stream, const void *a, const void *w, const float *bias, void *out,
                               int64_t out_row_stride, int B, int S, int N, int K);
 
@@ -38,6 +40,13 @@ bool tcgen05_linear_bias_bf16(cudaStream_t stream, const void *a, const void *w,
 bool launch_attn_core_bf16(cudaStream_t stream, const void *q, const void *k, const void *v, const void *gate,
                            const void *bias, int64_t bias_stride0, const void *nb, int64_t nb_stride_h,
                            int64_t nb_stride_q, void *avg, int B, int S, int H, int D, float scale);
+
+// The same operator with both products on tcgen05 and the accumulators in tensor memory (head size 32).
+// vt is v transposed, [B, H, D, S] with row pitch vt_pitch, as tcgen05_proj_qkvg_bf16 writes it.
+bool tcgen05_attn_core_bf16(cudaStream_t stream, const void *q, const void *k, const void *vt, int64_t vt_pitch,
+                            const void *gate, const void *bias, int64_t bias_stride0, const void *nb,
+                            int64_t nb_stride_h, int64_t nb_stride_q, void *avg, int B, int S, int H, int D,
+                            float scale);
 
 // ---- generic (any shape, bf16 or fp32 storage, fp32 math) ------------------------------------------
 // c[m, n] = sum_k a[m, k] * w[n, k] (+ bias[n]) (+ beta * c[m, n]); a row stride lda, w row stride

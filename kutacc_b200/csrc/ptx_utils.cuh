@@ -51,6 +51,21 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi)
     asm("cvt.rn.bf16x2.f32 %0, %1, %2;\n" : "=r"(r) : "f"(hi), "f"(lo));
     return r;
 }
+// fp32 value of x rounded to bf16 (round to nearest even): packing x with 0 leaves bf16(x) in the upper
+// half-word, which is exactly that value's fp32 bit pattern
+__device__ __forceinline__ float round_to_bf16_f32(float x)
+{
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;\n" : "=r"(r) : "f"(x), "f"(0.0f));
+    return __uint_as_float(r);
+}
+// three-input maximum (sm_100)
+__device__ __forceinline__ float fmax3(float a, float b, float c)
+{
+    float d;
+    asm("max.f32 %0, %1, %2, %3;\n" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
 __device__ __forceinline__ float bf16lo_to_f32(uint32_t v) { return __uint_as_float(v << 16); }
 __device__ __forceinline__ float bf16hi_to_f32(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
 

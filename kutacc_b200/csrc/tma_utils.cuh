@@ -73,6 +73,15 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int *er
     return true;
 }
 
+// The same wait for a whole warp. Lanes can leave the polling loop at different iterations; the vote at
+// the end brings the warp back together (instructions such as tcgen05.ld, ldmatrix and mma.sync are
+// .aligned and must be issued by a converged warp) and makes the result uniform.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, int *err, int code)
+{
+    const bool ok = mbar_wait(bar, parity, err, code);
+    return __all_sync(0xffffffffu, ok);
+}
+
 // ---- device: TMA -----------------------------------------------------------------------------------
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap *map)
 {
