@@ -110,4 +110,13 @@ DeviceArg resolve_out(void *p, size_t bytes);                          // no cop
 void finish_out(const DeviceArg &a);                                    // device -> host when staged
 void end_of_call();                                                    // stream sync unless async
 
+// Two extra non-blocking streams and a pool of events for calls that overlap host<->device copies with
+// compute on the runtime stream (created on first use, reused afterwards).
+struct CopyPipeline {
+    void *in = nullptr, *out = nullptr;       // cudaStream_t
+    void *start = nullptr;                    // cudaEvent_t
+    std::vector<void *> uploaded, computed;   // cudaEvent_t per chunk
+};
+CopyPipeline &copy_pipeline(int nchunks);
+
 }  // namespace kutacc

@@ -77,7 +77,14 @@ static void gating_attention_impl(Tensor &input, int64_t batch, int64_t seq_len,
     const size_t v_bytes = std::max(x_bytes, (size_t)B * C * s_pad8 * es);   // v may be stored key-major with padded rows
     if (!rt.reserve_workspace(4 * (x_bytes + 256) + v_bytes + 256 + nb_pad_bytes + 256)) return;
 
-    DeviceArg d_x = resolve_in(input.data_ptr(), x_bytes);
+    // When both the activations and the result live in host memory, the batch rows (independent problems)
+    // are processed in chunks so that the upload of chunk i+1, the kernels of chunk i and the download of
+    // chunk i-1 overlap on three streams. Otherwise the call is a single chunk on the runtime stream.
+    const bool x_host = staged_bytes_needed(input.data_ptr(), x_bytes) != 0;
+    const bool out_host = staged_bytes_needed(out.data_ptr(), out_bytes) != 0;
+    const bool pipelined = x_host && out_host && B >= 8 && x_bytes >= ((size_t)4 << 20);
+
+    DeviceArg d_x = pipelined ? resolve_out(input.data_ptr(), x_bytes) : resolve_in(input.data_ptr(), x_bytes);
     DeviceArg d_bias = resolve_in(bias.data_ptr(), bias_bytes);
     DeviceArg d_nb = has_nb ? resolve_in(nonbatched_bias.data_ptr(), nb_bytes) : DeviceArg{};
     DeviceArg d_wq = resolve_in(query_w.data_ptr(), w_bytes), d_wk = resolve_in(key_w.data_ptr(), w_bytes),
@@ -85,8 +92,9 @@ static void gating_attention_impl(Tensor &input, int64_t batch, int64_t seq_len,
               d_wo = resolve_in(output_w.data_ptr(), w_bytes);
     DeviceArg d_bg = resolve_in(gating_b.data_ptr(), b_bytes), d_bo = resolve_in(output_b.data_ptr(), b_bytes);
     DeviceArg d_out = resolve_out(out.data_ptr(), out_bytes);
-    void *wq_ = rt.take_workspace(x_bytes), *wk_ = rt.take_workspace(x_bytes), *wv_ = rt.take_workspace(v_bytes),
-         *wg_ = rt.take_workspace(x_bytes), *wavg = rt.take_workspace(x_bytes);
+    char *wq_ = (char *)rt.take_workspace(x_bytes), *wk_ = (char *)rt.take_workspace(x_bytes),
+         *wv_ = (char *)rt.take_workspace(v_bytes), *wg_ = (char *)rt.take_workspace(x_bytes),
+         *wavg = (char *)rt.take_workspace(x_bytes);
     void *nb_pad = nb_pad_bytes ? rt.take_workspace(nb_pad_bytes) : nullptr;
     if (kutacc_check_err_set) return;
 
@@ -96,66 +104,113 @@ static void gating_attention_impl(Tensor &input, int64_t batch, int64_t seq_len,
                       aligned16(d_x.dev) && aligned16(d_wq.dev) && aligned16(d_wk.dev) && aligned16(d_wv.dev) &&
                       aligned16(d_wg.dev) && aligned16(d_wo.dev) && (out_rs % 2 == 0) &&
                       (((uintptr_t)d_out.dev & 3u) == 0);
-    bool ok;
-    if (fast) {
-        // The TMA loads of the pair bias need 16-byte aligned rows. A pair bias whose strides are not
-        // multiples of 8 elements is first copied into the workspace with padded rows.
-        const void *nb_dev = has_nb ? d_nb.dev : nullptr;
-        int64_t nb_sh = nb_s0, nb_sq = nb_s1;
-        if (has_nb && ((nb_s0 % 8) || (nb_s1 % 8) || !aligned16(d_nb.dev))) {
-            const int64_t s_pad = s_pad8;
-            KUTACC_CUDA(cudaMemcpy2DAsync(nb_pad, (size_t)s_pad * 2, d_nb.dev, (size_t)nb_s1 * 2, (size_t)S * 2,
-                                          (size_t)(nb_s0 == S * nb_s1 ? H * S : S), cudaMemcpyDeviceToDevice, stream));
-            for (int64_t hh = 1; nb_s0 != S * nb_s1 && hh < H; ++hh)
-                KUTACC_CUDA(cudaMemcpy2DAsync((char *)nb_pad + (size_t)hh * S * s_pad * 2, (size_t)s_pad * 2,
-                                              (const char *)d_nb.dev + (size_t)hh * nb_s0 * 2, (size_t)nb_s1 * 2,
-                                              (size_t)S * 2, (size_t)S, cudaMemcpyDeviceToDevice, stream));
-            nb_dev = nb_pad;
-            nb_sq = s_pad;
-            nb_sh = S * s_pad;
+
+    // The TMA loads of the pair bias need 16-byte aligned rows. A pair bias whose strides are not
+    // multiples of 8 elements is first copied into the workspace with padded rows.
+    const void *nb_dev = has_nb ? d_nb.dev : nullptr;
+    int64_t nb_sh = nb_s0, nb_sq = nb_s1;
+    if (fast && has_nb && ((nb_s0 % 8) || (nb_s1 % 8) || !aligned16(d_nb.dev))) {
+        KUTACC_CUDA(cudaMemcpy2DAsync(nb_pad, (size_t)s_pad8 * 2, d_nb.dev, (size_t)nb_s1 * 2, (size_t)S * 2,
+                                      (size_t)(nb_s0 == S * nb_s1 ? H * S : S), cudaMemcpyDeviceToDevice, stream));
+        for (int64_t hh = 1; nb_s0 != S * nb_s1 && hh < H; ++hh)
+            KUTACC_CUDA(cudaMemcpy2DAsync((char *)nb_pad + (size_t)hh * S * s_pad8 * 2, (size_t)s_pad8 * 2,
+                                          (const char *)d_nb.dev + (size_t)hh * nb_s0 * 2, (size_t)nb_s1 * 2,
+                                          (size_t)S * 2, (size_t)S, cudaMemcpyDeviceToDevice, stream));
+        nb_dev = nb_pad;
+        nb_sq = s_pad8;
+        nb_sh = S * s_pad8;
+    }
+
+    // kernel sequence for batch rows [b0, b0 + nb): every buffer is batch-major, so a chunk is an offset
+    auto run_rows = [&](int64_t b0, int64_t nbr) -> bool {
+        const size_t row_bytes = (size_t)S * C * es;                       // one batch row of a [B, S, C]-sized buffer
+        const char *x_c = (const char *)d_x.dev + b0 * row_bytes;
+        char *q_c = wq_ + b0 * row_bytes, *k_c = wk_ + b0 * row_bytes, *g_c = wg_ + b0 * row_bytes,
+             *a_c = wavg + b0 * row_bytes;
+        const char *bias_c = (const char *)d_bias.dev + (size_t)b0 * bias_s0 * es;
+        char *out_c = (char *)d_out.dev + (size_t)b0 * S * out_rs * es;
+        const int64_t Mc = nbr * S;
+        bool ok;
+        if (fast) {
+            // Tensor-memory kernels where the shape allows it (head size 32: projection with v stored
+            // key-major plus the tcgen05 attention core), warp-level MMA kernels otherwise.
+            char *v_km = wv_ + (size_t)b0 * C * s_pad8 * es;                   // key-major v: [B, H, D, s_pad8]
+            char *v_c = wv_ + b0 * row_bytes;                                  // [B, H, S, D]
+            bool v_key_major = false;
+            ok = false;
+            if (D == 32) {
+                ok = dev::tcgen05_proj_qkvg_bf16(stream, x_c, d_wq.dev, d_wk.dev, d_wv.dev, d_wg.dev,
+                                                 (const float *)d_bg.dev, q_c, k_c, v_km, g_c, (int)nbr, (int)S, (int)H,
+                                                 (int)D, true, s_pad8);
+                v_key_major = ok;
+            }
+            if (!ok)
+                ok = dev::tcgen05_proj_qkvg_bf16(stream, x_c, d_wq.dev, d_wk.dev, d_wv.dev, d_wg.dev,
+                                                 (const float *)d_bg.dev, q_c, k_c, v_c, g_c, (int)nbr, (int)S, (int)H,
+                                                 (int)D, false, 0) ||
+                     dev::launch_proj_qkvg_bf16(stream, x_c, d_wq.dev, d_wk.dev, d_wv.dev, d_wg.dev,
+                                                (const float *)d_bg.dev, q_c, k_c, v_c, g_c, (int)nbr, (int)S, (int)H,
+                                                (int)D, 1.0f);
+            if (ok && v_key_major)
+                ok = dev::tcgen05_attn_core_bf16(stream, q_c, k_c, v_km, s_pad8, g_c, bias_c, bias_s0, nb_dev, nb_sh,
+                                                 nb_sq, a_c, (int)nbr, (int)S, (int)H, (int)D, scale);
+            else
+                ok = ok && dev::launch_attn_core_bf16(stream, q_c, k_c, v_c, g_c, bias_c, bias_s0, nb_dev, nb_sh, nb_sq,
+                                                      a_c, (int)nbr, (int)S, (int)H, (int)D, scale);
+            ok = ok && (dev::tcgen05_linear_bias_bf16(stream, a_c, d_wo.dev, (const float *)d_bo.dev, out_c, out_rs,
+                                                      (int)nbr, (int)S, (int)C, (int)C) ||
+                        dev::launch_linear_bias_bf16(stream, a_c, C, d_wo.dev, (const float *)d_bo.dev, out_c, out_rs,
+                                                     Mc, (int)C, (int)C));
+        } else {
+            const dev::ElemType et = dt == kFP32 ? dev::kElemF32 : dev::kElemBF16;
+            char *v_c = wv_ + b0 * row_bytes;
+            ok = dev::launch_gemm_generic(stream, et, x_c, C, d_wq.dev, C, nullptr, 0.f, q_c, C, Mc, C, C);
+            ok = ok && dev::launch_gemm_generic(stream, et, x_c, C, d_wk.dev, C, nullptr, 0.f, k_c, C, Mc, C, C);
+            ok = ok && dev::launch_gemm_generic(stream, et, x_c, C, d_wv.dev, C, nullptr, 0.f, v_c, C, Mc, C, C);
+            ok = ok && dev::launch_gemm_generic(stream, et, x_c, C, d_wg.dev, C, (const float *)d_bg.dev, 0.f, g_c, C,
+                                                Mc, C, C);
+            ok = ok && dev::launch_attn_generic(stream, et, q_c, k_c, v_c, g_c, bias_c, bias_s0,
+                                                has_nb ? d_nb.dev : nullptr, nb_s0, nb_s1, a_c, (int)nbr, (int)S, (int)H,
+                                                (int)D, scale);
+            ok = ok && dev::launch_gemm_generic(stream, et, a_c, C, d_wo.dev, C, (const float *)d_bo.dev, 0.f, out_c,
+                                                out_rs, Mc, C, C);
         }
-        // Tensor-memory kernels where the shape allows it (head size 32: projection with v stored
-        // key-major plus the tcgen05 attention core), warp-level MMA kernels otherwise.
-        bool v_key_major = false;
-        ok = false;
-        if (D == 32) {
-            ok = dev::tcgen05_proj_qkvg_bf16(stream, d_x.dev, d_wq.dev, d_wk.dev, d_wv.dev, d_wg.dev,
-                                             (const float *)d_bg.dev, wq_, wk_, wv_, wg_, (int)B, (int)S, (int)H,
-                                             (int)D, true, s_pad8);
-            v_key_major = ok;
-        }
-        if (!ok)
-            ok = dev::tcgen05_proj_qkvg_bf16(stream, d_x.dev, d_wq.dev, d_wk.dev, d_wv.dev, d_wg.dev,
-                                             (const float *)d_bg.dev, wq_, wk_, wv_, wg_, (int)B, (int)S, (int)H,
-                                             (int)D, false, 0) ||
-                 dev::launch_proj_qkvg_bf16(stream, d_x.dev, d_wq.dev, d_wk.dev, d_wv.dev, d_wg.dev,
-                                            (const float *)d_bg.dev, wq_, wk_, wv_, wg_, (int)B, (int)S, (int)H,
-                                            (int)D, 1.0f);
-        if (ok && v_key_major)
-            ok = dev::tcgen05_attn_core_bf16(stream, wq_, wk_, wv_, s_pad8, wg_, d_bias.dev, bias_s0, nb_dev, nb_sh,
-                                             nb_sq, wavg, (int)B, (int)S, (int)H, (int)D, scale);
-        else
-            ok = ok && dev::launch_attn_core_bf16(stream, wq_, wk_, wv_, wg_, d_bias.dev, bias_s0, nb_dev, nb_sh,
-                                                  nb_sq, wavg, (int)B, (int)S, (int)H, (int)D, scale);
-        ok = ok && (dev::tcgen05_linear_bias_bf16(stream, wavg, d_wo.dev, (const float *)d_bo.dev, d_out.dev, out_rs,
-                                                  (int)B, (int)S, (int)C, (int)C) ||
-                    dev::launch_linear_bias_bf16(stream, wavg, C, d_wo.dev, (const float *)d_bo.dev, d_out.dev, out_rs,
-                                                 M, (int)C, (int)C));
+        return ok;
+    };
+
+    bool ok = true;
+    if (!pipelined) {
+        ok = run_rows(0, B);
+        finish_out(d_out);
     } else {
-        const dev::ElemType et = dt == kFP32 ? dev::kElemF32 : dev::kElemBF16;
-        ok = dev::launch_gemm_generic(stream, et, d_x.dev, C, d_wq.dev, C, nullptr, 0.f, wq_, C, M, C, C);
-        ok = ok && dev::launch_gemm_generic(stream, et, d_x.dev, C, d_wk.dev, C, nullptr, 0.f, wk_, C, M, C, C);
-        ok = ok && dev::launch_gemm_generic(stream, et, d_x.dev, C, d_wv.dev, C, nullptr, 0.f, wv_, C, M, C, C);
-        ok = ok && dev::launch_gemm_generic(stream, et, d_x.dev, C, d_wg.dev, C, (const float *)d_bg.dev, 0.f, wg_, C,
-                                            M, C, C);
-        ok = ok && dev::launch_attn_generic(stream, et, wq_, wk_, wv_, wg_, d_bias.dev, bias_s0,
-                                            has_nb ? d_nb.dev : nullptr, nb_s0, nb_s1, wavg, (int)B, (int)S, (int)H,
-                                            (int)D, scale);
-        ok = ok && dev::launch_gemm_generic(stream, et, wavg, C, d_wo.dev, C, (const float *)d_bo.dev, 0.f, d_out.dev,
-                                            out_rs, M, C, C);
+        const int nchunks = (int)std::min<int64_t>(8, B / 4);
+        const int64_t rows_per_chunk = (B + nchunks - 1) / nchunks;
+        CopyPipeline &cp = copy_pipeline(nchunks);
+        if (kutacc_check_err_set) return;
+        cudaStream_t s_in = (cudaStream_t)cp.in, s_out = (cudaStream_t)cp.out;
+        // uploads must not start before the staging buffers are free of the previous call's work
+        KUTACC_CUDA(cudaEventRecord((cudaEvent_t)cp.start, stream));
+        KUTACC_CUDA(cudaStreamWaitEvent(s_in, (cudaEvent_t)cp.start, 0));
+        KUTACC_CUDA(cudaStreamWaitEvent(s_out, (cudaEvent_t)cp.start, 0));
+        const size_t row_bytes = (size_t)S * C * es;
+        for (int i = 0; i < nchunks && ok; ++i) {
+            const int64_t b0 = i * rows_per_chunk, nbr = std::min(rows_per_chunk, B - b0);
+            if (nbr <= 0) break;
+            KUTACC_CUDA(cudaMemcpyAsync((char *)d_x.dev + b0 * row_bytes, (const char *)input.data_ptr() + b0 * row_bytes,
+                                        (size_t)nbr * row_bytes, cudaMemcpyHostToDevice, s_in));
+            KUTACC_CUDA(cudaEventRecord((cudaEvent_t)cp.uploaded[i], s_in));
+            KUTACC_CUDA(cudaStreamWaitEvent(stream, (cudaEvent_t)cp.uploaded[i], 0));
+            ok = run_rows(b0, nbr);
+            KUTACC_CUDA(cudaEventRecord((cudaEvent_t)cp.computed[i], stream));
+            KUTACC_CUDA(cudaStreamWaitEvent(s_out, (cudaEvent_t)cp.computed[i], 0));
+            const size_t o_off = (size_t)b0 * S * out_rs * es;
+            const size_t o_len = std::min(out_bytes - o_off, (size_t)nbr * S * out_rs * es);
+            KUTACC_CUDA(cudaMemcpyAsync((char *)out.data_ptr() + o_off, (const char *)d_out.dev + o_off, o_len,
+                                        cudaMemcpyDeviceToHost, s_out));
+        }
+        KUTACC_CUDA(cudaStreamSynchronize(s_out));
     }
     KUTACC_CHECK(ok, "gating_attention: no device kernel for this shape (B=", B, " S=", S, " H=", H, " D=", D, ")");
-    finish_out(d_out);
     end_of_call();
 }
 

@@ -151,6 +151,29 @@ void finish_out(const DeviceArg &a)
         KUTACC_CUDA(cudaMemcpyAsync(a.host, a.dev, a.bytes, cudaMemcpyDeviceToHost, (cudaStream_t)runtime().stream));
 }
 
+CopyPipeline &copy_pipeline(int nchunks)
+{
+    static CopyPipeline cp;
+    if (cp.in == nullptr) {
+        cudaStream_t a = nullptr, b = nullptr;
+        KUTACC_CUDA(cudaStreamCreateWithFlags(&a, cudaStreamNonBlocking));
+        KUTACC_CUDA(cudaStreamCreateWithFlags(&b, cudaStreamNonBlocking));
+        cudaEvent_t e = nullptr;
+        KUTACC_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+        cp.in = a;
+        cp.out = b;
+        cp.start = e;
+    }
+    while ((int)cp.uploaded.size() < nchunks) {
+        cudaEvent_t e1 = nullptr, e2 = nullptr;
+        KUTACC_CUDA(cudaEventCreateWithFlags(&e1, cudaEventDisableTiming));
+        KUTACC_CUDA(cudaEventCreateWithFlags(&e2, cudaEventDisableTiming));
+        cp.uploaded.push_back(e1);
+        cp.computed.push_back(e2);
+    }
+    return cp;
+}
+
 void end_of_call()
 {
     cudaError_t e = cudaGetLastError();

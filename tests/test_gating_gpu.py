@@ -72,6 +72,15 @@ def test_host_pointers_give_the_same_bits_as_device_pointers(kutacc_lib):
     assert np.array_equal(dev, host)
 
 
+def test_pipelined_host_path_matches_device_path(kutacc_lib):
+    # large enough (>= 8 batch rows, >= 4 MiB of activations) for the chunked upload/compute/download pipeline
+    w = W.random_gating_case(seed=8, B=35, S=256, H=8, D=32, with_nb=True, full_mask_rows=2)
+    dev = _run(w, device=True)
+    host = _run(w, device=False)
+    assert np.array_equal(dev, host)
+    assert np.array_equal(_run(w, device=False), host)       # staging buffers are reused across calls
+
+
 def test_strided_out_and_bias(kutacc_lib):
     # out row stride (strides[1]) and bias row stride (strides[0]) are honoured
     w = W.random_gating_case(seed=9, B=2, S=64, H=2, D=32, with_nb=False)
