@@ -214,12 +214,18 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         const float scale = p.scale;
         float m2 = -INFINITY;                            // running (possibly stale) max of this half, log2 units
         bool ok = true;
-        for (int kt = 0; kt < nkt && ok; ++kt) {
-            const int s = kt % NST;
-            if (!mbar_wait_warp(s_full, (uint32_t)(kt & 1), p.err, 26)) {
-                ok = false;
-                break;
-            }
+        // Per-thread shared-memory addresses, hoisted out of the tile loop. The ring is unrolled by stage
+        // below, so every stage offset is a compile-time constant added to these.
+        const uint32_t st0 = smem + OFF_STAGE;
+        uint32_t nb_addr[4];                             // this row's 4 swizzled 16-byte chunks (pair bias in, P out)
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+            nb_addr[c] = st0 + K_BYTES + VT_BYTES + (uint32_t)row * 128 + (uint32_t)(((half * 4 + c) ^ (row & 7)) << 4);
+        const uint32_t mb_addr = st0 + K_BYTES + VT_BYTES + NB_BYTES + half * 128;
+
+        // One tile of the softmax; `soff` is the byte offset of the ring stage (a constant after unrolling)
+        auto do_tile = [&](const int kt, const uint32_t soff, const uint32_t kv_full_bar, const uint32_t p_full_bar) -> bool {
+            if (!mbar_wait_warp(s_full, (uint32_t)(kt & 1), p.err, 26)) return false;
             tc_fence_after();
             uint32_t sr[32];
             tmem_ld_32x32(t_lane + S_COL + half * 32, sr);
@@ -227,25 +233,18 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(s_free);
-            if (!mbar_wait_warp(kv_full(s), (uint32_t)((kt / NST) & 1), p.err, 27)) {
-                ok = false;
-                break;
-            }
-            const uint32_t st = stage_base(s);
-            const uint32_t nb_row = st + K_BYTES + VT_BYTES + (uint32_t)row * 128;     // also this row of P
-            const uint32_t mb_base = st + K_BYTES + VT_BYTES + NB_BYTES + half * 128;
+            if (!mbar_wait_warp(kv_full_bar, (uint32_t)((kt / NST) & 1), p.err, 27)) return false;
 
-            // x = bf16(logit)*scale + bias (+ pair bias); max over this thread's 32 keys
+            // x = bf16(logit)*scale + bias (+ pair bias) for 8 keys; keeps x in sr and tracks the tile max
             float tmax = -INFINITY;
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {                // 8 keys per step
-                const float4 mb0 = lds128_f32(mb_base + c * 32), mb1 = lds128_f32(mb_base + c * 32 + 16);
+            auto x_chunk = [&](const int c) {
+                const float4 mb0 = lds128_f32(mb_addr + soff + c * 32), mb1 = lds128_f32(mb_addr + soff + c * 32 + 16);
                 const float mbv[8] = {mb0.x, mb0.y, mb0.z, mb0.w, mb1.x, mb1.y, mb1.z, mb1.w};
                 uint32_t nbw[4] = {0, 0, 0, 0};
                 if (HAS_NB) {
                     asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];\n"
                                  : "=r"(nbw[0]), "=r"(nbw[1]), "=r"(nbw[2]), "=r"(nbw[3])
-                                 : "r"(nb_row + (uint32_t)(((half * 4 + c) ^ (row & 7)) << 4)));
+                                 : "r"(nb_addr[c] + soff));
                 }
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
@@ -261,37 +260,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     sr[i0 + 1] = __float_as_uint(x1);
                     tmax = fmax3(tmax, x0, x1);
                 }
-            }
-            // a half whose keys all lie beyond S has no max yet: park it on a finite floor
-            const float t2 = tmax > -INFINITY ? tmax * kLog2e : -1e30f;
-            const bool grow = kt == 0 || t2 > m2 + kRescaleThreshold;
-            if (__any_sync(0xffffffffu, grow && kt > 0)) {
-                // rescale this row of O_half (and its row-sum column) to the new max; the previous tile's
-                // P.V^T must have retired first
-                if (!mbar_wait_warp(pv_done, (uint32_t)((kt - 1) & 1), p.err, 28)) {
-                    ok = false;
-                    break;
-                }
-                tc_fence_after();
-                const float f = grow ? ex2_approx(m2 - t2) : 1.0f;
-                uint32_t o[32];
-                tmem_ld_32x32(o_col, o);
-                uint32_t osum = tmem_ld_32x1(o_col + 32);
-                tmem_ld_wait();
-#pragma unroll
-                for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
-                osum = __float_as_uint(__uint_as_float(osum) * f);
-                tmem_st_32x32(o_col, o);
-                tmem_st_32x1(o_col + 32, osum);
-                tmem_st_wait();
-                tc_fence_before();
-            }
-            if (grow) m2 = t2;
-
-            // probabilities -> bf16 -> over this thread's pair-bias chunks (A operand of P.V^T)
-            const float mneg = -m2;
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
+            };
+            // P = exp2(x*log2e - m2) for 8 keys -> bf16 -> over this thread's pair-bias chunk (A operand of P.V^T)
+            auto p_chunk = [&](const int c, const float mneg) {
                 uint32_t w[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
@@ -300,14 +271,67 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     const float p1 = ex2_approx(fmaf(__uint_as_float(sr[i0 + 1]), kLog2e, mneg));
                     w[j] = pack_bf16x2(p0, p1);
                 }
-                asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};\n" ::"r"(nb_row + (uint32_t)(((half * 4 + c) ^ (row & 7)) << 4)),
-                             "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3])
+                asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};\n" ::"r"(nb_addr[c] + soff), "r"(w[0]), "r"(w[1]),
+                             "r"(w[2]), "r"(w[3])
                              : "memory");
+            };
+
+            if (kt == 0) {
+                // first tile: the max must be known before any probability is formed
+#pragma unroll
+                for (int c = 0; c < 4; ++c) x_chunk(c);
+                // a half whose keys all lie beyond S has no max yet: park it on a finite floor
+                m2 = tmax > -INFINITY ? tmax * kLog2e : -1e30f;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) p_chunk(c, -m2);
+            } else {
+                // later tiles: form the probabilities against the running max straight away, chunk by chunk,
+                // so that the exp (XU pipe) of one chunk overlaps the arithmetic of the next; the running max
+                // may be stale by up to 2^8, which cancels in the final division
+                const float mneg = -m2;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    x_chunk(c);
+                    p_chunk(c, mneg);
+                }
+                const float t2 = tmax > -INFINITY ? tmax * kLog2e : -1e30f;
+                const bool grow = t2 > m2 + kRescaleThreshold;
+                if (__any_sync(0xffffffffu, grow)) {
+                    // rare: the max of some row grew past the threshold. Rescale those rows of O_half (and
+                    // their row-sum column) and redo this tile's probabilities against the new max. The
+                    // previous tile's P.V^T must have retired first (this warp is at most one phase behind
+                    // pv_done here).
+                    if (!mbar_wait_warp(pv_done, (uint32_t)((kt - 1) & 1), p.err, 28)) return false;
+                    tc_fence_after();
+                    const float f = grow ? ex2_approx(m2 - t2) : 1.0f;
+                    uint32_t o[32];
+                    tmem_ld_32x32(o_col, o);
+                    uint32_t osum = tmem_ld_32x1(o_col + 32);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
+                    osum = __float_as_uint(__uint_as_float(osum) * f);
+                    tmem_st_32x32(o_col, o);
+                    tmem_st_32x1(o_col + 32, osum);
+                    tmem_st_wait();
+                    tc_fence_before();
+                    if (grow) m2 = t2;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) p_chunk(c, -m2);
+                }
             }
             fence_proxy_async();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(p_full(s));
+            if (lane == 0) mbar_arrive(p_full_bar);
+            return true;
+        };
+
+        for (int kt0 = 0; kt0 < nkt && ok; kt0 += NST) {
+#pragma unroll
+            for (int s = 0; s < NST; ++s) {
+                if (kt0 + s < nkt && ok) ok = do_tile(kt0 + s, (uint32_t)s * STAGE_BYTES, kv_full(s), p_full(s));
+            }
         }
 
         // ---- epilogue: merge the two key halves of each row, normalise, gate, store ----
