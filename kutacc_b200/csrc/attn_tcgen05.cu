@@ -1,37 +1,47 @@
 // Fused gated-attention core on the fifth-generation tensor cores (head size 32).
 //
-// One CTA owns (batch row b, head h, 128 queries); two CTAs share an SM. Both matrix products run on
-// tcgen05.mma with accumulators in tensor memory, issued by one elected lane; the softmax runs
-// one-thread-per-query-row on the logits read back with tcgen05.ld, so no shuffles are needed for the row
-// max and row sum. The S x S logits never leave the SM.
+// A work item is (batch row b, head h, 128 queries). The kernel is persistent: two CTAs per SM each walk
+// a strided list of items, and every pipeline below keeps running across item boundaries, so the loads
+// and the first Q.K^T of the next item overlap the epilogue of the current one. Both matrix products run
+// on tcgen05.mma with accumulators in tensor memory, issued by one elected lane; the softmax runs on the
+// logits read back with tcgen05.ld. The S x S logits never leave the SM.
 //
-//   warp 0     producer: TMA tile loads (hardware swizzle) of Q once, then per 64-key tile K [64 x 32],
-//              V^T [32 x 64] and the 128 x 64 pair-bias tile; its lanes also convert the tile's 64
-//              mask-bias values to fp32
+//   warp 0     producer: TMA tile loads (hardware swizzle) of Q (double-buffered across items) and, per
+//              64-key tile, K [64 x 32], V^T [32 x 64] and the 128 x 64 pair-bias tile into a 3-stage ring;
+//              its lanes also convert the tile's 64 mask-bias values to fp32
 //   warp 1     MMA issuer: S = Q.K^T (M 128, N 64, K 32) into TMEM columns 0..63; then two products
 //              O_h += P[:, 32h..32h+31] . V^T[:, 32h..32h+31]^T (M 128, N 48, K 32), h = 0, 1, into two
 //              separate TMEM accumulators. Row 32 of the V^T operand is all ones, so column 32 of each O_h
 //              accumulates the row sum of the bf16 probabilities for free
 //   warps 2-9  softmax: two threads per query row, one per 32-key half of every tile (split-key online
-//              softmax: each half keeps its own running max and its own accumulator, merged once at the
-//              end). A thread pulls its 32 logits out of TMEM (S is free for the next tile's Q.K^T once all
-//              have done so), rounds each raw logit to bf16 as the reference's logits scratch does
+//              softmax: each half keeps its own running max and its own accumulator, merged once per item).
+//              A thread pulls its 32 logits out of TMEM (S is free for the next Q.K^T once all have done
+//              so), rounds each raw logit to bf16 as the reference's logits scratch does
 //              (src/attention/gating_attention.cpp:97-101), forms x = logit*scale + bias + pair_bias in
 //              fp32 in the reference's order (:112-117), and writes P = exp(x - max) as bf16 over the
 //              pair-bias values it has just consumed (same row, same swizzled chunks), which is the A
-//              operand of P.V^T. O_h is rescaled in TMEM only when the max grows by more than 2^8 (a stale
-//              max cancels in the final division), so the correction is rare. Epilogue: the two halves are
-//              merged through shared memory, O / rowsum, bf16 (:128-133), sigmoid gate (:134-147),
-//              64-byte row stores.
+//              operand of P.V^T. After the first tile of an item P is formed against the running max
+//              chunk by chunk, so exp (XU pipe) overlaps the arithmetic; O_h is rescaled in TMEM and the
+//              tile redone only when the max grows by more than 2^8 (a stale max cancels in the final
+//              division). Item epilogue: each thread merges both halves for 16 of the 32 channels straight
+//              from TMEM (only the two running maxima cross through shared memory), O / rowsum, bf16
+//              (:128-133), sigmoid gate (:134-147), 32-byte row stores.
 //
 // Fully masked rows stay uniform as in the reference (fp32 absorption of the logit by the -1e9 bias).
-// All mbarrier waits are bounded; on a timeout the roles fall through to the common tail, tensor memory
-// is released, and the host-visible error word carries the site.
+//
+// mbarrier phases. A parity wait names "the current or the preceding phase", so every barrier here is
+// awaited by each of its waiters once per completion, in order; the one exception (pv_done on the rare
+// rescale path) is safe because that waiter is provably at most one phase behind. All waits are bounded;
+// on a timeout the roles fall through to the common tail, tensor memory is released, and the host-visible
+// error word carries the site.
 #include "common.h"
 #include "kernels.h"
 #include "ptx_utils.cuh"
 #include "tcgen05_utils.cuh"
 #include "tma_utils.cuh"
+
+#include <algorithm>
+#include <climits>
 
 namespace kutacc {
 namespace dev {
@@ -40,24 +50,25 @@ namespace {
 
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr int D = 32;                 // head size
-constexpr int BM = 128;               // queries per CTA
+constexpr int BM = 128;               // queries per item
 constexpr int BN = 64;                // keys per tile
 constexpr int NST = 3;                // ring depth
 constexpr int VT_ROWS = 48;           // 32 channels + the ones row + zero padding to a multiple of 16
-constexpr int Q_BYTES = BM * D * 2;           // 8 KB, 64-byte rows, 64-byte swizzle
+constexpr int Q_BYTES = BM * D * 2;           // 8 KB, 64-byte rows, 64-byte swizzle (two buffers)
 constexpr int K_BYTES = BN * D * 2;           // 4 KB, 64-byte rows
 constexpr int VT_BYTES = VT_ROWS * BN * 2;    // 6 KB, 128-byte rows (TMA fills the first 32)
 constexpr int NB_BYTES = BM * BN * 2;         // 16 KB, 128-byte rows: pair bias in, probabilities out (in place)
 constexpr int MB_BYTES = 1024;                // 64 floats, padded
 constexpr int STAGE_BYTES = K_BYTES + VT_BYTES + NB_BYTES + MB_BYTES;
-constexpr int OFF_STAGE = Q_BYTES;
-constexpr int OFF_BAR = OFF_STAGE + NST * STAGE_BYTES;
+constexpr int OFF_STAGE = 2 * Q_BYTES;
+constexpr int OFF_XCH = OFF_STAGE + NST * STAGE_BYTES;      // running maxima of both halves, two item parities
+constexpr int XCH_BYTES = 2 * 2 * BM * 4;
+constexpr int OFF_BAR = OFF_XCH + XCH_BYTES;
 constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
 constexpr int SOFTMAX_WARPS = 8;
 constexpr int THREADS = (2 + SOFTMAX_WARPS) * 32;
 constexpr int TMEM_COLS = 256;
 constexpr int S_COL = 0, O_COL = 64, O_STRIDE = VT_ROWS;   // O_0 at 64..111, O_1 at 112..159
-constexpr int XCH_STRIDE = 36;        // floats per row of the end-of-kernel exchange buffer
 constexpr float kRescaleThreshold = 8.0f;     // log2 units
 
 struct AttnParams {
@@ -66,9 +77,21 @@ struct AttnParams {
     __nv_bfloat16 *avg;               // [B, S, H*D]
     int64_t bias_stride0;
     int *err;
-    int S, H;
+    int S, H, B;
+    int n_qt;                         // query tiles per (b, h)
+    int n_items;                      // B * H * n_qt
     float scale;
 };
+
+__device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
 
 template <bool HAS_NB>
 __global__ void __launch_bounds__(THREADS, 2)
@@ -79,26 +102,29 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     extern __shared__ unsigned char smem_raw[];
     const uint32_t smem = (smem_u32(smem_raw) + 1023u) & ~1023u;
     unsigned char *smem_gen = smem_raw + (smem - smem_u32(smem_raw));
-    const uint32_t q_base = smem;
+    auto q_buf = [&](int i) { return smem + (uint32_t)(i & 1) * Q_BYTES; };
     auto stage_base = [&](int s) { return smem + OFF_STAGE + (uint32_t)s * STAGE_BYTES; };
     const uint32_t bar = smem + OFF_BAR;
     auto kv_full = [&](int s) { return bar + 8u * (uint32_t)s; };
     auto kv_empty = [&](int s) { return bar + 8u * (uint32_t)(NST + s); };
-    // P lives in the ring stage, so "P written" is tracked per stage: a softmax warp that runs a tile ahead
-    // of a slower one then arrives on a different barrier instead of completing the slower tile's phase
     auto p_full = [&](int s) { return bar + 8u * (uint32_t)(2 * NST + s); };
-    // pv_done completes once per tile and is only awaited on the rare rescale path, where the waiter is
-    // provably at most one phase behind. The end of the last product has its own single-phase barrier: a
-    // parity wait names "the current or the preceding phase", so a warp that runs more than one tile ahead
-    // of the slowest one must not use pv_done's parity to learn that everything has retired.
-    const uint32_t q_full = bar + 8u * (3 * NST), s_full = q_full + 8, s_free = q_full + 16, pv_done = q_full + 24,
-                   o_final = q_full + 32, tmem_slot = q_full + 40;
+    auto q_full = [&](int i) { return bar + 8u * (uint32_t)(3 * NST + (i & 1)); };
+    auto q_empty = [&](int i) { return bar + 8u * (uint32_t)(3 * NST + 2 + (i & 1)); };
+    const uint32_t s_full = bar + 8u * (3 * NST + 4), s_free = s_full + 8, pv_done = s_full + 16, o_final = s_full + 24,
+                   o_free = s_full + 32, tmem_slot = s_full + 40;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int S = p.S;
-    const int q0 = blockIdx.x * BM, h = blockIdx.y, b = blockIdx.z;
-    const int bh = b * p.H + h;
     const int nkt = (S + BN - 1) / BN;
+    // items of this CTA: blockIdx.x, blockIdx.x + gridDim.x, ...
+    const int my_items = ((int)blockIdx.x < p.n_items) ? (p.n_items - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+    auto decode = [&](int i, int &q0, int &h, int &b) {
+        const int w = (int)blockIdx.x + i * (int)gridDim.x;
+        const int qt = w % p.n_qt, hb = w / p.n_qt;
+        q0 = qt * BM;
+        h = hb % p.H;
+        b = hb / p.H;
+    };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < NST; ++s) {
@@ -106,11 +132,15 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             mbar_init(kv_empty(s), 1);      // the commit that follows P.V^T (P lives in the stage)
             mbar_init(p_full(s), SOFTMAX_WARPS);
         }
-        mbar_init(q_full, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(q_full(i), 1);
+            mbar_init(q_empty(i), 1);
+        }
         mbar_init(s_full, 1);
         mbar_init(s_free, SOFTMAX_WARPS);
         mbar_init(pv_done, 1);
         mbar_init(o_final, 1);
+        mbar_init(o_free, SOFTMAX_WARPS);
         fence_barrier_init();
     }
     // static rows 32..47 of every V^T stage: row 32 = 1.0 (row-sum column of O), rows 33..47 = 0
@@ -138,71 +168,99 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             tma_prefetch_desc(&tm_k);
             tma_prefetch_desc(&tm_vt);
             if (HAS_NB) tma_prefetch_desc(&tm_nb);
-            mbar_arrive_expect_tx(q_full, Q_BYTES);
-            tma_load_3d(q_base, &tm_q, q_full, 0, q0, bh);
         }
-        const __nv_bfloat16 *__restrict__ biasg = p.bias + (int64_t)b * p.bias_stride0;
-        for (int kt = 0; kt < nkt; ++kt) {
-            const int s = kt % NST;
-            if (kt >= NST && !mbar_wait_warp(kv_empty(s), (uint32_t)((kt / NST - 1) & 1), p.err, 21)) break;
-            const uint32_t st = stage_base(s);
-            const int k0 = kt * BN;
-            float *mb = reinterpret_cast<float *>(smem_gen + OFF_STAGE + s * STAGE_BYTES + K_BYTES + VT_BYTES + NB_BYTES);
-#pragma unroll
-            for (int j = 0; j < 2; ++j) {
-                const int key = k0 + lane + 32 * j;
-                mb[lane + 32 * j] = key < S ? __bfloat162float(biasg[key]) : -INFINITY;
-            }
+        int g = 0;                                      // tiles issued so far (all items)
+        bool ok = true;
+        for (int i = 0; i < my_items && ok; ++i) {
+            int q0, h, b;
+            decode(i, q0, h, b);
+            const int bh = b * p.H + h;
+            if (i >= 2 && !mbar_wait_warp(q_empty(i), (uint32_t)(((i >> 1) - 1) & 1), p.err, 20)) break;
             if (lane == 0) {
-                mbar_arrive_expect_tx(kv_full(s), K_BYTES + BN * D * 2 + (HAS_NB ? NB_BYTES : 0));
-                tma_load_3d(st, &tm_k, kv_full(s), 0, k0, bh);
-                tma_load_3d(st + K_BYTES, &tm_vt, kv_full(s), k0, 0, bh);
-                if (HAS_NB) tma_load_3d(st + K_BYTES + VT_BYTES, &tm_nb, kv_full(s), k0, q0, h);
+                mbar_arrive_expect_tx(q_full(i), Q_BYTES);
+                tma_load_3d(q_buf(i), &tm_q, q_full(i), 0, q0, bh);
             }
-            mbar_arrive(kv_full(s));
+            const __nv_bfloat16 *__restrict__ biasg = p.bias + (int64_t)b * p.bias_stride0;
+            for (int kt = 0; kt < nkt; ++kt, ++g) {
+                const int s = g % NST;
+                if (g >= NST && !mbar_wait_warp(kv_empty(s), (uint32_t)((g / NST - 1) & 1), p.err, 21)) {
+                    ok = false;
+                    break;
+                }
+                const uint32_t st = stage_base(s);
+                const int k0 = kt * BN;
+                float *mb = reinterpret_cast<float *>(smem_gen + OFF_STAGE + s * STAGE_BYTES + K_BYTES + VT_BYTES + NB_BYTES);
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const int key = k0 + lane + 32 * j;
+                    mb[lane + 32 * j] = key < S ? __bfloat162float(biasg[key]) : -INFINITY;
+                }
+                if (lane == 0) {
+                    mbar_arrive_expect_tx(kv_full(s), K_BYTES + BN * D * 2 + (HAS_NB ? NB_BYTES : 0));
+                    tma_load_3d(st, &tm_k, kv_full(s), 0, k0, bh);
+                    tma_load_3d(st + K_BYTES, &tm_vt, kv_full(s), k0, 0, bh);
+                    if (HAS_NB) tma_load_3d(st + K_BYTES + VT_BYTES, &tm_nb, kv_full(s), k0, q0, h);
+                }
+                mbar_arrive(kv_full(s));
+            }
         }
     } else if (warp == 1) {
         // ================= MMA issuer =================
         constexpr uint32_t idesc_s = make_instr_desc_bf16(BM, BN);
         constexpr uint32_t idesc_o = make_instr_desc_bf16(BM, VT_ROWS);
-        bool ok = mbar_wait_warp(q_full, 0, p.err, 22);
-        auto issue_qk = [&](int kt) -> bool {
-            const int s = kt % NST;
-            if (!mbar_wait_warp(kv_full(s), (uint32_t)((kt / NST) & 1), p.err, 23)) return false;
-            if (kt > 0 && !mbar_wait_warp(s_free, (uint32_t)((kt - 1) & 1), p.err, 24)) return false;
+        const int total = my_items * nkt;               // tiles of this CTA, all items
+        // S = Q_i . K_g^T for global tile g of item i
+        auto issue_qk = [&](int g, int i, bool first_of_item) -> bool {
+            const int s = g % NST;
+            if (first_of_item && !mbar_wait_warp(q_full(i), (uint32_t)((i >> 1) & 1), p.err, 22)) return false;
+            if (!mbar_wait_warp(kv_full(s), (uint32_t)((g / NST) & 1), p.err, 23)) return false;
+            if (g > 0 && !mbar_wait_warp(s_free, (uint32_t)((g - 1) & 1), p.err, 24)) return false;
             tc_fence_after();
             if (lane == 0) {
-                const uint32_t kb = stage_base(s);
+                const uint32_t kb = stage_base(s), qb = q_buf(i);
 #pragma unroll
                 for (int k = 0; k < D / 16; ++k)
-                    tc_mma_bf16(tmem_base + S_COL, make_smem_desc_kmajor(q_base + k * 32, 64),
+                    tc_mma_bf16(tmem_base + S_COL, make_smem_desc_kmajor(qb + k * 32, 64),
                                 make_smem_desc_kmajor(kb + k * 32, 64), idesc_s, k > 0 ? 1u : 0u);
                 tc_commit(s_full);
             }
             __syncwarp();
             return true;
         };
-        if (ok) ok = issue_qk(0);
-        for (int kt = 0; kt < nkt && ok; ++kt) {
-            const int s = kt % NST;
-            if (kt + 1 < nkt) ok = issue_qk(kt + 1);     // overlaps the softmax of tile kt
-            if (!ok) break;
-            if (!mbar_wait_warp(p_full(s), (uint32_t)((kt / NST) & 1), p.err, 25)) {
-                ok = false;
-                break;
-            }
-            tc_fence_after();
-            if (lane == 0) {
-                const uint32_t vb = stage_base(s) + K_BYTES, pb = vb + VT_BYTES;
+        bool ok = total > 0 ? issue_qk(0, 0, true) : true;
+        int g = 0;
+        for (int i = 0; i < my_items && ok; ++i) {
+            for (int kt = 0; kt < nkt && ok; ++kt, ++g) {
+                const int s = g % NST;
+                // look one tile ahead in the stream (possibly the first tile of the next item): its Q.K^T
+                // overlaps the softmax of tile g
+                if (g + 1 < total) ok = issue_qk(g + 1, kt + 1 < nkt ? i : i + 1, kt + 1 == nkt);
+                if (!ok) break;
+                if (!mbar_wait_warp(p_full(s), (uint32_t)((g / NST) & 1), p.err, 25)) {
+                    ok = false;
+                    break;
+                }
+                // the first P.V^T of an item overwrites O: the previous item's epilogue must have read it
+                if (kt == 0 && i > 0 && !mbar_wait_warp(o_free, (uint32_t)((i - 1) & 1), p.err, 30)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                if (lane == 0) {
+                    const uint32_t vb = stage_base(s) + K_BYTES, pb = vb + VT_BYTES;
 #pragma unroll
-                for (int k = 0; k < BN / 16; ++k)        // k16 steps 0,1 -> O_0 (keys 0..31), 2,3 -> O_1 (keys 32..63)
-                    tc_mma_bf16(tmem_base + O_COL + (k >> 1) * O_STRIDE, make_smem_desc_kmajor(pb + k * 32, 128),
-                                make_smem_desc_kmajor(vb + k * 32, 128), idesc_o, (kt > 0 || (k & 1)) ? 1u : 0u);
-                tc_commit(pv_done);
-                tc_commit(kv_empty(s));
-                if (kt == nkt - 1) tc_commit(o_final);
+                    for (int k = 0; k < BN / 16; ++k)    // k16 steps 0,1 -> O_0 (keys 0..31), 2,3 -> O_1 (keys 32..63)
+                        tc_mma_bf16(tmem_base + O_COL + (k >> 1) * O_STRIDE, make_smem_desc_kmajor(pb + k * 32, 128),
+                                    make_smem_desc_kmajor(vb + k * 32, 128), idesc_o, (kt > 0 || (k & 1)) ? 1u : 0u);
+                    tc_commit(pv_done);
+                    tc_commit(kv_empty(s));
+                    if (kt == nkt - 1) {
+                        tc_commit(o_final);
+                        tc_commit(q_empty(i));
+                    }
+                }
+                __syncwarp();
             }
-            __syncwarp();
         }
     } else {
         // ================= softmax / epilogue =================
@@ -212,20 +270,22 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         const uint32_t t_lane = tmem_base + ((uint32_t)(quad * 32) << 16);
         const uint32_t o_col = t_lane + O_COL + half * O_STRIDE;
         const float scale = p.scale;
-        float m2 = -INFINITY;                            // running (possibly stale) max of this half, log2 units
         bool ok = true;
-        // Per-thread shared-memory addresses, hoisted out of the tile loop. The ring is unrolled by stage
-        // below, so every stage offset is a compile-time constant added to these.
+        // per-thread shared-memory addresses of stage 0; other stages add a multiple of STAGE_BYTES
         const uint32_t st0 = smem + OFF_STAGE;
         uint32_t nb_addr[4];                             // this row's 4 swizzled 16-byte chunks (pair bias in, P out)
 #pragma unroll
         for (int c = 0; c < 4; ++c)
             nb_addr[c] = st0 + K_BYTES + VT_BYTES + (uint32_t)row * 128 + (uint32_t)(((half * 4 + c) ^ (row & 7)) << 4);
         const uint32_t mb_addr = st0 + K_BYTES + VT_BYTES + NB_BYTES + half * 128;
+        float *xch = reinterpret_cast<float *>(smem_gen + OFF_XCH);      // [item parity][half][row]
+        float m2 = -INFINITY;                            // running (possibly stale) max of this half, log2 units
 
-        // One tile of the softmax; `soff` is the byte offset of the ring stage (a constant after unrolling)
-        auto do_tile = [&](const int kt, const uint32_t soff, const uint32_t kv_full_bar, const uint32_t p_full_bar) -> bool {
-            if (!mbar_wait_warp(s_full, (uint32_t)(kt & 1), p.err, 26)) return false;
+        // one tile of the softmax: global tile g, tile kt of its item
+        auto do_tile = [&](const int g, const int kt) -> bool {
+            const int s = g % NST;
+            const uint32_t soff = (uint32_t)s * STAGE_BYTES;
+            if (!mbar_wait_warp(s_full, (uint32_t)(g & 1), p.err, 26)) return false;
             tc_fence_after();
             uint32_t sr[32];
             tmem_ld_32x32(t_lane + S_COL + half * 32, sr);
@@ -233,7 +293,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(s_free);
-            if (!mbar_wait_warp(kv_full_bar, (uint32_t)((kt / NST) & 1), p.err, 27)) return false;
+            if (!mbar_wait_warp(kv_full(s), (uint32_t)((g / NST) & 1), p.err, 27)) return false;
 
             // x = bf16(logit)*scale + bias (+ pair bias) for 8 keys; keeps x in sr and tracks the tile max
             float tmax = -INFINITY;
@@ -277,7 +337,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             };
 
             if (kt == 0) {
-                // first tile: the max must be known before any probability is formed
+                // first tile of an item: the max must be known before any probability is formed
 #pragma unroll
                 for (int c = 0; c < 4; ++c) x_chunk(c);
                 // a half whose keys all lie beyond S has no max yet: park it on a finite floor
@@ -300,8 +360,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     // rare: the max of some row grew past the threshold. Rescale those rows of O_half (and
                     // their row-sum column) and redo this tile's probabilities against the new max. The
                     // previous tile's P.V^T must have retired first (this warp is at most one phase behind
-                    // pv_done here).
-                    if (!mbar_wait_warp(pv_done, (uint32_t)((kt - 1) & 1), p.err, 28)) return false;
+                    // pv_done here: s_full(g) implies that the product of tile g-2 has retired).
+                    if (!mbar_wait_warp(pv_done, (uint32_t)((g - 1) & 1), p.err, 28)) return false;
                     tc_fence_after();
                     const float f = grow ? ex2_approx(m2 - t2) : 1.0f;
                     uint32_t o[32];
@@ -323,69 +383,58 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             fence_proxy_async();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(p_full_bar);
+            if (lane == 0) mbar_arrive(p_full(s));
             return true;
         };
 
-        for (int kt0 = 0; kt0 < nkt && ok; kt0 += NST) {
-#pragma unroll
-            for (int s = 0; s < NST; ++s) {
-                if (kt0 + s < nkt && ok) ok = do_tile(kt0 + s, (uint32_t)s * STAGE_BYTES, kv_full(s), p_full(s));
-            }
-        }
+        int g = 0;
+        for (int i = 0; i < my_items && ok; ++i) {
+            int q0, h, b;
+            decode(i, q0, h, b);
+            for (int kt = 0; kt < nkt && ok; ++kt, ++g) ok = do_tile(g, kt);
+            if (!ok) break;
 
-        // ---- epilogue: merge the two key halves of each row, normalise, gate, store ----
-        ok = ok && mbar_wait_warp(o_final, 0, p.err, 29);
-        uint32_t o[32];
-        float lsum = 0.f;
-        if (ok) {
-            tc_fence_after();
-            tmem_ld_32x32(o_col, o);
-            lsum = __uint_as_float(tmem_ld_32x1(o_col + 32));
-            tmem_ld_wait();
-        }
-        // exchange buffer: stage 0 is idle now (every tile load has been consumed)
-        float *xch = reinterpret_cast<float *>(smem_gen + OFF_STAGE + K_BYTES + VT_BYTES) + row * XCH_STRIDE;
-        if (half == 1 && ok) {
-            xch[0] = m2;
-            xch[1] = lsum;
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-                *reinterpret_cast<float4 *>(xch + 4 + 4 * i) =
-                    make_float4(__uint_as_float(o[4 * i]), __uint_as_float(o[4 * i + 1]), __uint_as_float(o[4 * i + 2]),
-                                __uint_as_float(o[4 * i + 3]));
-        }
-        asm volatile("bar.sync 1, %0;\n" ::"n"(SOFTMAX_WARPS * 32) : "memory");
-        const int qi = q0 + row;
-        if (half == 0 && ok && qi < S) {
-            const float mB = xch[0], lB = xch[1];
-            const float mm = fmaxf(m2, mB);
-            const float fA = ex2_approx(m2 - mm), fB = ex2_approx(mB - mm);
-            const float inv = 1.0f / (lsum * fA + lB * fB);
-            const float cA = fA * inv, cB = fB * inv;
+            // ---- item epilogue: this thread finishes channels [16*half, 16*half + 16) of its row ----
+            const int qi = q0 + row;
             const int Cn = p.H * D;
-            const int64_t base = ((int64_t)b * S + qi) * Cn + h * D;
+            const int64_t base = ((int64_t)b * S + (qi < S ? qi : 0)) * Cn + h * D + half * 16;
             const uint4 *gp = reinterpret_cast<const uint4 *>(p.gate + base);
-            uint4 *op = reinterpret_cast<uint4 *>(p.avg + base);
+            const uint4 gv0 = __ldg(gp), gv1 = __ldg(gp + 1);         // in flight while the last product retires
+            float *xw = xch + (i & 1) * 2 * BM;
+            xw[half * BM + row] = m2;
+            if (!mbar_wait_warp(o_final, (uint32_t)(i & 1), p.err, 29)) {
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            uint32_t oa[16], ob[16];
+            tmem_ld_32x16(t_lane + O_COL + half * 16, oa);                       // O_0, this thread's channels
+            tmem_ld_32x16(t_lane + O_COL + O_STRIDE + half * 16, ob);            // O_1
+            const uint32_t la = tmem_ld_32x1(t_lane + O_COL + 32), lb = tmem_ld_32x1(t_lane + O_COL + O_STRIDE + 32);
+            tmem_ld_wait();
+            tc_fence_before();
+            asm volatile("bar.sync 1, %0;\n" ::"n"(SOFTMAX_WARPS * 32) : "memory");   // maxima visible, O read by all
+            if (lane == 0) mbar_arrive(o_free);
+            const float mA = xw[row], mB = xw[BM + row];
+            const float mm = fmaxf(mA, mB);
+            const float fA = ex2_approx(mA - mm), fB = ex2_approx(mB - mm);
+            const float inv = 1.0f / (__uint_as_float(la) * fA + __uint_as_float(lb) * fB);
+            const float cA = fA * inv, cB = fB * inv;
+            if (qi < S) {
+                const uint32_t gw[8] = {gv0.x, gv0.y, gv0.z, gv0.w, gv1.x, gv1.y, gv1.z, gv1.w};
+                uint32_t ow[8];
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                const uint4 gv = __ldg(gp + c);
-                const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
-                const float4 b0 = *reinterpret_cast<const float4 *>(xch + 4 + 8 * c);
-                const float4 b1 = *reinterpret_cast<const float4 *>(xch + 8 + 8 * c);
-                const float ob[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
-                uint32_t ow[4];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const int i0 = c * 8 + 2 * j;
+                for (int j = 0; j < 8; ++j) {
                     // the weighted average is stored as bf16 before gating in the reference (:128-133)
-                    const uint32_t wa = pack_bf16x2(__uint_as_float(o[i0]) * cA + ob[2 * j] * cB,
-                                                    __uint_as_float(o[i0 + 1]) * cA + ob[2 * j + 1] * cB);
+                    const uint32_t wa = pack_bf16x2(__uint_as_float(oa[2 * j]) * cA + __uint_as_float(ob[2 * j]) * cB,
+                                                    __uint_as_float(oa[2 * j + 1]) * cA + __uint_as_float(ob[2 * j + 1]) * cB);
                     const float s0 = 1.0f / (1.0f + ex2_approx(-bf16lo_to_f32(gw[j]) * kLog2e));
                     const float s1 = 1.0f / (1.0f + ex2_approx(-bf16hi_to_f32(gw[j]) * kLog2e));
                     ow[j] = pack_bf16x2(bf16lo_to_f32(wa) * s0, bf16hi_to_f32(wa) * s1);
                 }
-                op[c] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+                uint4 *op = reinterpret_cast<uint4 *>(p.avg + base);
+                op[0] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+                op[1] = make_uint4(ow[4], ow[5], ow[6], ow[7]);
             }
         }
     }
@@ -399,16 +448,28 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     }
 }
 
+int sm_count_attn()
+{
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        if (n <= 0) n = 148;
+    }
+    return n;
+}
+
 template <bool HAS_NB>
 bool launch_one(cudaStream_t stream, const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tvt,
-                const CUtensorMap &tnb, const AttnParams &p, int B)
+                const CUtensorMap &tnb, const AttnParams &p)
 {
     static bool configured = false;
     if (!configured) {
         KUTACC_CUDA(cudaFuncSetAttribute(attn_tc_kernel<HAS_NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
         configured = true;
     }
-    dim3 grid((unsigned)((p.S + BM - 1) / BM), (unsigned)p.H, (unsigned)B);
+    const unsigned grid = (unsigned)std::min<int64_t>(p.n_items, 2 * sm_count_attn());
     KernelTimer timer__("attn_core");
     attn_tc_kernel<HAS_NB><<<grid, THREADS, SMEM_BYTES, stream>>>(tq, tk, tvt, tnb, p);
     count_launch();
@@ -422,9 +483,11 @@ bool tcgen05_attn_core_bf16(cudaStream_t stream, const void *q, const void *k, c
                             int64_t nb_stride_h, int64_t nb_stride_q, void *avg, int B, int S, int H, int Dh,
                             float scale)
 {
-    if (Dh != D || B > 65535 || H > 65535 || vt_pitch % 8 != 0) return false;
+    if (Dh != D || vt_pitch % 8 != 0) return false;
     if (nb && ((nb_stride_h % 8) || (nb_stride_q % 8) || ((uintptr_t)nb % 16))) return false;
     if ((((uintptr_t)gate | (uintptr_t)avg) & 15u) != 0) return false;
+    const int64_t n_qt = (S + BM - 1) / BM, n_items = n_qt * H * B;
+    if (n_items > INT32_MAX / 64) return false;
     KernelErrorWord &ew = kernel_error_word();
     if (ew.device == nullptr) return false;
     AttnParams p;
@@ -435,6 +498,9 @@ bool tcgen05_attn_core_bf16(cudaStream_t stream, const void *q, const void *k, c
     p.err = ew.device;
     p.S = S;
     p.H = H;
+    p.B = B;
+    p.n_qt = (int)n_qt;
+    p.n_items = (int)n_items;
     p.scale = scale;
     const uint64_t Su = (uint64_t)S, BH = (uint64_t)B * H;
     CUtensorMap tq, tk, tvt, tnb;
@@ -445,10 +511,10 @@ bool tcgen05_attn_core_bf16(cudaStream_t stream, const void *q, const void *k, c
         if (!make_tensor_map_bf16_3d(&tnb, nb, Su, Su, (uint64_t)H, (uint64_t)nb_stride_q, (uint64_t)nb_stride_h, BN, BM,
                                      128))
             return false;
-        return launch_one<true>(stream, tq, tk, tvt, tnb, p, B);
+        return launch_one<true>(stream, tq, tk, tvt, tnb, p);
     }
     tnb = tk;
-    return launch_one<false>(stream, tq, tk, tvt, tnb, p, B);
+    return launch_one<false>(stream, tq, tk, tvt, tnb, p);
 }
 
 }  // namespace dev
