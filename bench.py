@@ -41,7 +41,10 @@ UNIT = "TFLOP/s"
 
 # DRAM bytes (read + write) of one launch of the dominant kernel from an ncu capture, per workload;
 # None until a capture exists for the current kernel. See profiles/.
-NCU_TRAFFIC = {}
+NCU_TRAFFIC = {
+    # attn_tc_kernel, ncu --set full, dram__bytes_read.sum + dram__bytes_write.sum (profiles/attn_core_triangle_start_384.md)
+    "triangle_start_384": 152.5e6 + 22.0e6,
+}
 
 
 def measured_peaks():
