@@ -218,6 +218,164 @@ __global__ void __launch_bounds__(CORE_THREADS) global_core_kernel(const __nv_bf
     }
 }
 
+// ---- core on tensor cores (8 heads x 8 channels) -----------------------------------------------------
+// Each warp walks 16-row tiles of x (double-buffered cp.async into its own shared-memory slab) and chains
+// four small products through registers, using the fact that an mma.sync accumulator fragment (row g,
+// columns 2t, 2t+1) has the layout of an A fragment of the next product and, read "transposed", of a B
+// fragment:
+//   k   [16 rows x 8]   = x . Wk^T                 m16n8k16 x 4   (A = x tile, B = Wk in registers)
+//   v^T [8 x 16 rows]   = Wv . x^T                 m16n8k16 x 8   (A = Wv in registers, B = the same x fragments)
+//   L^T [8 heads x 16]  = q . k^T                  m16n8k8  x 2   (B = bf16(k) accumulators)
+//   wa  [8 heads x 8]  += P^T . v                  m16n8k16 x 1   (A = bf16(P), B = bf16(v^T) accumulators)
+// Thread (g, t) therefore owns head g: its running max is shared by the quad (two shuffles per tile).
+__device__ __forceinline__ void mma_bf16_1688(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0)
+{
+    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(b0));
+}
+
+__global__ void __launch_bounds__(CORE_THREADS) global_core_mma_kernel(const __nv_bfloat16 *__restrict__ x,
+                                                                       const __nv_bfloat16 *__restrict__ mask,
+                                                                       const __nv_bfloat16 *__restrict__ wq,
+                                                                       const __nv_bfloat16 *__restrict__ wk,
+                                                                       const __nv_bfloat16 *__restrict__ wv, Scratch sc,
+                                                                       int b0, int S, int rows_per_split)
+{
+    constexpr int H = 8, D = 8, NW = CORE_THREADS / 32;
+    __shared__ float s_qa[GC];
+    __shared__ float s_q[GC];
+    __shared__ __align__(128) __nv_bfloat16 s_x[NW][2][16 * GC];
+    __shared__ float s_m[NW][H];
+    __shared__ float s_part[NW][H][1 + D];
+
+    const int b = b0 + blockIdx.y, split = blockIdx.x;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    if (tid < GC) {
+        float acc = 0.f, ms = 0.f;
+        for (int sp = 0; sp < sc.nsplit; ++sp) {
+            const float *pp = sc.pool + ((int64_t)b * sc.nsplit + sp) * (GC + 1);
+            acc += pp[tid];
+            ms += pp[GC];
+        }
+        s_qa[tid] = rbf(acc * (1.0f / (ms + 1e-10f)));
+    }
+    __syncthreads();
+    if (tid < GC) {
+        float acc = 0.f;
+        for (int c = 0; c < GC; ++c) acc = fmaf(s_qa[c], __bfloat162float(wq[tid * GC + c]), acc);
+        s_q[tid] = rbf(acc);
+    }
+    __syncthreads();
+
+    // operands that stay in registers: Wk as B fragments, Wv as A fragments (rows 8..15 zero), q as A fragment
+    uint32_t bk[4][2], av[4][2];
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) {
+        bk[ks][0] = *reinterpret_cast<const uint32_t *>(wk + g * GC + 16 * ks + 2 * t);
+        bk[ks][1] = *reinterpret_cast<const uint32_t *>(wk + g * GC + 16 * ks + 8 + 2 * t);
+        av[ks][0] = *reinterpret_cast<const uint32_t *>(wv + g * GC + 16 * ks + 2 * t);
+        av[ks][1] = *reinterpret_cast<const uint32_t *>(wv + g * GC + 16 * ks + 8 + 2 * t);
+    }
+    const uint32_t aq = pack_bf16x2(s_q[g * D + 2 * t], s_q[g * D + 2 * t + 1]);
+    const float scale = 1.0f / sqrtf((float)D);
+
+    const int s_begin = split * rows_per_split, s_end = min(S, s_begin + rows_per_split);
+    const int ntile = (s_end - s_begin + 15) / 16;
+    const __nv_bfloat16 *xb = x + (int64_t)b * S * GC;
+    const __nv_bfloat16 *mb = mask + (int64_t)b * S;
+
+    auto load_tile = [&](int tile, int buf) {
+        const int r0 = s_begin + tile * 16;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int idx = lane + 32 * i, r = idx >> 3, c = idx & 7;
+            const bool ok = r0 + r < s_end;
+            cp_async16(smem_u32(&s_x[warp][buf][r * GC + swz8(r, c) * 8]), xb + (int64_t)(ok ? r0 + r : s_begin) * GC + c * 8,
+                       ok ? 16 : 0);
+        }
+    };
+
+    float m_run = -INFINITY, l_run = 0.f, wa[4] = {0.f, 0.f, 0.f, 0.f};
+    int it = 0;
+    if (warp < ntile) load_tile(warp, 0);
+    cp_async_commit();
+    for (int tile = warp; tile < ntile; tile += NW, ++it) {
+        const int buf = it & 1;
+        if (tile + NW < ntile) load_tile(tile + NW, buf ^ 1);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncwarp();
+
+        float kacc[4] = {0.f, 0.f, 0.f, 0.f}, v0[4] = {0.f, 0.f, 0.f, 0.f}, v1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+            uint32_t a[4];
+            const int r = lane & 15, c = ks * 2 + (lane >> 4);
+            ldmatrix_x4(a[0], a[1], a[2], a[3], smem_u32(&s_x[warp][buf][r * GC + swz8(r, c) * 8]));
+            mma_bf16_16816(kacc, a, bk[ks][0], bk[ks][1]);
+            const uint32_t wvf[4] = {av[ks][0], 0u, av[ks][1], 0u};
+            mma_bf16_16816(v0, wvf, a[0], a[2]);       // rows 0..7 of the tile
+            mma_bf16_16816(v1, wvf, a[1], a[3]);       // rows 8..15
+        }
+        // logits of head g for rows 2t, 2t+1 (l0) and 8+2t, 9+2t (l1); k is stored as bf16 by the reference
+        float l0[4] = {0.f, 0.f, 0.f, 0.f}, l1[4] = {0.f, 0.f, 0.f, 0.f};
+        mma_bf16_1688(l0, aq, 0u, pack_bf16x2(kacc[0], kacc[1]));
+        mma_bf16_1688(l1, aq, 0u, pack_bf16x2(kacc[2], kacc[3]));
+        const int r0 = s_begin + tile * 16;
+        const int rows[4] = {r0 + 2 * t, r0 + 2 * t + 1, r0 + 8 + 2 * t, r0 + 9 + 2 * t};
+        const float lg[4] = {l0[0], l0[1], l1[0], l1[1]};
+        float xv[4];
+        float tmax = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const bool ok = rows[i] < s_end;
+            const float mbias = ok ? fmaf(__bfloat162float(mb[ok ? rows[i] : s_begin]), 1e9f, -1e9f) : -INFINITY;
+            xv[i] = rbf(lg[i]) * scale + mbias;
+            tmax = fmaxf(tmax, xv[i]);
+        }
+        tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
+        tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
+        const float m_new = fmaxf(m_run, tmax);
+        const float corr = __expf(m_run - m_new);      // first tile: exp(-inf) = 0
+        m_run = m_new;
+        float pv[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) pv[i] = __expf(xv[i] - m_new);
+        l_run = l_run * corr + (pv[0] + pv[1] + pv[2] + pv[3]);
+        wa[0] *= corr;
+        wa[1] *= corr;
+        const uint32_t pa[4] = {pack_bf16x2(pv[0], pv[1]), 0u, pack_bf16x2(pv[2], pv[3]), 0u};
+        mma_bf16_16816(wa, pa, pack_bf16x2(v0[0], v0[1]), pack_bf16x2(v1[0], v1[1]));
+        __syncwarp();
+    }
+    cp_async_wait<0>();
+
+    // merge: row sums across the quad, then the per-warp states across the block
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+    if (t == 0) {
+        s_m[warp][g] = m_run;
+        s_part[warp][g][0] = l_run;
+    }
+    s_part[warp][g][1 + 2 * t] = wa[0];
+    s_part[warp][g][2 + 2 * t] = wa[1];
+    __syncthreads();
+    float *dst = sc.core + ((int64_t)b * sc.nsplit + split) * H * (2 + D);
+    for (int i = tid; i < H * (1 + D); i += CORE_THREADS) {
+        const int h = i / (1 + D), j = i % (1 + D);
+        float mx = s_m[0][h];
+        for (int w = 1; w < NW; ++w) mx = fmaxf(mx, s_m[w][h]);
+        float acc = 0.f;
+        for (int w = 0; w < NW; ++w) {
+            const float f = (s_m[w][h] == -INFINITY) ? 0.f : __expf(s_m[w][h] - mx);
+            acc += s_part[w][h][j] * f;
+        }
+        dst[h * (2 + D) + 1 + j] = acc;
+        if (j == 0) dst[h * (2 + D)] = mx;
+    }
+}
+
 // ---- out -----------------------------------------------------------------------------------------
 struct OutSmem {
     __nv_bfloat16 x[OUT_ROWS * GC];   // activations tile, later reused to stage the output tile
@@ -239,14 +397,8 @@ __global__ void __launch_bounds__(256) global_out_kernel(const __nv_bfloat16 *__
     __shared__ __align__(128) OutSmem sm;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int b = b0 + blockIdx.y;
-    const int s0 = blockIdx.x * OUT_ROWS;
-    const __nv_bfloat16 *xb = x + ((int64_t)b * S + s0) * GC;
+    const int ntiles = (S + OUT_ROWS - 1) / OUT_ROWS;
 
-    for (int idx = tid; idx < OUT_ROWS * 8; idx += 256) {
-        const int r = idx >> 3, c = idx & 7;
-        const bool ok = s0 + r < S;
-        cp_async16(smem_u32(&sm.x[r * GC + swz8(r, c) * 8]), xb + (int64_t)(ok ? r : 0) * GC + c * 8, ok ? 16 : 0);
-    }
     for (int idx = tid; idx < GC * 8; idx += 256) {
         const int r = idx >> 3, c = idx & 7;
         cp_async16(smem_u32(&sm.wg[r * GC + swz8(r, c) * 8]), wg + r * GC + c * 8, 16);
@@ -270,10 +422,20 @@ __global__ void __launch_bounds__(256) global_out_kernel(const __nv_bfloat16 *__
         sm.bg[tid] = bg[tid];
         sm.bo[tid] = bo[tid];
     }
+    const int g = lane >> 2, t = lane & 3;
+    // the weights and wa stay resident; the CTA walks several 128-row tiles of this column
+    for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+    const int s0 = tile * OUT_ROWS;
+    const __nv_bfloat16 *xb = x + ((int64_t)b * S + s0) * GC;
+    for (int idx = tid; idx < OUT_ROWS * 8; idx += 256) {
+        const int r = idx >> 3, c = idx & 7;
+        const bool ok = s0 + r < S;
+        cp_async16(smem_u32(&sm.x[r * GC + swz8(r, c) * 8]), xb + (int64_t)(ok ? r : 0) * GC + c * 8, ok ? 16 : 0);
+    }
+    cp_async_commit();
     cp_async_wait<0>();
     __syncthreads();
 
-    const int g = lane >> 2, t = lane & 3;
     // gate = x . Wg^T : 16 rows x 64 per warp
     float acc[8][4];
 #pragma unroll
@@ -348,6 +510,8 @@ __global__ void __launch_bounds__(256) global_out_kernel(const __nv_bfloat16 *__
             *reinterpret_cast<uint4 *>(ob + (int64_t)r * out_row_stride + c * 8) = val;
         }
     }
+    __syncthreads();   // the tile buffer is reloaded in the next iteration
+    }
 }
 
 struct Plan {
@@ -362,9 +526,9 @@ Plan make_plan(int B, int S)
     const int64_t col_bytes = (int64_t)S * GC * 2;
     const int64_t l2_budget = (int64_t)32 << 20;
     p.group = (int)std::max<int64_t>(1, std::min<int64_t>(B, l2_budget / std::max<int64_t>(col_bytes, 1)));
-    int ns = (148 * 4 + p.group - 1) / p.group;
-    ns = std::max(1, std::min(ns, 32));
-    ns = std::min(ns, std::max(1, S / 256));
+    // The row slices of a column depend on S alone, so a column's partial sums are formed and
+    // merged in the same order whatever the batch it arrives in.
+    const int ns = std::max(1, std::min(32, S / 384));
     p.nsplit = ns;
     p.rows_per_split = (S + ns - 1) / ns;
     return p;
@@ -390,11 +554,17 @@ void run_global(cudaStream_t stream, const void *x, const void *mask, const void
         }
         {
             KernelTimer timer__("global_core");
-        global_core_kernel<H, D><<<g1, CORE_THREADS, 0, stream>>>(
-            (const __nv_bfloat16 *)x, (const __nv_bfloat16 *)mask, (const __nv_bfloat16 *)wq,
-            (const __nv_bfloat16 *)wk, (const __nv_bfloat16 *)wv, sc, b0, S, pl.rows_per_split);
+        if (H == 8 && D == 8)
+            global_core_mma_kernel<<<g1, CORE_THREADS, 0, stream>>>(
+                (const __nv_bfloat16 *)x, (const __nv_bfloat16 *)mask, (const __nv_bfloat16 *)wq,
+                (const __nv_bfloat16 *)wk, (const __nv_bfloat16 *)wv, sc, b0, S, pl.rows_per_split);
+        else
+            global_core_kernel<H, D><<<g1, CORE_THREADS, 0, stream>>>(
+                (const __nv_bfloat16 *)x, (const __nv_bfloat16 *)mask, (const __nv_bfloat16 *)wq,
+                (const __nv_bfloat16 *)wk, (const __nv_bfloat16 *)wv, sc, b0, S, pl.rows_per_split);
         }
-        dim3 g3((unsigned)((S + OUT_ROWS - 1) / OUT_ROWS), (unsigned)nb);
+        const int out_tiles = (S + OUT_ROWS - 1) / OUT_ROWS;
+        dim3 g3((unsigned)((out_tiles + 3) / 4), (unsigned)nb);
         {
             KernelTimer timer__("global_out");
         global_out_kernel<H, D><<<g3, 256, 0, stream>>>((const __nv_bfloat16 *)x, (const __nv_bfloat16 *)wg, bg,
