@@ -116,8 +116,8 @@ def dominant_kernel(workload):
     if workload.kind == "gating":
         # Q.K^T and P.V: 4*B*S^2*C FLOPs, all inside the fused attention core
         return "attn_core", "tensor", 4.0 * workload.B * workload.S * workload.S * workload.C, "TFLOP/s"
-    # global attention: the output kernel streams x once more and writes out: bandwidth bound
-    return "global_out", "hbm", 2.0 * workload.B * workload.S * workload.C * 2, "GB/s"
+    # global attention: one kernel reads x once and writes out once: bandwidth bound
+    return "global_fused", "hbm", 2.0 * workload.B * workload.S * workload.C * 2, "GB/s"
 
 
 def cpu_baseline(name: str, budget_s: float = 12.0):

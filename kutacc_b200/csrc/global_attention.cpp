@@ -67,9 +67,16 @@ extern "C" void kutacc_af2_global_attention(kutacc_af2_attention_inputs_t *q_bas
     KUTACC_CHECK((((uintptr_t)d_x.dev | (uintptr_t)d_out.dev | (uintptr_t)d_wg.dev | (uintptr_t)d_wo.dev) & 15u) == 0,
                  "global_attention: q_data, out and weights must be 16-byte aligned");
     if (kutacc_check_err_set) return;
-    const bool ok = dev::launch_global_attention_bf16(stream, d_x.dev, d_m.dev, d_wq.dev, d_wk.dev, d_wv.dev, d_wg.dev,
-                                                      (const float *)d_bg.dev, d_wo.dev, (const float *)d_bo.dev,
-                                                      d_out.dev, out_rs, scratch, (int)B, (int)S, (int)H, (int)D);
+    // one pass over HBM where the shape allows it (a cluster of CTAs holds each column in shared memory),
+    // otherwise three kernels per L2-sized group of columns with the split-softmax state in `scratch`
+    bool ok = dev::launch_global_fused_bf16(stream, d_x.dev, d_m.dev, d_wq.dev, d_wk.dev, d_wv.dev, d_wg.dev,
+                                            (const float *)d_bg.dev, d_wo.dev, (const float *)d_bo.dev, d_out.dev,
+                                            out_rs, (int)B, (int)S, (int)H, (int)D);
+    if (kutacc_check_err_set) return;
+    if (!ok)
+        ok = dev::launch_global_attention_bf16(stream, d_x.dev, d_m.dev, d_wq.dev, d_wk.dev, d_wv.dev, d_wg.dev,
+                                               (const float *)d_bg.dev, d_wo.dev, (const float *)d_bo.dev, d_out.dev,
+                                               out_rs, scratch, (int)B, (int)S, (int)H, (int)D);
     KUTACC_CHECK(ok, "global_attention: no device kernel for nheads=", H, " head_size=", D, " out row stride ", out_rs);
     finish_out(d_out);
     end_of_call();

@@ -67,6 +67,11 @@ bool launch_pair_bias(cudaStream_t stream, ElemType t, const void *z, const void
 
 // ---- global attention (bf16, C = 64) ---------------------------------------------------------------
 // scratch: qk [B, H, 64] fp32-sized slots and wa [B, 64]; see global_attention.cu
+// Global attention in one pass over HBM (thread-block clusters hold a column in shared memory); 8 heads x 8
+// only. Returns false when the shape is not covered.
+bool launch_global_fused_bf16(cudaStream_t stream, const void *x, const void *mask, const void *wq, const void *wk,
+                              const void *wv, const void *wg, const float *bg, const void *wo, const float *bo,
+                              void *out, int64_t out_row_stride, int B, int S, int H, int D);
 size_t global_attention_scratch_bytes(int B, int S, int H, int D);
 bool launch_global_attention_bf16(cudaStream_t stream, const void *x, const void *mask, const void *wq,
                                   const void *wk, const void *wv, const void *wg, const float *bg, const void *wo,

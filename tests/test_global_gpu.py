@@ -17,7 +17,8 @@ def _run(w, device=True):
     return runner.out_to_f32(out)
 
 
-@pytest.mark.parametrize("B,S,H,D", [(2, 48, 8, 8), (3, 130, 8, 8), (1, 1000, 8, 8), (2, 257, 4, 16), (2, 64, 2, 32),
+@pytest.mark.parametrize("B,S,H,D", [(2, 48, 8, 8), (3, 130, 8, 8), (1, 1000, 8, 8), (2, 1500, 8, 8), (1, 5300, 8, 8),
+                                     (1, 14100, 8, 8), (2, 257, 4, 16), (2, 64, 2, 32),
                                      (1, 96, 16, 4), (1, 70, 1, 64)])
 def test_matches_faithful_oracle(kutacc_lib, B, S, H, D):
     w = W.random_global_case(seed=400 + S, B=B, S=S, H=H, D=D, zero_mask_rows=1 if B > 1 else 0)
@@ -51,3 +52,25 @@ def test_columns_are_independent_at_full_size(kutacc_lib):
     full = _run(w)
     sub = W.make("extra_msa_global", rows=3)
     assert np.array_equal(_run(sub), full[:3])
+
+
+def test_many_short_columns_wrap_the_shared_memory_ring(kutacc_lib):
+    # more columns than resident clusters: every CTA walks several columns and reuses its slots
+    w = W.random_global_case(seed=23, B=700, S=300, zero_mask_rows=3)
+    got = _run(w)
+    assert np.isfinite(got).all()
+    assert helpers.rel_err(got, helpers.oracle_faithful(w)) <= helpers.BF16_TOL
+
+
+def test_strided_output_rows(kutacc_lib):
+    w = W.random_global_case(seed=24, B=3, S=333)
+    want = _run(w)
+    case = runner.DeviceCase(w)
+    wide = torch.full((w.B, w.S, 96), 7.0, dtype=torch.bfloat16, device="cuda:0")
+    out_t = api.Tensor(wide.data_ptr(), [w.B, w.S, w.C], [w.S * 96, 96, 1], api.DTYPE_BF16, keep=wide)
+    api.global_attention(case.inputs, case.t_x, case.t_mask, case.weights, out_t)
+    torch.cuda.synchronize()
+    api.raise_if_error()
+    got = wide.float().cpu().numpy()
+    assert np.array_equal(got[:, :, :w.C], want)
+    assert (got[:, :, w.C:] == 7.0).all()                   # the gap between rows is left alone

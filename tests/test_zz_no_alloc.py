@@ -42,11 +42,13 @@ def test_noalloc_entry_matches_regular_operator_twice_in_a_row(kutacc_lib):
         torch.cuda.synchronize()
         api.raise_if_error()
         got = out.float().cpu().numpy()
-        # same kernels, same split plan: the results agree to the last bit; the parity tolerance of the
-        # other tests (1e-2 relative) is the formal bound
+        # the parity tolerance of the other tests (1e-2 relative) is the formal bound; where the regular
+        # operator runs the same three kernels with the same split plan (every shape but 8 heads x 8, which
+        # it computes in one cluster kernel) the results agree to the last bit
         assert np.isfinite(got).all()
         assert np.abs(got - want).max() <= 1e-2 * np.abs(want).max()
-        assert np.array_equal(got, want)
+        if (w.H, w.D) != (8, 8):
+            assert np.array_equal(got, want)
         assert api.lib().kutacc_b200_workspace_bytes() == held      # the library's pool did not grow
 
 
