@@ -37,37 +37,58 @@ constexpr int FC = 64;                 // channels
 constexpr int FH = 8, FD = 8;          // heads x head size
 constexpr int CH_ROWS = 128;           // rows per slot
 constexpr int CH_BYTES = CH_ROWS * FC * 2;
-constexpr int NSLOT = 11;              // slots in the ring
-constexpr int NCW = 16;                // consumer warps: two groups of 8, group g takes the chunks c = g (mod 2)
-constexpr int IO_WARP = NCW, MMA_WARP = NCW + 1;
-constexpr int NTHREADS = (NCW + 2) * 32;
-constexpr int NACC = 8;                // TMEM accumulators (128 lanes x 64 fp32 columns each), two per warp group
-constexpr int CT = 1;                  // tiles per step of the core loop
-constexpr int NGRP = 4;                // warp groups of the output stage (4 warps = 128 rows each)
-constexpr int TMEM_COLS = NACC * FC;
 constexpr int MAX_CTA = 8;             // portable cluster size limit
-constexpr int MAX_ROWS = NSLOT * CH_ROWS;
+constexpr int CT = 1;                  // tiles per step of the core loop
 
+// Two shapes of CTA:
+//   Wide  : 16 computing warps, 11 slots, one CTA per SM. A column of up to 11 * 128 * 8 rows.
+//   Half  : 8 computing warps, 5 slots, two CTAs per SM, so that the stages of two columns overlap on
+//           every SM (the output stage is bound by the MUFU pipe, pooling and the softmax by latency).
+//           A column of up to 5 * 128 * 8 = 5120 rows; Wq is read from global memory.
+template <int NCW_, int NSLOT_, bool WQ_SMEM_, int MIN_CTAS_, int BOUND_THREADS_>
+struct Cfg {
+    static constexpr int NCW = NCW_;                    // computing warps
+    static constexpr int NSLOT = NSLOT_;                // slots in the ring
+    static constexpr int IO_WARP = NCW_, MMA_WARP = NCW_ + 1;
+    static constexpr int NTHREADS = (NCW_ + 2) * 32;
+    static constexpr int NPG = NCW_ / 8;                // groups of 8 warps in pool and core: group g takes chunks c = g (mod NPG)
+    static constexpr int NGRP = NCW_ / 4;               // groups of 4 warps (128 rows) in the output stage
+    static constexpr int NACC = 2 * NGRP;               // TMEM accumulators (128 lanes x 64 fp32 columns), two per group
+    static constexpr int TMEM_COLS = NACC * FC;
+    static constexpr int MAX_ROWS = NSLOT_ * CH_ROWS;
+    static constexpr bool WQ_SMEM = WQ_SMEM_;
+    static constexpr int MIN_CTAS = MIN_CTAS_;
+    // thread count handed to __launch_bounds__: registers are split between the four schedulers of an SM by whole
+    // warps, so two 10-warp CTAs need the register budget of two 12-warp CTAs (3 warps per scheduler each)
+    static constexpr int BOUND_THREADS = BOUND_THREADS_;
+};
+using WideCfg = Cfg<16, 11, true, 1, 18 * 32>;
+using HalfCfg = Cfg<8, 5, false, 2, 12 * 32>;
+
+template <class K>
 struct __align__(1024) FusedSmem {
-    unsigned char slot[NSLOT][CH_BYTES];
-    __nv_bfloat16 wg[FC * FC];         // 16-byte chunks swizzled by row, as ldmatrix wants them
+    unsigned char slot[K::NSLOT][CH_BYTES];
+    __nv_bfloat16 wg[FC * FC];         // 16-byte chunks swizzled by row: the K-major 128-byte-swizzle operand layout
     __nv_bfloat16 wo[FC * FC];
-    __nv_bfloat16 wq[FC * FC];
+    __nv_bfloat16 wq[K::WQ_SMEM ? FC * FC : 8];
     __nv_bfloat16 wk[FD * FC];
     __nv_bfloat16 wv[FD * FC];
-    unsigned short mask[2][MAX_ROWS];  // bf16 bits of this CTA's rows of the mask, double-buffered by column
+    unsigned short mask[2][K::MAX_ROWS];  // bf16 bits of this CTA's rows of the mask, double-buffered by column
     float pool_part[MAX_CTA][FC + 1];  // written by the CTA of that rank (remote stores)
     float core_part[MAX_CTA][FH][2 + FD];
-    float red[NCW][FC + 1];
-    float s_m[NCW][FH];
-    float s_part[NCW][FH][1 + FD];
+    union {                            // pooling and the softmax merge never overlap in time
+        float red[K::NCW][FC + 1];
+        float s_part[K::NCW][FH][1 + FD];
+    };
+    float s_m[K::NCW][FH];
     __align__(16) float qa[FC], q[FC], hwa[FC], bg[FC], bo[FC];   // hwa = wa / 2
-    uint64_t full[NSLOT], done[NSLOT], pool_bar, core_bar;
-    uint64_t g1_done[NACC], p_ready[NACC], g2_done[NACC], d_free[NACC];
+    uint64_t full[K::NSLOT], done[K::NSLOT], pool_bar, core_bar;
+    uint64_t g1_done[K::NACC], p_ready[K::NACC], g2_done[K::NACC], d_free[K::NACC];
     uint32_t tmem_base;
     int abort_flag;
 };
-static_assert(sizeof(FusedSmem) <= 232448, "shared memory of one CTA");
+static_assert(sizeof(FusedSmem<WideCfg>) + 1024 <= 232448, "shared memory of one CTA");
+static_assert(2 * (sizeof(FusedSmem<HalfCfg>) + 1024 + 1024) <= 233472, "two CTAs per SM");
 
 struct FusedArgs {
     const __nv_bfloat16 *mask, *wq, *wk, *wv, *wg, *wo;
@@ -80,10 +101,12 @@ struct FusedArgs {
 
 __device__ __forceinline__ float rbf(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 __device__ __forceinline__ float bits_to_f32(unsigned short b) { return __uint_as_float((uint32_t)b << 16); }
-__device__ __forceinline__ void consumer_bar() { asm volatile("bar.sync 1, %0;\n" ::"n"(NCW * 32) : "memory"); }
+template <class K>
+__device__ __forceinline__ void consumer_bar_t() { asm volatile("bar.sync 1, %0;\n" ::"n"(K::NCW * 32) : "memory"); }
 
 // barrier over the consumer warps that also ORs a predicate across them
-__device__ __forceinline__ bool consumer_bar_or(bool pred)
+template <class K>
+__device__ __forceinline__ bool consumer_bar_or_t(bool pred)
 {
     uint32_t r;
     asm volatile(
@@ -94,7 +117,7 @@ __device__ __forceinline__ bool consumer_bar_or(bool pred)
         "selp.u32 %0, 1, 0, p;\n"
         "}\n"
         : "=r"(r)
-        : "r"((uint32_t)pred), "n"(NCW * 32)
+        : "r"((uint32_t)pred), "n"(K::NCW * 32)
         : "memory");
     return r != 0;
 }
@@ -111,9 +134,10 @@ constexpr int ERR_FULL = 0x4701, ERR_DONE = 0x4702, ERR_POOL = 0x4703, ERR_CORE 
               ERR_G1 = 0x4706, ERR_G2 = 0x4707, ERR_MMA = 0x4708;
 
 // ---- the thread that moves data ----------------------------------------------------------------------
-// Chunk `seq` (counted over all columns of this CTA) lives in slot seq % NSLOT. Loads run ahead of the
+// Chunk `seq` (counted over all columns of this CTA) lives in slot seq % K::NSLOT. Loads run ahead of the
 // consumers as far as free slots allow; a slot is free once the store out of it has been read.
-__device__ __forceinline__ void io_thread(FusedSmem &sm, const CUtensorMap *xmap, const CUtensorMap *omap,
+template <class K>
+__device__ __forceinline__ void io_thread(FusedSmem<K> &sm, const CUtensorMap *xmap, const CUtensorMap *omap,
                                           const FusedArgs &a, int cluster_id, int nclusters, int ncols, int mych,
                                           int row_base)
 {
@@ -121,8 +145,8 @@ __device__ __forceinline__ void io_thread(FusedSmem &sm, const CUtensorMap *xmap
     const int total = ncols * mych;
     int issued = 0, committed = 0, freed = 0;
     auto issue_loads = [&]() {
-        while (issued < total && issued - NSLOT < freed) {
-            const int j = issued / mych, c = issued - j * mych, s = issued % NSLOT;
+        while (issued < total && issued - K::NSLOT < freed) {
+            const int j = issued / mych, c = issued - j * mych, s = issued % K::NSLOT;
             const uint32_t bar = smem_u32(&sm.full[s]);
             mbar_arrive_expect_tx(bar, CH_BYTES);
             tma_load_3d(slot0 + s * CH_BYTES, xmap, bar, 0, row_base + c * CH_ROWS, cluster_id + j * nclusters);
@@ -132,14 +156,14 @@ __device__ __forceinline__ void io_thread(FusedSmem &sm, const CUtensorMap *xmap
     issue_loads();
     bool ok = true;
     for (int st = 0; st < total; ++st) {
-        const int j = st / mych, c = st - j * mych, s = st % NSLOT;
+        const int j = st / mych, c = st - j * mych, s = st % K::NSLOT;
         if (c == 0 && st > 0) {
             // between columns nothing else will free the last slots: wait for the stores in flight
             tma_store_wait_read<0>();
             freed = committed;
             issue_loads();
         }
-        if (!mbar_wait(smem_u32(&sm.done[s]), (st / NSLOT) & 1, a.err, ERR_DONE)) {
+        if (!mbar_wait(smem_u32(&sm.done[s]), (st / K::NSLOT) & 1, a.err, ERR_DONE)) {
             ok = false;
             break;
         }
@@ -153,14 +177,15 @@ __device__ __forceinline__ void io_thread(FusedSmem &sm, const CUtensorMap *xmap
     if (!ok) {
         // unwind: no load may still be in flight into this CTA's shared memory when it exits
         sm.abort_flag = 1;
-        for (int seq = max(0, issued - NSLOT); seq < issued; ++seq)
-            mbar_wait(smem_u32(&sm.full[seq % NSLOT]), (seq / NSLOT) & 1, a.err, ERR_DRAIN);
+        for (int seq = max(0, issued - K::NSLOT); seq < issued; ++seq)
+            mbar_wait(smem_u32(&sm.full[seq % K::NSLOT]), (seq / K::NSLOT) & 1, a.err, ERR_DRAIN);
     }
     tma_store_wait<0>();
 }
 
 // ---- the warps that compute --------------------------------------------------------------------------
-__device__ __forceinline__ void consumer_warps(FusedSmem &sm, const FusedArgs &a, int rank, int cluster_id,
+template <class K>
+__device__ __forceinline__ void consumer_warps(FusedSmem<K> &sm, const FusedArgs &a, int rank, int cluster_id,
                                                int nclusters, int ncols, int mych, int row_base)
 {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, grp = warp >> 3, w8 = warp & 7;
@@ -172,7 +197,7 @@ __device__ __forceinline__ void consumer_warps(FusedSmem &sm, const FusedArgs &a
     volatile int *abort_flag = &sm.abort_flag;
 
     for (int j = 0; j < ncols; ++j) {
-        if (consumer_bar_or(*abort_flag != 0)) break;          // the same answer in every consumer thread
+        if (consumer_bar_or_t<K>(*abort_flag != 0)) break;          // the same answer in every consumer thread
         const int b = cluster_id + j * nclusters;
         const int mb = j & 1;
         if (tid == 0) {
@@ -184,7 +209,7 @@ __device__ __forceinline__ void consumer_warps(FusedSmem &sm, const FusedArgs &a
         unsigned short next_mask[3];
 #pragma unroll
         for (int i = 0; i < 3; ++i) {
-            const int r = tid + i * (NCW * 32);
+            const int r = tid + i * (K::NCW * 32);
             const bool ok = (j + 1 < ncols) && r < mych * CH_ROWS && row_base + r < S;
             next_mask[i] = ok ? __ldg(mask_bits + (int64_t)(b + nclusters) * S + row_base + r) : (unsigned short)0;
         }
@@ -194,10 +219,10 @@ __device__ __forceinline__ void consumer_warps(FusedSmem &sm, const FusedArgs &a
             float pacc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
             float pms = 0.f;
             const int sub = lane & 7, r4 = lane >> 3;
-            for (int c = grp; c < mych; c += 2) {
-                const int seq = j * mych + c, s = seq % NSLOT;
+            for (int c = grp; c < mych; c += K::NPG) {
+                const int seq = j * mych + c, s = seq % K::NSLOT;
                 if (!__any_sync(0xffffffffu, *abort_flag != 0) &&
-                    !mbar_wait_warp(smem_u32(&sm.full[s]), (seq / NSLOT) & 1, a.err, ERR_FULL))
+                    !mbar_wait_warp(smem_u32(&sm.full[s]), (seq / K::NSLOT) & 1, a.err, ERR_FULL))
                     *abort_flag = 1;
                 const uint32_t tile = slot0 + s * CH_BYTES + w8 * 16 * 128;
 #pragma unroll
@@ -231,14 +256,14 @@ __device__ __forceinline__ void consumer_warps(FusedSmem &sm, const FusedArgs &a
         }
 #pragma unroll
         for (int i = 0; i < 3; ++i) {
-            const int r = tid + i * (NCW * 32);
-            if (r < MAX_ROWS) sm.mask[mb ^ 1][r] = next_mask[i];
+            const int r = tid + i * (K::NCW * 32);
+            if (r < K::MAX_ROWS) sm.mask[mb ^ 1][r] = next_mask[i];
         }
-        consumer_bar();
+        consumer_bar_t<K>();
         if (tid <= FC) {
             float tsum = 0.f;
 #pragma unroll
-            for (int w = 0; w < NCW; ++w) tsum += sm.red[w][tid];
+            for (int w = 0; w < K::NCW; ++w) tsum += sm.red[w][tid];
             // asynchronous stores: each word credits 4 bytes to the destination CTA's barrier when it lands
             const uint32_t local = smem_u32(&sm.pool_part[rank][tid]), bar = smem_u32(&sm.pool_bar);
             for (int r = 0; r < a.ncta; ++r)
@@ -256,10 +281,14 @@ __device__ __forceinline__ void consumer_warps(FusedSmem &sm, const FusedArgs &a
             }
             sm.qa[tid] = rbf(tsum * (1.0f / (ms + 1e-10f)));
         }
-        consumer_bar();
-        {
-            const int o = tid >> 3, part = tid & 7;
-            const uint4 raw = *reinterpret_cast<const uint4 *>(&sm.wq[o * FC + ((part ^ (o & 7)) << 3)]);
+        consumer_bar_t<K>();
+        for (int o = tid >> 3; o < FC; o += K::NCW * 4) {
+            const int part = tid & 7;
+            uint4 raw;
+            if (K::WQ_SMEM)
+                raw = *reinterpret_cast<const uint4 *>(&sm.wq[o * FC + ((part ^ (o & 7)) << 3)]);
+            else
+                raw = __ldg(reinterpret_cast<const uint4 *>(a.wq + o * FC) + part);
             const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
             float acc = 0.f;
 #pragma unroll
@@ -272,7 +301,7 @@ __device__ __forceinline__ void consumer_warps(FusedSmem &sm, const FusedArgs &a
             acc += __shfl_xor_sync(0xffffffffu, acc, 4);
             if (part == 0) sm.q[o] = rbf(acc);
         }
-        consumer_bar();
+        consumer_bar_t<K>();
 
         // ---- core: thread (g, t) owns head g; four products chained through mma.sync fragments:
         //   k [16 x 8] = x.Wk^T, v^T [8 x 16] = Wv.x^T, logits^T [8 heads x 16] = q.k^T, wa [8 x 8] += P^T.v
@@ -288,17 +317,17 @@ __device__ __forceinline__ void consumer_warps(FusedSmem &sm, const FusedArgs &a
             const uint32_t aq = pack_bf16x2(sm.q[g * FD + 2 * t], sm.q[g * FD + 2 * t + 1]);
             float m_run = -INFINITY, l_run = 0.f, wa[4] = {0.f, 0.f, 0.f, 0.f};
             // CT tiles per step (independent chains of products in flight)
-            for (int c = grp; c < mych; c += 2 * CT) {
+            for (int c = grp; c < mych; c += K::NPG * CT) {
                 int loc0[CT];
                 bool valid[CT];
                 uint32_t tile[CT];
 #pragma unroll
                 for (int u = 0; u < CT; ++u) {
-                    const int cu = c + 2 * u;
+                    const int cu = c + K::NPG * u;
                     loc0[u] = cu * CH_ROWS + w8 * 16;            // first row of the tile within this CTA's slab
                     valid[u] = cu < mych && row_base + loc0[u] < S;
                     const int sq = j * mych + (valid[u] ? cu : c);
-                    tile[u] = slot0 + (sq % NSLOT) * CH_BYTES + w8 * 16 * 128;
+                    tile[u] = slot0 + (sq % K::NSLOT) * CH_BYTES + w8 * 16 * 128;
                 }
                 if (!valid[0]) continue;
                 float kacc[CT][4], v0[CT][4], v1[CT][4];
@@ -368,15 +397,15 @@ __device__ __forceinline__ void consumer_warps(FusedSmem &sm, const FusedArgs &a
             sm.s_part[warp][g][1 + 2 * t] = wa[0];
             sm.s_part[warp][g][2 + 2 * t] = wa[1];
         }
-        consumer_bar();
+        consumer_bar_t<K>();
         if (tid < FH * (1 + FD)) {
             const int h = tid / (1 + FD), jj = tid % (1 + FD);
             float mx = sm.s_m[0][h];
 #pragma unroll
-            for (int w = 1; w < NCW; ++w) mx = fmaxf(mx, sm.s_m[w][h]);
+            for (int w = 1; w < K::NCW; ++w) mx = fmaxf(mx, sm.s_m[w][h]);
             float acc = 0.f;
 #pragma unroll
-            for (int w = 0; w < NCW; ++w) {
+            for (int w = 0; w < K::NCW; ++w) {
                 const float f = (sm.s_m[w][h] == -INFINITY) ? 0.f : __expf(sm.s_m[w][h] - mx);
                 acc += sm.s_part[w][h][jj] * f;
             }
@@ -403,7 +432,7 @@ __device__ __forceinline__ void consumer_warps(FusedSmem &sm, const FusedArgs &a
             }
             sm.hwa[tid] = 0.5f * rbf(av / l);
         }
-        consumer_bar();
+        consumer_bar_t<K>();
 
         // ---- out: both 64 x 64 products run on tcgen05 (issued by the MMA warp). Chunk `seq` uses TMEM
         // accumulator seq % 4 and is finished by the four warps of group seq % 4, one row per thread:
@@ -415,8 +444,8 @@ __device__ __forceinline__ void consumer_warps(FusedSmem &sm, const FusedArgs &a
             const uint32_t tmem_lane = sm.tmem_base + ((uint32_t)(quarter * 32) << 16);
             // first half of a chunk's epilogue: gate -> gated rows, written over x
             auto gate_rows = [&](int seq) {
-                const int k = seq & (NACC - 1), s = seq % NSLOT;
-                const uint32_t par = (uint32_t)(seq / NACC) & 1u;
+                const int k = seq & (K::NACC - 1), s = seq % K::NSLOT;
+                const uint32_t par = (uint32_t)(seq / K::NACC) & 1u;
                 const uint32_t rowaddr = slot0 + s * CH_BYTES + row * 128;
                 const uint32_t taddr = tmem_lane + (uint32_t)(k * FC);
                 if (!__any_sync(0xffffffffu, *abort_flag != 0) &&
@@ -463,8 +492,8 @@ __device__ __forceinline__ void consumer_warps(FusedSmem &sm, const FusedArgs &a
             };
             // second half: out rows, written over the gated rows, then handed to the TMA store
             auto out_rows = [&](int seq) {
-                const int k = seq & (NACC - 1), s = seq % NSLOT;
-                const uint32_t par = (uint32_t)(seq / NACC) & 1u;
+                const int k = seq & (K::NACC - 1), s = seq % K::NSLOT;
+                const uint32_t par = (uint32_t)(seq / K::NACC) & 1u;
                 const uint32_t rowaddr = slot0 + s * CH_BYTES + row * 128;
                 const uint32_t taddr = tmem_lane + (uint32_t)(k * FC);
                 if (!__any_sync(0xffffffffu, *abort_flag != 0) &&
@@ -508,10 +537,10 @@ __device__ __forceinline__ void consumer_warps(FusedSmem &sm, const FusedArgs &a
             // this group's chunks of the column: seq = eg (mod 4). The gate of the next one is computed
             // while the tensor core forms the output product of the current one.
             const int seq0 = j * mych;
-            int c = (eg - seq0) & (NGRP - 1);
+            int c = (eg - seq0) & (K::NGRP - 1);
             if (c < mych) gate_rows(seq0 + c);
-            for (; c < mych; c += NGRP) {
-                if (c + NGRP < mych) gate_rows(seq0 + c + NGRP);
+            for (; c < mych; c += K::NGRP) {
+                if (c + K::NGRP < mych) gate_rows(seq0 + c + K::NGRP);
                 out_rows(seq0 + c);
             }
         }
@@ -521,7 +550,8 @@ __device__ __forceinline__ void consumer_warps(FusedSmem &sm, const FusedArgs &a
 // ---- the thread that issues the tensor-core products of the output stage ---------------------------------
 // In chunk order: D[seq % 4] = x.Wg^T as soon as the chunk has landed and the accumulator is free, then,
 // three chunks behind, D[seq' % 4] = gated.Wo^T once the warps have written the gated rows.
-__device__ __forceinline__ void mma_thread(FusedSmem &sm, const FusedArgs &a, int ncols, int mych)
+template <class K>
+__device__ __forceinline__ void mma_thread(FusedSmem<K> &sm, const FusedArgs &a, int ncols, int mych)
 {
     const uint32_t slot0 = smem_u32(&sm.slot[0][0]);
     const uint32_t wg_addr = smem_u32(&sm.wg[0]), wo_addr = smem_u32(&sm.wo[0]);
@@ -533,9 +563,9 @@ __device__ __forceinline__ void mma_thread(FusedSmem &sm, const FusedArgs &a, in
     while (b_seq < total) {
         bool progress = false;
         if (a_seq < total) {
-            const int k = a_seq & (NACC - 1), u = a_seq / NACC, s = a_seq % NSLOT;
+            const int k = a_seq & (K::NACC - 1), u = a_seq / K::NACC, s = a_seq % K::NSLOT;
             if ((u == 0 || mbar_try_wait(smem_u32(&sm.d_free[k]), (uint32_t)(u - 1) & 1u)) &&
-                mbar_try_wait(smem_u32(&sm.full[s]), (uint32_t)(a_seq / NSLOT) & 1u)) {
+                mbar_try_wait(smem_u32(&sm.full[s]), (uint32_t)(a_seq / K::NSLOT) & 1u)) {
                 tc_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < FC / 16; ++ks)
@@ -547,8 +577,8 @@ __device__ __forceinline__ void mma_thread(FusedSmem &sm, const FusedArgs &a, in
             }
         }
         if (b_seq < a_seq) {
-            const int k = b_seq & (NACC - 1), s = b_seq % NSLOT;
-            if (mbar_try_wait(smem_u32(&sm.p_ready[k]), (uint32_t)(b_seq / NACC) & 1u)) {
+            const int k = b_seq & (K::NACC - 1), s = b_seq % K::NSLOT;
+            if (mbar_try_wait(smem_u32(&sm.p_ready[k]), (uint32_t)(b_seq / K::NACC) & 1u)) {
                 tc_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < FC / 16; ++ks)
@@ -569,12 +599,13 @@ __device__ __forceinline__ void mma_thread(FusedSmem &sm, const FusedArgs &a, in
     }
 }
 
-__global__ void __launch_bounds__(NTHREADS, 1)
+template <class K>
+__global__ void __launch_bounds__(K::BOUND_THREADS, K::MIN_CTAS)
 global_fused_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap omap,
                     const FusedArgs a)
 {
     extern __shared__ unsigned char smem_raw[];
-    FusedSmem &sm = *reinterpret_cast<FusedSmem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    FusedSmem<K> &sm = *reinterpret_cast<FusedSmem<K> *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int rank = (int)cluster_cta_rank();
     const int cluster_id = blockIdx.x / a.ncta, nclusters = gridDim.x / a.ncta;
@@ -583,11 +614,11 @@ global_fused_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
     const int ncols = cluster_id < a.B ? (a.B - cluster_id + nclusters - 1) / nclusters : 0;
 
     if (tid == 0) {
-        for (int s = 0; s < NSLOT; ++s) {
+        for (int s = 0; s < K::NSLOT; ++s) {
             mbar_init(smem_u32(&sm.full[s]), 1);
             mbar_init(smem_u32(&sm.done[s]), 4);
         }
-        for (int k = 0; k < NACC; ++k) {
+        for (int k = 0; k < K::NACC; ++k) {
             mbar_init(smem_u32(&sm.g1_done[k]), 1);
             mbar_init(smem_u32(&sm.p_ready[k]), 4);
             mbar_init(smem_u32(&sm.g2_done[k]), 1);
@@ -601,14 +632,14 @@ global_fused_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
         tma_prefetch_desc(&omap);
     }
     // weights, once per CTA: 16-byte chunks, swizzled by row for the three 64 x 64 matrices
-    for (int idx = tid; idx < FC * 8; idx += NTHREADS) {
+    for (int idx = tid; idx < FC * 8; idx += K::NTHREADS) {
         const int r = idx >> 3, c = idx & 7;
         const int dst = r * FC + ((c ^ (r & 7)) << 3);
         *reinterpret_cast<uint4 *>(&sm.wg[dst]) = __ldg(reinterpret_cast<const uint4 *>(a.wg + r * FC) + c);
         *reinterpret_cast<uint4 *>(&sm.wo[dst]) = __ldg(reinterpret_cast<const uint4 *>(a.wo + r * FC) + c);
-        *reinterpret_cast<uint4 *>(&sm.wq[dst]) = __ldg(reinterpret_cast<const uint4 *>(a.wq + r * FC) + c);
+        if (K::WQ_SMEM) *reinterpret_cast<uint4 *>(&sm.wq[dst]) = __ldg(reinterpret_cast<const uint4 *>(a.wq + r * FC) + c);
     }
-    for (int idx = tid; idx < FD * FC; idx += NTHREADS) {
+    for (int idx = tid; idx < FD * FC; idx += K::NTHREADS) {
         sm.wk[idx] = a.wk[idx];
         sm.wv[idx] = a.wv[idx];
     }
@@ -618,13 +649,13 @@ global_fused_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
     }
     if (ncols > 0) {
         const unsigned short *mask_bits = reinterpret_cast<const unsigned short *>(a.mask);
-        for (int r = tid; r < MAX_ROWS; r += NTHREADS) {
+        for (int r = tid; r < K::MAX_ROWS; r += K::NTHREADS) {
             const bool ok = r < mych * CH_ROWS && row_base + r < a.S;
             sm.mask[0][r] = ok ? mask_bits[(int64_t)cluster_id * a.S + row_base + r] : (unsigned short)0;
         }
     }
-    if (warp == MMA_WARP) {
-        tmem_alloc(smem_u32(&sm.tmem_base), TMEM_COLS);
+    if (warp == K::MMA_WARP) {
+        tmem_alloc(smem_u32(&sm.tmem_base), K::TMEM_COLS);
         tmem_relinquish();
     }
     tc_fence_before();
@@ -632,20 +663,109 @@ global_fused_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
     tc_fence_after();
     cluster_barrier_all();          // every CTA's barriers exist before a peer arrives on them
 
-    if (warp == IO_WARP) {
-        if (lane == 0) io_thread(sm, &xmap, &omap, a, cluster_id, nclusters, ncols, mych, row_base);
-    } else if (warp == MMA_WARP) {
-        if (lane == 0) mma_thread(sm, a, ncols, mych);
+    if (warp == K::IO_WARP) {
+        if (lane == 0) io_thread<K>(sm, &xmap, &omap, a, cluster_id, nclusters, ncols, mych, row_base);
+    } else if (warp == K::MMA_WARP) {
+        if (lane == 0) mma_thread<K>(sm, a, ncols, mych);
     } else {
-        consumer_warps(sm, a, rank, cluster_id, nclusters, ncols, mych, row_base);
+        consumer_warps<K>(sm, a, rank, cluster_id, nclusters, ncols, mych, row_base);
     }
     tc_fence_before();
     __syncthreads();                // every tcgen05.ld and every product has been waited for by now
-    if (warp == MMA_WARP) {
+    if (warp == K::MMA_WARP) {
         tc_fence_after();
-        tmem_dealloc(sm.tmem_base, TMEM_COLS);
+        tmem_dealloc(sm.tmem_base, K::TMEM_COLS);
     }
     cluster_barrier_all();          // no CTA leaves while a peer may still write into its shared memory
+}
+
+// The occupancy calculator answers "one CTA per SM" for every kernel that allocates tensor memory, although
+// two such CTAs do share an SM when their columns fit (measured). This empty kernel with the same block
+// size, dynamic shared memory and residency bound stands in for the real one in the cluster-occupancy
+// query; the real kernel's registers (at most 96 x 576 or 80 x 320 x 2 threads) fit the register file.
+template <class K>
+__global__ void __launch_bounds__(K::BOUND_THREADS, K::MIN_CTAS) occupancy_twin_kernel(int *p)
+{
+    extern __shared__ unsigned char twin_smem[];
+    if (p) p[threadIdx.x] = twin_smem[threadIdx.x];
+}
+
+// Launch with configuration K; ncta CTAs per cluster, nch slots per CTA and column.
+template <class K>
+bool launch_fused(cudaStream_t stream, const void *x, const void *out, int64_t out_row_stride, FusedArgs a)
+{
+    const int smem_bytes = (int)sizeof(FusedSmem<K>) + 1024;
+    static bool attr_set[64] = {};
+    static int max_clusters[64][MAX_CTA + 1] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+    if (!attr_set[dev]) {
+        if (cudaFuncSetAttribute(global_fused_kernel<K>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) !=
+            cudaSuccess) {
+            cudaGetLastError();
+            return false;
+        }
+        // two CTAs of the Half shape fill the SM's shared memory exactly: ask for the largest carve-out
+        cudaFuncSetAttribute(global_fused_kernel<K>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                             cudaSharedmemCarveoutMaxShared);
+        cudaGetLastError();
+        attr_set[dev] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)a.ncta;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.blockDim = dim3(K::NTHREADS);
+    cfg.dynamicSmemBytes = (size_t)smem_bytes;
+    cfg.stream = stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (max_clusters[dev][a.ncta] == 0) {
+        cfg.gridDim = dim3((unsigned)(a.ncta * 64));
+        int n = 0;
+        if (cudaFuncSetAttribute(occupancy_twin_kernel<K>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) !=
+                cudaSuccess ||
+            cudaOccupancyMaxActiveClusters(&n, occupancy_twin_kernel<K>, &cfg) != cudaSuccess || n < 1) {
+            cudaGetLastError();
+            max_clusters[dev][a.ncta] = -1;
+        } else {
+            max_clusters[dev][a.ncta] = n;
+        }
+    }
+    if (max_clusters[dev][a.ncta] < 1) return false;
+    const int nclusters = std::min(a.B, max_clusters[dev][a.ncta]);
+    cfg.gridDim = dim3((unsigned)(nclusters * a.ncta));
+
+    CUtensorMap xmap, omap;
+    if (!make_tensor_map_bf16_3d(&xmap, x, FC, (uint64_t)a.S, (uint64_t)a.B, FC, (uint64_t)a.S * FC, FC, CH_ROWS, 128))
+        return false;
+    if (!make_tensor_map_bf16_3d(&omap, out, FC, (uint64_t)a.S, (uint64_t)a.B, (uint64_t)out_row_stride,
+                                 (uint64_t)a.S * (uint64_t)out_row_stride, FC, CH_ROWS, 128))
+        return false;
+    {
+        KernelTimer timer__("global_fused");
+        const cudaError_t e = cudaLaunchKernelEx(&cfg, global_fused_kernel<K>, xmap, omap, a);
+        KUTACC_CHECK(e == cudaSuccess, "global_fused_kernel launch failed: ", cudaGetErrorString(e));
+        if (e != cudaSuccess) return false;
+    }
+    count_launch(1);
+    return true;
+}
+
+// smallest power-of-two cluster whose CTAs hold a column in at most `max_per` slots each
+bool pick_cluster(int chunks, int max_per, int *ncta, int *nch)
+{
+    for (int n = 1; n <= MAX_CTA; n *= 2) {
+        const int per = (chunks + n - 1) / n;
+        if (per <= max_per) {
+            *ncta = n;
+            *nch = per;
+            return true;
+        }
+    }
+    return false;
 }
 
 }  // namespace
@@ -659,63 +779,6 @@ bool launch_global_fused_bf16(cudaStream_t stream, const void *x, const void *ma
     if (H != FH || D != FD || B < 1 || S < 1 || (out_row_stride % 8) != 0 || out_row_stride < FC) return false;
     if ((((uintptr_t)x | (uintptr_t)out | (uintptr_t)wq | (uintptr_t)wg | (uintptr_t)wo) & 15u) != 0) return false;
     if ((((uintptr_t)wk | (uintptr_t)wv) & 3u) != 0) return false;
-    // cluster size from S alone, so that a column is partitioned the same way in every batch
-    const int chunks = (S + CH_ROWS - 1) / CH_ROWS;
-    int ncta = 0, nch = 0;
-    for (int n = 1; n <= MAX_CTA; n *= 2) {
-        const int per = (chunks + n - 1) / n;
-        if (per <= NSLOT - 1 || (n == MAX_CTA && per <= NSLOT)) {
-            ncta = n;
-            nch = per;
-            break;
-        }
-    }
-    if (ncta == 0) return false;
-
-    const int smem_bytes = (int)sizeof(FusedSmem) + 1024;
-    static bool attr_set[64] = {};
-    static int max_clusters[64][MAX_CTA + 1] = {};
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
-    if (!attr_set[dev]) {
-        if (cudaFuncSetAttribute(global_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) !=
-            cudaSuccess) {
-            cudaGetLastError();
-            return false;
-        }
-        attr_set[dev] = true;
-    }
-    cudaLaunchConfig_t cfg = {};
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = (unsigned)ncta;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.blockDim = dim3(NTHREADS);
-    cfg.dynamicSmemBytes = (size_t)smem_bytes;
-    cfg.stream = stream;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    if (max_clusters[dev][ncta] == 0) {
-        cfg.gridDim = dim3((unsigned)(ncta * 64));
-        int n = 0;
-        if (cudaOccupancyMaxActiveClusters(&n, global_fused_kernel, &cfg) != cudaSuccess || n < 1) {
-            cudaGetLastError();
-            max_clusters[dev][ncta] = -1;
-        } else {
-            max_clusters[dev][ncta] = n;
-        }
-    }
-    if (max_clusters[dev][ncta] < 1) return false;
-    const int nclusters = std::min(B, max_clusters[dev][ncta]);
-    cfg.gridDim = dim3((unsigned)(nclusters * ncta));
-
-    CUtensorMap xmap, omap;
-    if (!make_tensor_map_bf16_3d(&xmap, x, FC, (uint64_t)S, (uint64_t)B, FC, (uint64_t)S * FC, FC, CH_ROWS, 128))
-        return false;
-    if (!make_tensor_map_bf16_3d(&omap, out, FC, (uint64_t)S, (uint64_t)B, (uint64_t)out_row_stride,
-                                 (uint64_t)S * (uint64_t)out_row_stride, FC, CH_ROWS, 128))
-        return false;
     FusedArgs a;
     a.mask = (const __nv_bfloat16 *)mask;
     a.wq = (const __nv_bfloat16 *)wq;
@@ -727,17 +790,14 @@ bool launch_global_fused_bf16(cudaStream_t stream, const void *x, const void *ma
     a.bo = bo;
     a.B = B;
     a.S = S;
-    a.ncta = ncta;
-    a.nch = nch;
     a.err = kernel_error_word().device;
-    {
-        KernelTimer timer__("global_fused");
-        const cudaError_t e = cudaLaunchKernelEx(&cfg, global_fused_kernel, xmap, omap, a);
-        KUTACC_CHECK(e == cudaSuccess, "global_fused_kernel launch failed: ", cudaGetErrorString(e));
-        if (e != cudaSuccess) return false;
-    }
-    count_launch(1);
-    return true;
+    // The cluster shape depends on S alone, so that a column is partitioned the same way in every batch.
+    const int chunks = (S + CH_ROWS - 1) / CH_ROWS;
+    if (pick_cluster(chunks, HalfCfg::NSLOT, &a.ncta, &a.nch))
+        return launch_fused<HalfCfg>(stream, x, out, out_row_stride, a);
+    if (pick_cluster(chunks, WideCfg::NSLOT, &a.ncta, &a.nch))
+        return launch_fused<WideCfg>(stream, x, out, out_row_stride, a);
+    return false;
 }
 
 }  // namespace dev
