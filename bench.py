@@ -192,6 +192,71 @@ def run_reference_arm(args):
     return 0
 
 
+def run_strong_scaling(args, torch, dist, api, W, dev, world, rank, local_rank):
+    """One triangle-attention problem split over the ranks: pair-bias projection, bias all-gather, attention
+    on this rank's rows, output all-gather (kutacc_b200/sharding.py). Total work is fixed as N grows."""
+    from kutacc_b200 import sharding
+    w = W.make(args.workload)
+    if not (w.kind == "gating" and w.has_nb and "z" in w.arrays and w.B == w.S):
+        raise SystemExit("--scaling strong needs a triangle workload (triangle_start_384, triangle_end_1024)")
+    if world > 1:
+        uid = torch.zeros(128, dtype=torch.uint8, device=dev)
+        if rank == 0:
+            uid = torch.tensor(list(api.comm_unique_id()), dtype=torch.uint8, device=dev)
+        dist.broadcast(uid, 0)
+        api.comm_init(world, rank, 0, bytes(uid.cpu().tolist()))
+    op = sharding.ShardedTriangleAttention(w, rank, world, args.slabs, dev, sm_margin=args.sm_margin)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        op.step()
+    barrier()
+    launches0 = api.launch_count()
+    step_ms = []
+    with ClockSampler(local_rank) as clocks:
+        for _ in range(args.steps):
+            flush.zero_()
+            barrier()                                                 # ranks enter the step together
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            op.step()
+            e1.record()
+            e1.synchronize()
+            step_ms.append(e0.elapsed_time(e1))
+        barrier()
+    launches = api.launch_count() - launches0
+    t = torch.tensor(step_ms, dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)                      # per step, the slowest rank
+    ms_per_step = float(t.sum().item()) / args.steps
+    value = w.flops() / (ms_per_step * 1e-3) / 1e12
+    checksum = float(op.out_full.float().abs().mean().item())
+    if world > 1:
+        api.comm_fini()
+    if rank == 0:
+        peaks = measured_peaks()
+        print(json.dumps({
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": w.dtype, "data": "synthetic (seeded numpy, AlphaFold2 model shapes)",
+            "config": {"workload": args.workload, "B": w.B, "S": w.S, "H": w.H, "D": w.D, "C": w.C, "pair_bias": True,
+                       "gflop_per_call": w.flops() / 1e9, "slabs": args.slabs, "sm_margin": op.sm_margin,
+                       "l2": "flushed between timed steps (256 MiB memset)",
+                       "parallelism": f"rows of one problem over {world} GPU(s); NCCL all-gather of the projected "
+                                      f"pair bias and of the output rows, output gather overlapped slab by slab"},
+            "frac_of_bf16_peak": value / world / peaks["bf16_tflops"],
+            "roofline": None, "cpu_baseline": None, "e2e": None, "gpu_launches": int(launches),
+            "result_mean_abs": checksum, "clocks": clocks.summary(),
+        }))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -204,6 +269,11 @@ def main():
     ap.add_argument("--rows", type=int, default=0,
                     help="profiling aid: run only this many of the workload's batch rows (0 = all); the JSON "
                          "line then describes that smaller case and is not a benchmark result")
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
+                    help="weak (default): every rank runs the whole workload on its own rows, no collective; "
+                         "strong: one triangle workload split over the ranks with the two all-gathers")
+    ap.add_argument("--sm-margin", type=int, default=8, help="strong scaling: SMs the kernels leave to NCCL")
+    ap.add_argument("--slabs", type=int, default=2, help="strong scaling: slabs the output gather is pipelined in")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -227,6 +297,12 @@ def main():
     if not os.path.exists(api.LIB_PATH):
         build.build()
     api.lib()
+
+    if args.scaling == "strong":
+        rc = run_strong_scaling(args, torch, dist, api, W, dev, world, rank, local_rank)
+        if world > 1:
+            dist.destroy_process_group()
+        return rc
 
     w = W.make(args.workload, rows=args.rows) if args.rows > 0 else W.make(args.workload)
     case = runner.DeviceCase(w, device=dev)

@@ -166,6 +166,11 @@ KUTACC_B200_API void kutacc_b200_clear_error(void);
  * calls with device-resident tensors only enqueue work on the stream. */
 KUTACC_B200_API void kutacc_b200_set_stream(void *cuda_stream);
 KUTACC_B200_API void kutacc_b200_set_async(int enabled);
+/* The persistent kernels (projections, attention core) normally fill every SM. A caller that runs a
+ * collective on another stream beside them (the output all-gather of one slab of rows while the next
+ * slab is computed) can ask them to leave `sms` SMs free, 0..64, so that the collective's CTAs find room
+ * at once instead of waiting for the persistent CTAs to finish. Default 0. */
+KUTACC_B200_API void kutacc_b200_set_sm_margin(int sms);
 KUTACC_B200_API void kutacc_b200_synchronize(void);
 
 /* Device memory helpers for callers without a CUDA runtime of their own. */

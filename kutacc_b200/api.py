@@ -28,7 +28,7 @@ EXPORTS = [
     "kutacc_af2_linear_weight_prepack", "kutacc_af2_gemm_pack_get_size",
     # part 2: additions
     "kutacc_b200_tensor_create", "kutacc_b200_tensor_destroy", "kutacc_b200_error_set", "kutacc_b200_last_error",
-    "kutacc_b200_clear_error", "kutacc_b200_set_stream", "kutacc_b200_set_async", "kutacc_b200_synchronize",
+    "kutacc_b200_clear_error", "kutacc_b200_set_stream", "kutacc_b200_set_async", "kutacc_b200_set_sm_margin", "kutacc_b200_synchronize",
     "kutacc_b200_device_malloc", "kutacc_b200_device_free", "kutacc_b200_memcpy_h2d", "kutacc_b200_memcpy_d2h",
     "kutacc_b200_workspace_bytes", "kutacc_b200_release_workspace", "kutacc_b200_launch_count",
     "kutacc_b200_set_profile", "kutacc_b200_profile_read", "kutacc_b200_comm_unique_id", "kutacc_b200_comm_init_with_id", "kutacc_b200_pair_bias",
@@ -100,6 +100,8 @@ def lib() -> C.CDLL:
     L.kutacc_b200_set_stream.restype = None
     L.kutacc_b200_set_async.argtypes = [C.c_int]
     L.kutacc_b200_set_async.restype = None
+    L.kutacc_b200_set_sm_margin.argtypes = [C.c_int]
+    L.kutacc_b200_set_sm_margin.restype = None
     L.kutacc_b200_synchronize.restype = None
     L.kutacc_b200_device_malloc.argtypes = [C.c_size_t]
     L.kutacc_b200_device_malloc.restype = vp
@@ -182,6 +184,10 @@ def set_stream(stream_ptr: int) -> None:
 
 def set_async(enabled: bool) -> None:
     lib().kutacc_b200_set_async(1 if enabled else 0)
+
+
+def set_sm_margin(sms: int) -> None:
+    lib().kutacc_b200_set_sm_margin(int(sms))
 
 
 def synchronize() -> None:

@@ -71,6 +71,7 @@ namespace kutacc {
 struct Runtime {
     void *stream = nullptr;   // cudaStream_t
     bool async = false;
+    int sm_margin = 0;        // SMs the persistent kernels leave free (for a collective running beside them)
 
     char *ws_base = nullptr;
     size_t ws_cap = 0, ws_off = 0;

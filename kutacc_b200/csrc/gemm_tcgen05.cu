@@ -314,7 +314,7 @@ bool launch(cudaStream_t stream, const GemmMaps &maps, const GemmParams &p, cons
     }
     const int s_tiles = (p.S + BM - 1) / BM;
     const int64_t tiles = (int64_t)p.B * s_tiles * (p.seg_n / BN) * p.nseg;
-    const unsigned grid = (unsigned)std::min<int64_t>(tiles, sm_count());
+    const unsigned grid = (unsigned)std::min<int64_t>(tiles, std::max(1, sm_count() - runtime().sm_margin));
     KernelTimer timer__(name);
     gemm_tcgen05_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(maps, p);
     count_launch();

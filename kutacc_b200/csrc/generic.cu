@@ -282,6 +282,88 @@ __global__ void __launch_bounds__(256) pair_bias_vec_kernel(const __nv_bfloat16 
     }
 }
 
+// bf16 pair bias on tensor cores: a CTA streams 128-position tiles of z through a cp.async ring (16-byte
+// chunks, swizzled by row), each warp multiplies its 16 positions by Wb^T (heads padded to 8) with
+// mma.sync m16n8k16 and writes nb[h, pos]. Bandwidth bound: z is read once, 128-bit loads.
+template <int CZ>
+__global__ void __launch_bounds__(256) pair_bias_mma_kernel(const __nv_bfloat16 *__restrict__ z,
+                                                            const __nv_bfloat16 *__restrict__ wb,
+                                                            __nv_bfloat16 *__restrict__ nb, int64_t nb_head_stride,
+                                                            int64_t total, int H)
+{
+    constexpr int ROWB = CZ * 2, CHUNKS = ROWB / 16, TP = 128, STAGES = 3, STAGE_BYTES = TP * ROWB;
+    extern __shared__ __align__(128) unsigned char pb_smem[];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    uint32_t bf[CZ / 16][2];
+#pragma unroll
+    for (int ks = 0; ks < CZ / 16; ++ks) {
+        bf[ks][0] = g < H ? *reinterpret_cast<const uint32_t *>(wb + g * CZ + ks * 16 + 2 * t) : 0u;
+        bf[ks][1] = g < H ? *reinterpret_cast<const uint32_t *>(wb + g * CZ + ks * 16 + 8 + 2 * t) : 0u;
+    }
+    const int64_t ntiles = (total + TP - 1) / TP;
+    const uint32_t smem0 = smem_u32(pb_smem);
+    auto load_tile = [&](int64_t tile, int stage) {
+        if (tile < ntiles) {
+#pragma unroll
+            for (int i = 0; i < TP * CHUNKS / 256; ++i) {
+                const int idx = tid + i * 256, r = idx / CHUNKS, c = idx % CHUNKS;
+                const int64_t pos = tile * TP + r;
+                const bool ok = pos < total;
+                cp_async16(smem0 + stage * STAGE_BYTES + r * ROWB + ((c ^ (r & 7)) << 4), z + (ok ? pos : 0) * CZ + c * 8,
+                           ok ? 16 : 0);
+            }
+        }
+        cp_async_commit();
+    };
+    int64_t tile = blockIdx.x;
+    for (int st = 0; st < STAGES - 1; ++st) load_tile(tile + (int64_t)st * gridDim.x, st);
+    for (int it = 0; tile < ntiles; tile += gridDim.x, ++it) {
+        cp_async_wait<STAGES - 2>();
+        __syncthreads();                       // tile `it` has landed; the stage refilled below is no longer read
+        load_tile(tile + (int64_t)(STAGES - 1) * gridDim.x, (it + STAGES - 1) % STAGES);
+        const uint32_t base = smem0 + (it % STAGES) * STAGE_BYTES + warp * 16 * ROWB;
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int ks = 0; ks < CZ / 16; ++ks) {
+            uint32_t a[4];
+            const int r = lane & 15, c = ks * 2 + (lane >> 4);
+            ldmatrix_x4(a[0], a[1], a[2], a[3], base + r * ROWB + ((c ^ (r & 7)) << 4));
+            mma_bf16_16816(acc, a, bf[ks][0], bf[ks][1]);
+        }
+        const int64_t p0 = tile * TP + warp * 16 + g, p1 = p0 + 8;
+        const int h0 = 2 * t, h1 = 2 * t + 1;
+        if (p0 < total) {
+            if (h0 < H) nb[h0 * nb_head_stride + p0] = __float2bfloat16_rn(acc[0]);
+            if (h1 < H) nb[h1 * nb_head_stride + p0] = __float2bfloat16_rn(acc[1]);
+        }
+        if (p1 < total) {
+            if (h0 < H) nb[h0 * nb_head_stride + p1] = __float2bfloat16_rn(acc[2]);
+            if (h1 < H) nb[h1 * nb_head_stride + p1] = __float2bfloat16_rn(acc[3]);
+        }
+    }
+    cp_async_wait<0>();
+}
+
+template <int CZ>
+bool launch_pair_bias_mma(cudaStream_t stream, const void *z, const void *wb, void *nb, int64_t nb_head_stride,
+                          int64_t total, int H)
+{
+    constexpr int SMEM = 3 * 128 * CZ * 2;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(pair_bias_mma_kernel<CZ>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) {
+            cudaGetLastError();
+            return false;
+        }
+        configured = true;
+    }
+    const int64_t ntiles = (total + 127) / 128;
+    const unsigned grid = (unsigned)std::min<int64_t>(ntiles, 148 * 2);
+    pair_bias_mma_kernel<CZ><<<grid, 256, SMEM, stream>>>((const __nv_bfloat16 *)z, (const __nv_bfloat16 *)wb,
+                                                          (__nv_bfloat16 *)nb, nb_head_stride, total, H);
+    return true;
+}
+
 }  // namespace
 
 bool launch_gemm_generic(cudaStream_t stream, ElemType t, const void *a, int64_t lda, const void *w, int64_t ldw,
@@ -347,6 +429,15 @@ bool launch_pair_bias(cudaStream_t stream, ElemType t, const void *z, const void
     const size_t smem = (size_t)H * Cz * 4;
     const int lanes = Cz / 8;
     const bool pow2 = lanes > 0 && (lanes & (lanes - 1)) == 0 && lanes <= 32 && Cz % 8 == 0;
+    if (t == kElemBF16 && H <= 8 && pos_stride == 1 && ((uintptr_t)z % 16) == 0 && ((uintptr_t)wb % 4) == 0 &&
+        (Cz == 128 || Cz == 64)) {
+        const bool ok = Cz == 128 ? launch_pair_bias_mma<128>(stream, z, wb, nb, nb_head_stride, pos, H)
+                                  : launch_pair_bias_mma<64>(stream, z, wb, nb, nb_head_stride, pos, H);
+        if (ok) {
+            count_launch();
+            return true;
+        }
+    }
     if (t == kElemBF16 && pow2 && H <= 8 && ((uintptr_t)z % 16) == 0) {
         const int64_t ppb = 256 / lanes;
         const unsigned gridv = (unsigned)std::min<int64_t>((pos + ppb - 1) / ppb, 148 * 32);

@@ -195,6 +195,7 @@ extern "C" {
 
 void kutacc_b200_set_stream(void *cuda_stream) { kutacc::runtime().stream = cuda_stream; }
 void kutacc_b200_set_async(int enabled) { kutacc::runtime().async = enabled != 0; }
+void kutacc_b200_set_sm_margin(int sms) { kutacc::runtime().sm_margin = sms < 0 ? 0 : (sms > 64 ? 64 : sms); }
 void kutacc_b200_synchronize(void) { KUTACC_CUDA(cudaStreamSynchronize((cudaStream_t)kutacc::runtime().stream)); }
 
 void *kutacc_b200_device_malloc(size_t bytes)

@@ -20,3 +20,117 @@ def row_range(x: int, world: int, rank: int) -> Tuple[int, int]:
     b = block(x, world)
     lo = min(x, rank * b)
     return lo, lo + chunk(x, world, rank)
+
+
+# ---------------------------------------------------------------------------------------------------
+# Triangle attention with its rows spread over several GPUs
+#
+# The operator itself never communicates (as in the reference, where the caller shards and gathers):
+# every rank projects the pair bias of the rows of z it holds, the ranks all-gather the bias
+# [H, N, N], every rank runs the gated attention on its rows against the whole bias, and the ranks
+# all-gather the output rows. To let the output gather of one part run while the next part is being
+# computed, the N rows are cut into `nslab` contiguous slabs and inside each slab rank r owns block r:
+# the gather of a slab is then a dense in-place all-gather, issued on its own stream.
+# ---------------------------------------------------------------------------------------------------
+def slab_plan(n_rows: int, world: int, nslab: int):
+    """[(slab_start, slab_rows, block_rows)] for each slab; every slab splits evenly over the ranks."""
+    if nslab < 1 or n_rows % (world * nslab) != 0:
+        raise ValueError(f"{n_rows} rows do not split into {nslab} slabs of {world} equal blocks")
+    slab_rows = n_rows // nslab
+    return [(c * slab_rows, slab_rows, slab_rows // world) for c in range(nslab)]
+
+
+def owned_rows(n_rows: int, world: int, rank: int, nslab: int):
+    """[(first_row, n)] of the rows rank `rank` owns, one entry per slab."""
+    return [(start + rank * blk, blk) for start, _, blk in slab_plan(n_rows, world, nslab)]
+
+
+class ShardedTriangleAttention:
+    """One rank's share of a triangle-attention workload (x = z, pair bias projected from z).
+
+    ``step()`` runs pair-bias projection -> bias all-gather -> per slab: attention, output all-gather
+    (the gather of slab c overlaps the attention of slab c + 1). After ``step()`` every rank holds the
+    whole output in ``out_full``. With world == 1 the gathers are skipped.
+    """
+
+    def __init__(self, w, rank: int, world: int, nslab: int, device, sm_margin: int = 8):
+        import numpy as np
+        import torch
+        from . import api
+        from .runner import _to_torch
+        assert w.kind == "gating" and w.has_nb and "z" in w.arrays and w.B == w.S, "needs a full triangle workload"
+        self.w, self.rank, self.world, self.device = w, rank, world, device
+        self.sm_margin = sm_margin if world > 1 else 0      # SMs left to the collective that runs beside the kernels
+        self.api = api
+        N, S, C, H = w.B, w.S, w.C, w.H
+        self.slabs = slab_plan(N, world, nslab)
+        self.mine = owned_rows(N, world, rank, nslab)
+        A = w.arrays
+        dt = api.DTYPE_BF16 if w.dtype == "bf16" else api.DTYPE_FP32
+        esz = 2 if w.dtype == "bf16" else 4
+        f = lambda a: _to_torch(a, w.dtype, device)
+        f32 = lambda a: _to_torch(a, "fp32", device)
+        # this rank's rows only (activations, mask bias); weights everywhere
+        self.x = [f(A["x"][r0:r0 + n]) for r0, n in self.mine]
+        self.bias = [f(A["bias"][r0:r0 + n]) for r0, n in self.mine]
+        self.wq, self.wk, self.wv, self.wg, self.wo = (f(A[k]) for k in ("wq", "wk", "wv", "wg", "wo"))
+        self.bg, self.bo = f32(A["bg"]), f32(A["bo"])
+        self.wb = f(np.ascontiguousarray(A["wb"].T))                                   # [H, c_z]
+        tdt = torch.bfloat16 if w.dtype == "bf16" else torch.float32
+        self.nb_full = torch.zeros((H, S, S), dtype=tdt, device=device)
+        self.out_full = torch.zeros((N, S, C), dtype=tdt, device=device)
+        self.weights = api.make_weights(C, H, w.D, self.wq, self.wk, self.wv, self.wg, self.bg, self.wo, self.bo)
+        self.t_wb = api.tensor(self.wb)
+        self.t_nb = api.tensor(self.nb_full)
+        self.parts = []
+        for (r0, n), (s0, srows, blk), x, bias in zip(self.mine, self.slabs, self.x, self.bias):
+            nb_rows = self.nb_full[:, r0:r0 + n, :]
+            out_rows = self.out_full[r0:r0 + n]
+            part = {
+                "inputs": api.make_inputs(n, S),
+                "t_x": api.tensor(x, sizes=[n * S, C], strides=[C, 1]),
+                "t_z": api.tensor(x),                                                   # z[q, k, :] = x[q, k, :]
+                "t_bias": api.tensor(bias),
+                "t_nb_rows": api.Tensor(nb_rows.data_ptr(), [H, n, S], [S * S, S, 1], dt, keep=self.nb_full),
+                "t_out_rows": api.Tensor(out_rows.data_ptr(), [n, S, C], [S * C, C, 1], dt, keep=self.out_full),
+                # byte views for the collectives: [m, n, len]
+                "g_nb_src": api.Tensor(nb_rows.data_ptr(), [H, n, S * esz], [S * S * esz, S * esz, 1], api.DTYPE_BF16,
+                                       keep=self.nb_full),
+                "g_nb_dst": api.Tensor(self.nb_full[:, s0:s0 + srows, :].data_ptr(), [H, srows, S * esz],
+                                       [S * S * esz, S * esz, 1], api.DTYPE_BF16, keep=self.nb_full),
+                "g_out_src": api.Tensor(out_rows.data_ptr(), [n, S, C * esz], [S * C * esz, C * esz, 1], api.DTYPE_BF16,
+                                        keep=self.out_full),
+                "g_out_dst": api.Tensor(self.out_full[s0:s0 + srows].data_ptr(), [srows, S, C * esz],
+                                        [S * C * esz, C * esz, 1], api.DTYPE_BF16, keep=self.out_full),
+            }
+            self.parts.append(part)
+        self.compute = torch.cuda.current_stream(device)
+        self.comm = torch.cuda.Stream(device=device)
+        self.events = [torch.cuda.Event() for _ in self.parts]
+
+    def step(self, block_size: int = 128):
+        api = self.api
+        api.set_async(True)
+        api.set_sm_margin(self.sm_margin)
+        try:
+            api.set_stream(self.compute.cuda_stream)
+            for p in self.parts:
+                api.pair_bias(p["t_z"], self.t_wb, p["t_nb_rows"])
+            if self.world > 1:
+                for p in self.parts:
+                    api.all_gather(p["g_nb_src"], p["g_nb_dst"])
+            for p, ev in zip(self.parts, self.events):
+                api.set_stream(self.compute.cuda_stream)
+                api.gating_attention(p["t_x"], p["inputs"], p["t_bias"], self.t_nb, self.weights, p["t_out_rows"],
+                                     block_size)
+                if self.world > 1:
+                    ev.record(self.compute)
+                    self.comm.wait_event(ev)
+                    api.set_stream(self.comm.cuda_stream)
+                    api.all_gather(p["g_out_src"], p["g_out_dst"])
+            self.compute.wait_stream(self.comm)
+        finally:
+            api.set_stream(self.compute.cuda_stream)
+            api.set_async(False)
+            api.set_sm_margin(0)
+        return self.out_full

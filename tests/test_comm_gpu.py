@@ -57,6 +57,56 @@ WORKER = textwrap.dedent("""
 """)
 
 
+SHARDED_WORKER = textwrap.dedent("""
+    import os, sys
+    import numpy as np, torch
+    sys.path.insert(0, {root!r})
+    from kutacc_b200 import api, sharding
+    from kutacc_b200 import workloads as W
+    rank, world = int(sys.argv[1]), int(sys.argv[2])
+    torch.cuda.set_device(rank)
+    dev = "cuda:%d" % rank
+    w = W.make("triangle_start_384", rows=128, seq=128)
+    alone = sharding.ShardedTriangleAttention(w, 0, 1, 1, dev).step().float().cpu().numpy()
+    torch.cuda.synchronize()
+    api.comm_init(world, rank, 0)
+    op = sharding.ShardedTriangleAttention(w, rank, world, 2, dev)
+    for _ in range(2):                      # the second step reuses every buffer
+        got = op.step().float().cpu().numpy()
+    torch.cuda.synchronize()
+    api.raise_if_error()
+    api.comm_fini()
+    # rows are independent and the kernels are the same: every rank holds the whole result, bit for bit
+    assert np.array_equal(got, alone), (rank, float(np.abs(got - alone).max()))
+    print("rank", rank, "ok")
+""")
+
+
+def _run_ranks(script, world, tag):
+    env = dict(os.environ, SHMID=f"kutacc_{tag}_{os.getpid()}", NCCL_NVLS_ENABLE="0", KUTACC_RENDEZVOUS_TIMEOUT_S="60")
+    procs = [subprocess.Popen([sys.executable, str(script), str(r), str(world)], env=env, stdout=subprocess.PIPE,
+                              stderr=subprocess.STDOUT, text=True) for r in range(world)]
+    outs = []
+    for p in procs:
+        try:
+            out, _ = p.communicate(timeout=240)
+        except subprocess.TimeoutExpired:
+            p.kill()
+            out, _ = p.communicate()
+        outs.append(out)
+    for r, (p, out) in enumerate(zip(procs, outs)):
+        assert p.returncode == 0, f"rank {r} failed:\n{out[-2000:]}"
+
+
+@pytest.mark.parametrize("world", [2])
+def test_sharded_triangle_attention_over_nccl(kutacc_lib, tmp_path, world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    script = tmp_path / "sharded_worker.py"
+    script.write_text(SHARDED_WORKER.format(root=ROOT))
+    _run_ranks(script, world, "sharded_test")
+
+
 @pytest.mark.parametrize("world", [2])
 def test_all_gather_over_nccl(kutacc_lib, tmp_path, world):
     if torch.cuda.device_count() < world:

@@ -141,3 +141,17 @@ def test_repeat_calls_are_deterministic(kutacc_lib):
     a = runner.out_to_f32(case.run()).copy()
     b = runner.out_to_f32(case.run()).copy()
     assert np.array_equal(a, b)
+
+
+def test_sharded_triangle_flow_on_one_rank_matches_the_plain_call(kutacc_lib):
+    # pair-bias projection + attention slab by slab (kutacc_b200/sharding.py) against one call with the
+    # workload's own pair bias; the two biases may differ in the last bf16 bit (fp32 summation order)
+    from kutacc_b200 import sharding
+    w = W.make("triangle_start_384", rows=128, seq=128)
+    want = runner.out_to_f32(runner.DeviceCase(w).run())
+    op = sharding.ShardedTriangleAttention(w, 0, 1, 2, "cuda:0")
+    got = runner.out_to_f32(op.step())
+    torch.cuda.synchronize()
+    api.raise_if_error()
+    assert helpers.rel_err(got, want) <= 2e-3
+    assert helpers.rel_err(got, helpers.oracle_faithful(w)) <= helpers.BF16_TOL

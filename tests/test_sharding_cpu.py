@@ -68,3 +68,18 @@ def test_gloo_grid_equals_reference_golden():
     lo0, hi0 = sharding.row_range(8, 2, 0)
     lo1, hi1 = sharding.row_range(8, 2, 1)
     assert np.array_equal(out[lo0:hi0], g["shard0"]) and np.array_equal(out[lo1:hi1], g["shard1"])
+
+
+def test_slab_plan_gives_every_row_to_exactly_one_rank():
+    from kutacc_b200 import sharding
+    for n, world, nslab in [(1024, 8, 2), (1024, 4, 4), (384, 2, 3), (128, 1, 2)]:
+        seen = []
+        for rank in range(world):
+            own = sharding.owned_rows(n, world, rank, nslab)
+            assert len(own) == nslab
+            for (r0, cnt), (s0, srows, blk) in zip(own, sharding.slab_plan(n, world, nslab)):
+                assert cnt == blk and s0 + rank * blk == r0 and r0 + cnt <= s0 + srows
+                seen += list(range(r0, r0 + cnt))
+        assert sorted(seen) == list(range(n))
+    with pytest.raises(ValueError):
+        sharding.slab_plan(1000, 8, 3)
