@@ -270,6 +270,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         const uint32_t t_lane = tmem_base + ((uint32_t)(quad * 32) << 16);
         const uint32_t o_col = t_lane + O_COL + half * O_STRIDE;
         const float scale = p.scale;
+        const uint64_t scale2 = pack_f32x2(scale, scale), log2e2 = pack_f32x2(kLog2e, kLog2e);
         bool ok = true;
         // per-thread shared-memory addresses of stage 0; other stages add a multiple of STAGE_BYTES
         const uint32_t st0 = smem + OFF_STAGE;
@@ -309,13 +310,14 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const int i0 = c * 8 + 2 * j;
-                    // the raw logit is stored as bf16 by the reference: one cvt gives its fp32 image
-                    float x0 = fmaf(round_to_bf16_f32(__uint_as_float(sr[i0])), scale, mbv[2 * j]);
-                    float x1 = fmaf(round_to_bf16_f32(__uint_as_float(sr[i0 + 1])), scale, mbv[2 * j + 1]);
-                    if (HAS_NB) {
-                        x0 += bf16lo_to_f32(nbw[j]);
-                        x1 += bf16hi_to_f32(nbw[j]);
-                    }
+                    // the raw logit is stored as bf16 by the reference: one cvt gives its fp32 image. The two
+                    // keys of a pair go through the packed fp32 pipe (one issue slot for both).
+                    uint64_t x2 = fma_f32x2(pack_f32x2(round_to_bf16_f32(__uint_as_float(sr[i0])),
+                                                       round_to_bf16_f32(__uint_as_float(sr[i0 + 1]))),
+                                            scale2, pack_f32x2(mbv[2 * j], mbv[2 * j + 1]));
+                    if (HAS_NB) x2 = add_f32x2(x2, pack_f32x2(bf16lo_to_f32(nbw[j]), bf16hi_to_f32(nbw[j])));
+                    float x0, x1;
+                    unpack_f32x2(x2, x0, x1);
                     sr[i0] = __float_as_uint(x0);
                     sr[i0 + 1] = __float_as_uint(x1);
                     tmax = fmax3(tmax, x0, x1);
@@ -327,9 +329,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const int i0 = c * 8 + 2 * j;
-                    const float p0 = ex2_approx(fmaf(__uint_as_float(sr[i0]), kLog2e, mneg));
-                    const float p1 = ex2_approx(fmaf(__uint_as_float(sr[i0 + 1]), kLog2e, mneg));
-                    w[j] = pack_bf16x2(p0, p1);
+                    float e0, e1;
+                    unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sr[i0]), __uint_as_float(sr[i0 + 1])), log2e2,
+                                           pack_f32x2(mneg, mneg)), e0, e1);
+                    w[j] = pack_bf16x2(ex2_approx(e0), ex2_approx(e1));
                 }
                 asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};\n" ::"r"(nb_addr[c] + soff), "r"(w[0]), "r"(w[1]),
                              "r"(w[2]), "r"(w[3])

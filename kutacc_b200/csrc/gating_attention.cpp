@@ -183,8 +183,21 @@ static void gating_attention_impl(Tensor &input, int64_t batch, int64_t seq_len,
         ok = run_rows(0, B);
         finish_out(d_out);
     } else {
-        const int nchunks = (int)std::min<int64_t>(8, B / 4);
-        const int64_t rows_per_chunk = (B + nchunks - 1) / nchunks;
+        // about 8 MiB of activations per chunk on average, between 2 and 12 chunks of at least 4 rows
+        int nchunks = (int)std::max<int64_t>(2, std::min<int64_t>(12, (int64_t)((x_bytes + ((size_t)4 << 20)) >> 23)));
+        nchunks = (int)std::max<int64_t>(1, std::min<int64_t>(nchunks, B / 4));
+        // Chunk i gets a share of the rows proportional to nchunks + 2 - i: the chunks shrink towards the end,
+        // because the kernels and the download of the last chunk are the part of the call nothing overlaps.
+        int64_t chunk_begin[17];
+        {
+            const int64_t wsum = (int64_t)nchunks * (nchunks + 5) / 2;      // sum of (nchunks + 2 - i), i = 0..nchunks-1
+            int64_t acc = 0;
+            for (int i = 0; i < nchunks; ++i) {
+                chunk_begin[i] = std::min<int64_t>(B, (acc * B + wsum / 2) / wsum);
+                acc += nchunks + 2 - i;
+            }
+            chunk_begin[nchunks] = B;
+        }
         CopyPipeline &cp = copy_pipeline(nchunks);
         if (kutacc_check_err_set) return;
         cudaStream_t s_in = (cudaStream_t)cp.in, s_out = (cudaStream_t)cp.out;
@@ -194,8 +207,8 @@ static void gating_attention_impl(Tensor &input, int64_t batch, int64_t seq_len,
         KUTACC_CUDA(cudaStreamWaitEvent(s_out, (cudaEvent_t)cp.start, 0));
         const size_t row_bytes = (size_t)S * C * es;
         for (int i = 0; i < nchunks && ok; ++i) {
-            const int64_t b0 = i * rows_per_chunk, nbr = std::min(rows_per_chunk, B - b0);
-            if (nbr <= 0) break;
+            const int64_t b0 = chunk_begin[i], nbr = chunk_begin[i + 1] - b0;
+            if (nbr <= 0) continue;
             KUTACC_CUDA(cudaMemcpyAsync((char *)d_x.dev + b0 * row_bytes, (const char *)input.data_ptr() + b0 * row_bytes,
                                         (size_t)nbr * row_bytes, cudaMemcpyHostToDevice, s_in));
             KUTACC_CUDA(cudaEventRecord((cudaEvent_t)cp.uploaded[i], s_in));
