@@ -37,8 +37,8 @@ namespace dev {
 namespace {
 
 constexpr int BM = 128, BN = 128, BK = 64;
-constexpr int NSTAGE = 5;
-constexpr int ACC_STAGES = 4;
+constexpr int NSTAGE = 2;
+constexpr int ACC_STAGES = 2;
 constexpr int SLAB_BYTES = BM * BK * 2;                 // 16 KB, A and W slabs alike
 constexpr int STAGE_BYTES = 2 * SLAB_BYTES;
 constexpr int EPI_WARPS = 8;                            // two per TMEM lane quarter, 64 columns each
@@ -49,7 +49,7 @@ constexpr int BAR_OFF = STG_OFF + EPI_WARPS * STG_PER_WARP * STG_BYTES;
 constexpr int NBARS = 2 * NSTAGE + 2 * ACC_STAGES;
 constexpr int SMEM_BYTES = BAR_OFF + NBARS * 8 + 16 + 1024;
 constexpr int THREADS = 32 * (2 + EPI_WARPS);
-constexpr int TMEM_COLS = ACC_STAGES * BN;              // 512: the whole tensor memory of the SM
+constexpr int TMEM_COLS = ACC_STAGES * BN;              // 256: half of the SM's tensor memory (two CTAs per SM)
 
 struct alignas(64) GemmMaps {
     CUtensorMap a;        // X  [B][S][K], box [64, 128, 1], 128-byte swizzle
@@ -86,7 +86,7 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr)
 // instruction descriptor: D fp32, A and B bf16, both K-major, N = 128, M = 128
 constexpr uint32_t kInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(THREADS, 2)
 gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p)
 {
     extern __shared__ unsigned char smem_raw[];
@@ -314,7 +314,7 @@ bool launch(cudaStream_t stream, const GemmMaps &maps, const GemmParams &p, cons
     }
     const int s_tiles = (p.S + BM - 1) / BM;
     const int64_t tiles = (int64_t)p.B * s_tiles * (p.seg_n / BN) * p.nseg;
-    const unsigned grid = (unsigned)std::min<int64_t>(tiles, std::max(1, sm_count() - runtime().sm_margin));
+    const unsigned grid = (unsigned)std::min<int64_t>(tiles, 2 * std::max(1, sm_count() - runtime().sm_margin));
     KernelTimer timer__(name);
     gemm_tcgen05_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(maps, p);
     count_launch();

@@ -2,6 +2,7 @@
 // Replaces src/attention/global_attention.cpp:30-205 of the reference.
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <climits>
 
 #include "common.h"
@@ -56,7 +57,12 @@ extern "C" void kutacc_af2_global_attention(kutacc_af2_attention_inputs_t *q_bas
     if (!rt.reserve_stage(stage)) return;
     const size_t scratch_bytes = dev::global_attention_scratch_bytes((int)B, (int)S, (int)H, (int)D);
     if (!rt.reserve_workspace(scratch_bytes + 256)) return;
-    DeviceArg d_x = resolve_in(x.data_ptr(), x_bytes), d_m = resolve_in(mask.data_ptr(), m_bytes);
+    // Host-resident activations and result: the batch columns are independent, so they go through in
+    // chunks with upload, kernels and download overlapped on three streams (as in the gated attention).
+    const bool pipelined = staged_bytes_needed(x.data_ptr(), x_bytes) != 0 && staged_bytes_needed(o.data_ptr(), out_bytes) != 0 &&
+                           B >= 8 && x_bytes >= ((size_t)4 << 20) && out_rs == C;
+    DeviceArg d_x = pipelined ? resolve_out(x.data_ptr(), x_bytes) : resolve_in(x.data_ptr(), x_bytes);
+    DeviceArg d_m = resolve_in(mask.data_ptr(), m_bytes);
     DeviceArg d_wq = resolve_in(wq.data_ptr(), wcc), d_wk = resolve_in(wk.data_ptr(), wdc),
               d_wv = resolve_in(wv.data_ptr(), wdc), d_wg = resolve_in(wg.data_ptr(), wcc),
               d_wo = resolve_in(wo.data_ptr(), wcc), d_bg = resolve_in(bg.data_ptr(), bb),
@@ -69,15 +75,59 @@ extern "C" void kutacc_af2_global_attention(kutacc_af2_attention_inputs_t *q_bas
     if (kutacc_check_err_set) return;
     // one pass over HBM where the shape allows it (a cluster of CTAs holds each column in shared memory),
     // otherwise three kernels per L2-sized group of columns with the split-softmax state in `scratch`
-    bool ok = dev::launch_global_fused_bf16(stream, d_x.dev, d_m.dev, d_wq.dev, d_wk.dev, d_wv.dev, d_wg.dev,
-                                            (const float *)d_bg.dev, d_wo.dev, (const float *)d_bo.dev, d_out.dev,
-                                            out_rs, (int)B, (int)S, (int)H, (int)D);
+    auto run_cols = [&](int64_t b0, int64_t nb) -> bool {
+        const char *xc = (const char *)d_x.dev + (size_t)b0 * S * C * 2;
+        const char *mc = (const char *)d_m.dev + (size_t)b0 * S * 2;
+        char *oc = (char *)d_out.dev + (size_t)b0 * S * out_rs * 2;
+        bool done = dev::launch_global_fused_bf16(stream, xc, mc, d_wq.dev, d_wk.dev, d_wv.dev, d_wg.dev,
+                                                  (const float *)d_bg.dev, d_wo.dev, (const float *)d_bo.dev, oc, out_rs,
+                                                  (int)nb, (int)S, (int)H, (int)D);
+        if (kutacc_check_err_set) return false;
+        if (!done)
+            done = dev::launch_global_attention_bf16(stream, xc, mc, d_wq.dev, d_wk.dev, d_wv.dev, d_wg.dev,
+                                                     (const float *)d_bg.dev, d_wo.dev, (const float *)d_bo.dev, oc,
+                                                     out_rs, scratch, (int)nb, (int)S, (int)H, (int)D);
+        return done;
+    };
+    bool ok = true;
+    if (!pipelined) {
+        ok = run_cols(0, B);
+    } else {
+        int nchunks = (int)std::max<int64_t>(2, std::min<int64_t>(12, (int64_t)((x_bytes + ((size_t)4 << 20)) >> 23)));
+        nchunks = (int)std::max<int64_t>(1, std::min<int64_t>(nchunks, B / 4));
+        // chunk sizes shrink towards the end: the kernels and the download of the last chunk overlap nothing
+        int64_t chunk_begin[17];
+        const int64_t wsum = (int64_t)nchunks * (nchunks + 5) / 2;
+        int64_t acc = 0;
+        for (int i = 0; i < nchunks; ++i) {
+            chunk_begin[i] = std::min<int64_t>(B, (acc * B + wsum / 2) / wsum);
+            acc += nchunks + 2 - i;
+        }
+        chunk_begin[nchunks] = B;
+        CopyPipeline &cp = copy_pipeline(nchunks);
+        if (kutacc_check_err_set) return;
+        cudaStream_t s_in = (cudaStream_t)cp.in, s_out = (cudaStream_t)cp.out;
+        KUTACC_CUDA(cudaEventRecord((cudaEvent_t)cp.start, stream));
+        KUTACC_CUDA(cudaStreamWaitEvent(s_in, (cudaEvent_t)cp.start, 0));
+        KUTACC_CUDA(cudaStreamWaitEvent(s_out, (cudaEvent_t)cp.start, 0));
+        const size_t col_bytes = (size_t)S * C * 2;
+        for (int i = 0; i < nchunks && ok; ++i) {
+            const int64_t b0 = chunk_begin[i], nb = chunk_begin[i + 1] - b0;
+            if (nb <= 0) continue;
+            KUTACC_CUDA(cudaMemcpyAsync((char *)d_x.dev + b0 * col_bytes, (const char *)x.data_ptr() + b0 * col_bytes,
+                                        (size_t)nb * col_bytes, cudaMemcpyHostToDevice, s_in));
+            KUTACC_CUDA(cudaEventRecord((cudaEvent_t)cp.uploaded[i], s_in));
+            KUTACC_CUDA(cudaStreamWaitEvent(stream, (cudaEvent_t)cp.uploaded[i], 0));
+            ok = run_cols(b0, nb);
+            KUTACC_CUDA(cudaEventRecord((cudaEvent_t)cp.computed[i], stream));
+            KUTACC_CUDA(cudaStreamWaitEvent(s_out, (cudaEvent_t)cp.computed[i], 0));
+            KUTACC_CUDA(cudaMemcpyAsync((char *)o.data_ptr() + b0 * col_bytes, (const char *)d_out.dev + b0 * col_bytes,
+                                        (size_t)nb * col_bytes, cudaMemcpyDeviceToHost, s_out));
+        }
+        KUTACC_CUDA(cudaStreamSynchronize(s_out));
+    }
     if (kutacc_check_err_set) return;
-    if (!ok)
-        ok = dev::launch_global_attention_bf16(stream, d_x.dev, d_m.dev, d_wq.dev, d_wk.dev, d_wv.dev, d_wg.dev,
-                                               (const float *)d_bg.dev, d_wo.dev, (const float *)d_bo.dev, d_out.dev,
-                                               out_rs, scratch, (int)B, (int)S, (int)H, (int)D);
     KUTACC_CHECK(ok, "global_attention: no device kernel for nheads=", H, " head_size=", D, " out row stride ", out_rs);
-    finish_out(d_out);
+    if (!pipelined) finish_out(d_out);
     end_of_call();
 }

@@ -155,3 +155,18 @@ def test_sharded_triangle_flow_on_one_rank_matches_the_plain_call(kutacc_lib):
     api.raise_if_error()
     assert helpers.rel_err(got, want) <= 2e-3
     assert helpers.rel_err(got, helpers.oracle_faithful(w)) <= helpers.BF16_TOL
+
+
+def test_sm_margin_changes_the_grid_not_the_result(kutacc_lib):
+    # the persistent kernels walk their work items with a stride of the grid size: leaving SMs free for a
+    # collective must not change a single bit
+    w = W.random_gating_case(seed=77, B=6, S=200, H=4, D=32)
+    case = runner.DeviceCase(w)
+    want = runner.out_to_f32(case.run()).copy()
+    api.set_sm_margin(40)
+    try:
+        got = runner.out_to_f32(case.run()).copy()
+    finally:
+        api.set_sm_margin(0)
+    torch.cuda.synchronize()
+    assert np.array_equal(got, want)

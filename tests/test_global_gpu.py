@@ -74,3 +74,10 @@ def test_strided_output_rows(kutacc_lib):
     got = wide.float().cpu().numpy()
     assert np.array_equal(got[:, :, :w.C], want)
     assert (got[:, :, w.C:] == 7.0).all()                   # the gap between rows is left alone
+
+
+def test_pipelined_host_call_matches_device_call(kutacc_lib):
+    # 16 columns x 2048 rows = 4 MiB of activations in pinned host memory: the library uploads, computes and
+    # downloads the columns in chunks on three streams; the result must not change by a bit
+    w = W.random_global_case(seed=25, B=16, S=2048, zero_mask_rows=2)
+    assert np.array_equal(_run(w, True), _run(w, False))
