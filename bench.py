@@ -120,6 +120,40 @@ def dominant_kernel(workload):
     return "global_fused", "hbm", 2.0 * workload.B * workload.S * workload.C * 2, "GB/s"
 
 
+def torch_cpu_gating(w, reps: int = 3):
+    """The same operator written with torch CPU ops in the workload's dtype (oneDNN bf16 GEMMs), all host
+    threads: a second, library-grade CPU number beside the restatement of the reference's own loops."""
+    import torch
+    dt = torch.bfloat16 if w.dtype == "bf16" else torch.float32
+    A = {k: torch.from_numpy(v).to(dt) for k, v in w.arrays.items() if k in ("x", "wq", "wk", "wv", "wg", "wo", "bias", "nb")}
+    bg, bo = torch.from_numpy(w.arrays["bg"]).to(dt), torch.from_numpy(w.arrays["bo"]).to(dt)
+    B, S, H, D = w.B, w.S, w.H, w.D
+
+    def run():
+        x = A["x"]
+        q = (x @ A["wq"].T).view(B, S, H, D).transpose(1, 2)
+        k = (x @ A["wk"].T).view(B, S, H, D).transpose(1, 2)
+        v = (x @ A["wv"].T).view(B, S, H, D).transpose(1, 2)
+        gate = torch.sigmoid(x @ A["wg"].T + bg)
+        logits = (q @ k.transpose(-1, -2)) * (1.0 / D ** 0.5) + A["bias"][:, None, None, :]
+        if "nb" in A:
+            logits = logits + A["nb"][None]
+        p = torch.softmax(logits.float(), dim=-1).to(dt)
+        avg = (p @ v).transpose(1, 2).reshape(B, S, H * D) * gate
+        return avg @ A["wo"].T + bo
+
+    with torch.no_grad():
+        run()
+        times = []
+        for _ in range(reps):
+            t0 = time.perf_counter()
+            run()
+            times.append(time.perf_counter() - t0)
+    t = min(times)
+    return {"value": w.flops() / t / 1e12, "unit": UNIT, "threads": torch.get_num_threads(), "ms_per_pass": t * 1e3,
+            "sample_rows": w.B}
+
+
 def cpu_baseline(name: str, budget_s: float = 12.0):
     """CPU restatement of the reference on a bounded sample (a subset of the batch rows)."""
     from kutacc_b200 import workloads as W
@@ -144,7 +178,14 @@ def cpu_baseline(name: str, budget_s: float = 12.0):
         run(w)
         times.append(time.perf_counter() - t0)
     t = min(times)
+    torch_cpu = None
+    if kind == "gating":
+        try:
+            torch_cpu = torch_cpu_gating(w)
+        except Exception as exc:                                       # a second opinion only: never fatal
+            torch_cpu = {"error": str(exc)[:200]}
     return {"value": w.flops() / t / 1e12, "unit": UNIT, "cores": O.num_threads(), "kind": "port",
+            "torch_cpu": torch_cpu,
             "sample": f"{w.B} of {B} batch rows of {name} (full sequence length {S}), best of {len(times)} runs, "
                       f"{t * 1e3:.1f} ms per pass",
             "ms_full_call_est": t * 1e3 * B / w.B}
@@ -215,7 +256,7 @@ def run_strong_scaling(args, torch, dist, api, W, dev, world, rank, local_rank):
         torch.cuda.synchronize()
 
     for _ in range(args.warmup):
-        op.step()
+        op.step(gather_output=not args.leave_sharded)
     barrier()
     launches0 = api.launch_count()
     step_ms = []
@@ -225,7 +266,7 @@ def run_strong_scaling(args, torch, dist, api, W, dev, world, rank, local_rank):
             barrier()                                                 # ranks enter the step together
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            op.step()
+            op.step(gather_output=not args.leave_sharded)
             e1.record()
             e1.synchronize()
             step_ms.append(e0.elapsed_time(e1))
@@ -246,7 +287,7 @@ def run_strong_scaling(args, torch, dist, api, W, dev, world, rank, local_rank):
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": w.dtype, "data": "synthetic (seeded numpy, AlphaFold2 model shapes)",
             "config": {"workload": args.workload, "B": w.B, "S": w.S, "H": w.H, "D": w.D, "C": w.C, "pair_bias": True,
-                       "gflop_per_call": w.flops() / 1e9, "slabs": args.slabs, "sm_margin": op.sm_margin,
+                       "gflop_per_call": w.flops() / 1e9, "slabs": args.slabs, "sm_margin": op.sm_margin, "output_gathered": not args.leave_sharded,
                        "l2": "flushed between timed steps (256 MiB memset)",
                        "parallelism": f"rows of one problem over {world} GPU(s); NCCL all-gather of the projected "
                                       f"pair bias and of the output rows, output gather overlapped slab by slab"},
@@ -273,6 +314,9 @@ def main():
                     help="weak (default): every rank runs the whole workload on its own rows, no collective; "
                          "strong: one triangle workload split over the ranks with the two all-gathers")
     ap.add_argument("--sm-margin", type=int, default=8, help="strong scaling: SMs the kernels leave to NCCL")
+    ap.add_argument("--leave-sharded", action="store_true",
+                    help="strong scaling: skip the all-gather of the output rows (compute-only scaling, the state the "
+                         "reference operator itself leaves)")
     ap.add_argument("--slabs", type=int, default=2, help="strong scaling: slabs the output gather is pipelined in")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup

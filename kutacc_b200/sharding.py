@@ -50,7 +50,8 @@ class ShardedTriangleAttention:
 
     ``step()`` runs pair-bias projection -> bias all-gather -> per slab: attention, output all-gather
     (the gather of slab c overlaps the attention of slab c + 1). After ``step()`` every rank holds the
-    whole output in ``out_full``. With world == 1 the gathers are skipped.
+    whole output in ``out_full`` (with ``gather_output=False`` only its own rows, as the reference operator
+    leaves them). With world == 1 the gathers are skipped.
     """
 
     def __init__(self, w, rank: int, world: int, nslab: int, device, sm_margin: int = 8):
@@ -108,7 +109,7 @@ class ShardedTriangleAttention:
         self.comm = torch.cuda.Stream(device=device)
         self.events = [torch.cuda.Event() for _ in self.parts]
 
-    def step(self, block_size: int = 128):
+    def step(self, block_size: int = 128, gather_output: bool = True):
         api = self.api
         api.set_async(True)
         api.set_sm_margin(self.sm_margin)
@@ -123,7 +124,7 @@ class ShardedTriangleAttention:
                 api.set_stream(self.compute.cuda_stream)
                 api.gating_attention(p["t_x"], p["inputs"], p["t_bias"], self.t_nb, self.weights, p["t_out_rows"],
                                      block_size)
-                if self.world > 1:
+                if self.world > 1 and gather_output:
                     ev.record(self.compute)
                     self.comm.wait_event(ev)
                     api.set_stream(self.comm.cuda_stream)
