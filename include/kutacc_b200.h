@@ -137,6 +137,13 @@ KUTACC_B200_API void kutacc_af2_linear(kutacc_tensor_h act, kutacc_tensor_h weig
 KUTACC_B200_API void kutacc_af2_linear_weight_prepack(const uint16_t *weight, uint16_t *result, int64_t n, int64_t k,
                                                       int64_t ldb, int64_t num_threads);
 
+/* replaces include/kutacc.h:334 (src/normalization/layernorm.cpp:17-20, layernorm_kernel.h:22-53): LayerNorm
+ * of ONE row of `size` bf16 channels, out = bf16(fma(fma(x, rstd, -rstd * mean), gamma, beta)) with the
+ * reference's shifted-data statistics. Host or device pointers. A launch per row is what this signature
+ * implies; use kutacc_b200_layernorm_rows for a matrix. bf16 taken as uint16_t bit patterns. */
+KUTACC_B200_API void kutacc_af2_layernorm(uint16_t *data, float *gamma, float *beta, int64_t size, float eps,
+                                          uint16_t *out);
+
 /* replaces include/kutacc.h:418 (src/utils/blas.cpp:93-98): 'A' -> m*k, 'B' -> k*n elements */
 KUTACC_B200_API size_t kutacc_af2_gemm_pack_get_size(char identifier, char transa, char transb, int m, int n, int k);
 
@@ -220,6 +227,13 @@ KUTACC_B200_API int kutacc_b200_global_attention_noalloc(const void *q_data, con
  * [nheads, rows, n_k] (row stride of head h = nb_head_stride elements). Same arithmetic as
  * kutacc_af2_linear on z viewed [rows*n_k, c_z] followed by the caller's permute. dtype bf16/fp32. */
 KUTACC_B200_API void kutacc_b200_pair_bias(kutacc_tensor_h z, kutacc_tensor_h wb, kutacc_tensor_h nb);
+
+/* The same LayerNorm over every row of a [rows, size] bf16 matrix in one launch (the loop over rows that the
+ * reference leaves to its caller). Strides in elements, row_stride and out_row_stride >= size; out may alias
+ * data. Host or device pointers. */
+KUTACC_B200_API void kutacc_b200_layernorm_rows(const void *data, const float *gamma, const float *beta, int64_t rows,
+                                                int64_t size, int64_t row_stride, int64_t out_row_stride, float eps,
+                                                void *out);
 
 #ifdef __cplusplus
 } /* extern "C" */

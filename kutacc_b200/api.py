@@ -25,14 +25,14 @@ EXPORTS = [
     # part 1: the reference's interface for this path
     "kutacc_get_version", "kutacc_comm_init", "kutacc_comm_fini", "kutacc_af2_all_gather",
     "kutacc_af2_gating_attention", "kutacc_af2_global_attention", "kutacc_af2_linear",
-    "kutacc_af2_linear_weight_prepack", "kutacc_af2_gemm_pack_get_size",
+    "kutacc_af2_linear_weight_prepack", "kutacc_af2_gemm_pack_get_size", "kutacc_af2_layernorm",
     # part 2: additions
     "kutacc_b200_tensor_create", "kutacc_b200_tensor_destroy", "kutacc_b200_error_set", "kutacc_b200_last_error",
     "kutacc_b200_clear_error", "kutacc_b200_set_stream", "kutacc_b200_set_async", "kutacc_b200_set_sm_margin", "kutacc_b200_synchronize",
     "kutacc_b200_device_malloc", "kutacc_b200_device_free", "kutacc_b200_memcpy_h2d", "kutacc_b200_memcpy_d2h",
     "kutacc_b200_workspace_bytes", "kutacc_b200_release_workspace", "kutacc_b200_launch_count",
     "kutacc_b200_set_profile", "kutacc_b200_profile_read", "kutacc_b200_comm_unique_id", "kutacc_b200_comm_init_with_id", "kutacc_b200_pair_bias",
-    "kutacc_b200_global_attention_noalloc",
+    "kutacc_b200_global_attention_noalloc", "kutacc_b200_layernorm_rows",
 ]
 EXPORTED_DATA = ["world_size", "rank"]
 
@@ -126,6 +126,10 @@ def lib() -> C.CDLL:
     L.kutacc_b200_global_attention_noalloc.restype = C.c_int
     L.kutacc_b200_pair_bias.argtypes = [vp, vp, vp]
     L.kutacc_b200_pair_bias.restype = None
+    L.kutacc_af2_layernorm.argtypes = [vp, vp, vp, C.c_int64, C.c_float, vp]
+    L.kutacc_af2_layernorm.restype = None
+    L.kutacc_b200_layernorm_rows.argtypes = [vp, vp, vp, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_float, vp]
+    L.kutacc_b200_layernorm_rows.restype = None
     _lib = L
     return L
 
@@ -298,6 +302,24 @@ def linear(act, weight, bias_ptr: Optional[int], result, beta: int = 0, check: b
 
 def pair_bias(z, wb, nb, check: bool = True) -> None:
     lib().kutacc_b200_pair_bias(_h(z), _h(wb), _h(nb))
+    if check:
+        raise_if_error()
+
+
+def layernorm_rows(data_ptr: int, gamma_ptr: int, beta_ptr: int, rows: int, size: int, eps: float, out_ptr: int,
+                   row_stride: Optional[int] = None, out_row_stride: Optional[int] = None, check: bool = True) -> None:
+    """LayerNorm of every row of a [rows, size] bf16 matrix (raw host or device addresses)."""
+    lib().kutacc_b200_layernorm_rows(C.c_void_p(data_ptr), C.c_void_p(gamma_ptr), C.c_void_p(beta_ptr), int(rows),
+                                     int(size), int(row_stride or size), int(out_row_stride or size), float(eps),
+                                     C.c_void_p(out_ptr))
+    if check:
+        raise_if_error()
+
+
+def layernorm(data_ptr: int, gamma_ptr: int, beta_ptr: int, size: int, eps: float, out_ptr: int, check: bool = True) -> None:
+    """The reference's one-row entry point."""
+    lib().kutacc_af2_layernorm(C.c_void_p(data_ptr), C.c_void_p(gamma_ptr), C.c_void_p(beta_ptr), int(size), float(eps),
+                               C.c_void_p(out_ptr))
     if check:
         raise_if_error()
 

@@ -67,6 +67,10 @@ bool launch_pair_bias(cudaStream_t stream, ElemType t, const void *z, const void
 
 // ---- global attention (bf16, C = 64) ---------------------------------------------------------------
 // scratch: qk [B, H, 64] fp32-sized slots and wa [B, 64]; see global_attention.cu
+// LayerNorm of every row of a [rows, size] bf16 matrix (strides in elements); fp32 gamma and beta.
+bool launch_layernorm_rows(cudaStream_t stream, const void *x, const float *gamma, const float *beta, void *out,
+                           int64_t rows, int64_t size, int64_t x_stride, int64_t out_stride, float eps);
+
 // Global attention in one pass over HBM (thread-block clusters hold a column in shared memory); 8 heads x 8
 // only. Returns false when the shape is not covered.
 bool launch_global_fused_bf16(cudaStream_t stream, const void *x, const void *mask, const void *wq, const void *wk,

@@ -127,6 +127,27 @@ def linear_exact(act, w, bias, beta=0, result=None):
     return res
 
 
+def layernorm_bf16(x, gamma, beta, eps):
+    """x [rows, size] u16 (bf16 bits), gamma/beta [size] f32; returns [rows, size] u16."""
+    x = np.ascontiguousarray(x, dtype=np.uint16)
+    gamma = np.ascontiguousarray(gamma, dtype=np.float32)
+    beta = np.ascontiguousarray(beta, dtype=np.float32)
+    rows, size = x.shape
+    out = np.empty_like(x)
+    lib().orc_layernorm_bf16(_p(x), _p(gamma), _p(beta), C.c_int64(rows), C.c_int64(size), C.c_float(eps), _p(out))
+    return out
+
+
+def layernorm_exact(x, gamma, beta, eps):
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    gamma = np.ascontiguousarray(gamma, dtype=np.float32)
+    beta = np.ascontiguousarray(beta, dtype=np.float32)
+    rows, size = x.shape
+    out = np.empty_like(x)
+    lib().orc_layernorm_exact(_p(x), _p(gamma), _p(beta), C.c_int64(rows), C.c_int64(size), C.c_float(eps), _p(out))
+    return out
+
+
 def all_gather_bytes(shards, out_shape, data_size0):
     """shards: list of contiguous uint8 arrays [a,b,len] (one per rank); returns gathered [m,n,len]."""
     world = len(shards)

@@ -542,4 +542,53 @@ void orc_all_gather_bytes(const uint8_t *const *shards, int64_t world, int64_t d
     }
 }
 
+// ------------------------------------------------------------------------------------------------
+// LayerNorm of each row. Follows src/normalization/layernorm_kernel.h:22-53 (one row per call there):
+// sums of (x - x[0]) accumulated per vector lane (16 fp32 lanes) and then across the lanes, mean = sum/n +
+// x[0], var = max((sum2 - sum*sum/n)/n, 0), rstd = 1/sqrt(var + eps), y = fma(fma(x, rstd, -rstd*mean),
+// gamma, beta), bf16 RNE on store. The exact variant uses the textbook two-pass formula in double.
+// ------------------------------------------------------------------------------------------------
+void orc_layernorm_bf16(const uint16_t *x, const float *gamma, const float *beta, int64_t rows, int64_t size, float eps,
+                        uint16_t *out)
+{
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < rows; ++r) {
+        const uint16_t *xr = x + r * size;
+        const float delta = bf2f(xr[0]);
+        float lane_sum[16] = {0}, lane_sum2[16] = {0};
+        for (int64_t i = 0; i < size; ++i) {
+            const float v = bf2f(xr[i]) - delta;
+            lane_sum[i & 15] += v;
+            lane_sum2[i & 15] = std::fma(v, v, lane_sum2[i & 15]);
+        }
+        float sum = 0.f, sum2 = 0.f;
+        for (int l = 0; l < 16; ++l) {
+            sum += lane_sum[l];
+            sum2 += lane_sum2[l];
+        }
+        const float mean = sum / (float)size + delta;
+        const float var = std::max((sum2 - sum * sum / (float)size) / (float)size, 0.f);
+        const float rstd = 1 / std::sqrt(var + eps);
+        const float bias = -rstd * mean;
+        for (int64_t i = 0; i < size; ++i)
+            out[r * size + i] = f2bf(std::fma(std::fma(bf2f(xr[i]), rstd, bias), gamma[i], beta[i]));
+    }
+}
+
+void orc_layernorm_exact(const float *x, const float *gamma, const float *beta, int64_t rows, int64_t size, float eps,
+                         float *out)
+{
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < rows; ++r) {
+        const float *xr = x + r * size;
+        double mean = 0, var = 0;
+        for (int64_t i = 0; i < size; ++i) mean += xr[i];
+        mean /= (double)size;
+        for (int64_t i = 0; i < size; ++i) var += (xr[i] - mean) * (xr[i] - mean);
+        var /= (double)size;
+        const double rstd = 1.0 / std::sqrt(var + (double)eps);
+        for (int64_t i = 0; i < size; ++i) out[r * size + i] = (float)((xr[i] - mean) * rstd * gamma[i] + beta[i]);
+    }
+}
+
 }  // extern "C"

@@ -170,3 +170,24 @@ def test_workload_shapes_and_flops():
     w = W.make("triangle_start_384", rows=4)
     assert w.arrays["x"].shape == (4, 384, 128) and w.arrays["nb"].shape == (4, 384, 384)
     assert w.arrays["bias"].shape == (4, 384)
+
+
+def test_layernorm_oracle_against_textbook_formula():
+    # the exact variant is the textbook formula; the faithful one (shifted-data sums in fp32, bf16 store,
+    # layernorm_kernel.h:22-53) stays within bf16 rounding of it, also for rows with a large common offset
+    from kutacc_b200.workloads import as_f32, bf16_bits
+    rng = np.random.default_rng(11)
+    for size, offset in [(64, 0.0), (128, 50.0), (256, -7.0), (100, 3.0)]:
+        x = as_f32(bf16_bits(rng.standard_normal((9, size), dtype=np.float32) * 2 + offset))
+        g = rng.standard_normal(size).astype(np.float32)
+        b = rng.standard_normal(size).astype(np.float32)
+        x64 = x.astype(np.float64)
+        ref = (x64 - x64.mean(1, keepdims=True)) / np.sqrt(x64.var(1, keepdims=True) + 1e-5) * g + b
+        exact = O.layernorm_exact(x, g, b, 1e-5)
+        faithful = as_f32(O.layernorm_bf16(bf16_bits(x), g, b, 1e-5))
+        assert np.abs(exact - ref).max() <= 1e-5 * max(np.abs(ref).max(), 1.0)
+        assert np.abs(faithful - ref).max() <= 6e-3 * np.abs(ref).max()
+    # a constant row: variance 0, output = beta exactly (rstd * 0 * gamma + beta)
+    x = np.full((1, 64), 3.0, dtype=np.float32)
+    out = as_f32(O.layernorm_bf16(bf16_bits(x), np.ones(64, np.float32), np.full(64, 0.5, np.float32), 1e-5))
+    assert np.array_equal(out, np.full((1, 64), 0.5, dtype=np.float32))
