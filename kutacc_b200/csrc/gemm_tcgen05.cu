@@ -3,16 +3,18 @@
 //
 //   C[b, s, n] = sum_k X[b, s, k] * W[n, k] (+ bias[n])         X [B, S, K] bf16, W [N, K] bf16 (W[out][in])
 //
-// A persistent CTA (one per SM) walks 128 x 128 output tiles; a row tile never crosses a batch row, so
+// Persistent CTAs (two per SM) walk 128 x 128 output tiles; a row tile never crosses a batch row, so
 // every TMA box lies inside one [S, *] slab and rows past S are zero-filled on load and clipped on
 // store. Warp roles:
-//   warp 0      producer: TMA loads of 128 x 64 slabs of X and W (128-byte swizzle) into a 5-stage ring
+//   warp 0      producer: TMA loads of 128 x 64 slabs of X and W (128-byte swizzle) into a 2-stage ring
 //   warp 1      MMA issuer: one elected lane issues tcgen05.mma (M = 128, N = 128, K = 16) four times per
-//               slab into one of four 128-column TMEM accumulators and commits to mbarriers
+//               slab into one of two 128-column TMEM accumulators and commits to mbarriers
 //   warps 2-9   epilogue: each warp owns 32 TMEM lanes x 64 columns of the tile: two tcgen05.ld in flight,
 //               bias add, bf16 rounding, swizzled 32 x 32 staging tiles in shared memory, TMA stores into
 //               the destination layout
-// The four accumulators let the epilogue of tile i overlap the MMAs of tiles i+1 .. i+3.
+// The two accumulators let the epilogue of tile i overlap the MMAs of tile i+1; with K = 128 a tile is only
+// eight MMAs, so what hides the rest of the per-tile chain (TMA in, tcgen05.ld, staging, TMA store) is the
+// second CTA resident on the SM (99 KB of shared memory and half of the tensor memory each).
 //
 // For the fused Q/K/V/gate projection the four weights are four tensor maps and the destination maps
 // scatter straight into the attention kernel's [B, H, S, D] layout (q, k, v) and into [B, S, C] (gate,
