@@ -169,9 +169,12 @@ static void gating_attention_impl(Tensor &input, int64_t batch, int64_t seq_len,
             ok = ok && dev::launch_gemm_generic(stream, et, x_c, C, d_wv.dev, C, nullptr, 0.f, v_c, C, Mc, C, C);
             ok = ok && dev::launch_gemm_generic(stream, et, x_c, C, d_wg.dev, C, (const float *)d_bg.dev, 0.f, g_c, C,
                                                 Mc, C, C);
-            ok = ok && dev::launch_attn_generic(stream, et, q_c, k_c, v_c, g_c, bias_c, bias_s0,
-                                                has_nb ? d_nb.dev : nullptr, nb_s0, nb_s1, a_c, (int)nbr, (int)S, (int)H,
-                                                (int)D, scale);
+            ok = ok && ((dt == kFP32 && dev::launch_attn_f32(stream, q_c, k_c, v_c, g_c, bias_c, bias_s0,
+                                                              has_nb ? d_nb.dev : nullptr, nb_s0, nb_s1, a_c, (int)nbr,
+                                                              (int)S, (int)H, (int)D, scale)) ||
+                        dev::launch_attn_generic(stream, et, q_c, k_c, v_c, g_c, bias_c, bias_s0,
+                                                 has_nb ? d_nb.dev : nullptr, nb_s0, nb_s1, a_c, (int)nbr, (int)S, (int)H,
+                                                 (int)D, scale));
             ok = ok && dev::launch_gemm_generic(stream, et, a_c, C, d_wo.dev, C, (const float *)d_bo.dev, 0.f, out_c,
                                                 out_rs, Mc, C, C);
         }

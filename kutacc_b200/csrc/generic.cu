@@ -106,6 +106,111 @@ __global__ void __launch_bounds__(256) gemm_generic_kernel(const T *__restrict__
     }
 }
 
+// ---- fp32 GEMM on tensor cores with error compensation ("3xTF32") -------------------------------------
+// Each fp32 operand is split into a tf32 head and a tf32 tail (x = hi + lo, |lo| <= 2^-11 |x|); the product
+// is accumulated as hi*hi + hi*lo + lo*hi in fp32 (the lo*lo term, 2^-22 relative, is dropped), which keeps
+// the result within a few fp32 ulps of a plain fp32 GEMM at a third of the tf32 tensor rate.
+// 128 x 128 x 32 tiles, 8 warps (4 x 2), cp.async double buffering, rows padded to 36 floats so that the
+// fragment loads (row g, column t) touch 32 different banks.
+constexpr int TM = 128, TN = 128, TK = 32, TPAD = 36;
+constexpr int T_STAGE_FLOATS = (TM + TN) * TPAD;
+constexpr int T_SMEM_BYTES = 2 * T_STAGE_FLOATS * 4;
+
+__device__ __forceinline__ uint32_t to_tf32(float x)
+{
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;\n" : "=r"(r) : "f"(x));
+    return r;
+}
+__device__ __forceinline__ void mma_tf32_1688(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1)
+{
+    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__global__ void __launch_bounds__(256) gemm_tf32x3_kernel(const float *__restrict__ a, int64_t lda,
+                                                          const float *__restrict__ w, int64_t ldw,
+                                                          const float *__restrict__ bias, float *__restrict__ c,
+                                                          int64_t ldc, int64_t M, int64_t N, int64_t K)
+{
+    extern __shared__ __align__(16) float t_smem[];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int wm = warp >> 1, wn = warp & 1;                   // warp tile: rows wm*32.., columns wn*64..
+    const int64_t m0 = (int64_t)blockIdx.x * TM, n0 = (int64_t)blockIdx.y * TN;
+    const uint32_t smem0 = smem_u32(t_smem);
+    auto load_stage = [&](int stage, int64_t k0) {
+        const uint32_t sa = smem0 + stage * T_STAGE_FLOATS * 4, sw = sa + TM * TPAD * 4;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int idx = tid + i * 256, r = idx >> 3, ch = idx & 7;
+            const bool oka = m0 + r < M, okw = n0 + r < N;
+            cp_async16(sa + (r * TPAD + ch * 4) * 4, a + (oka ? m0 + r : 0) * lda + k0 + ch * 4, oka ? 16 : 0);
+            cp_async16(sw + (r * TPAD + ch * 4) * 4, w + (okw ? n0 + r : 0) * ldw + k0 + ch * 4, okw ? 16 : 0);
+        }
+        cp_async_commit();
+    };
+    float acc[2][8][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[i][j][e] = 0.f;
+    const int nk = (int)(K / TK);
+    load_stage(0, 0);
+    for (int kc = 0; kc < nk; ++kc) {
+        if (kc + 1 < nk) load_stage((kc + 1) & 1, (int64_t)(kc + 1) * TK);
+        else cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        const float *sa = t_smem + (kc & 1) * T_STAGE_FLOATS, *sw = sa + TM * TPAD;
+#pragma unroll
+        for (int k8 = 0; k8 < TK / 8; ++k8) {
+            uint32_t ahi[2][4], alo[2][4];
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt) {
+                const float *p0 = sa + (wm * 32 + mt * 16 + g) * TPAD + k8 * 8 + t;
+                const float v[4] = {p0[0], p0[8 * TPAD], p0[4], p0[8 * TPAD + 4]};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    ahi[mt][e] = to_tf32(v[e]);
+                    alo[mt][e] = to_tf32(v[e] - __uint_as_float(ahi[mt][e]));
+                }
+            }
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt) {
+                const float *q0 = sw + (wn * 64 + nt * 8 + g) * TPAD + k8 * 8 + t;
+                const float b0 = q0[0], b1 = q0[4];
+                const uint32_t bh0 = to_tf32(b0), bh1 = to_tf32(b1);
+                const uint32_t bl0 = to_tf32(b0 - __uint_as_float(bh0)), bl1 = to_tf32(b1 - __uint_as_float(bh1));
+#pragma unroll
+                for (int mt = 0; mt < 2; ++mt) {
+                    mma_tf32_1688(acc[mt][nt], alo[mt], bh0, bh1);     // small terms first
+                    mma_tf32_1688(acc[mt][nt], ahi[mt], bl0, bl1);
+                    mma_tf32_1688(acc[mt][nt], ahi[mt], bh0, bh1);
+                }
+            }
+        }
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+            const int64_t n = n0 + wn * 64 + nt * 8 + 2 * t;
+#pragma unroll
+            for (int hrow = 0; hrow < 2; ++hrow) {
+                const int64_t m = m0 + wm * 32 + mt * 16 + g + 8 * hrow;
+                if (m >= M) continue;
+#pragma unroll
+                for (int e = 0; e < 2; ++e)
+                    if (n + e < N) c[m * ldc + n + e] = acc[mt][nt][2 * hrow + e] + (bias ? bias[n + e] : 0.f);
+            }
+        }
+}
+
 // ---- attention: one warp per (b, h, query) --------------------------------------------------------
 // Lanes split the keys for the logits (each lane a dot product over D) and split the head
 // channels for P.V. Online softmax across 32-key chunks.
@@ -369,6 +474,23 @@ bool launch_pair_bias_mma(cudaStream_t stream, const void *z, const void *wb, vo
 bool launch_gemm_generic(cudaStream_t stream, ElemType t, const void *a, int64_t lda, const void *w, int64_t ldw,
                          const float *bias, float beta, void *c, int64_t ldc, int64_t M, int64_t N, int64_t K)
 {
+    if (t == kElemF32 && beta == 0.f && K % TK == 0 && lda % 4 == 0 && ldw % 4 == 0 &&
+        (((uintptr_t)a | (uintptr_t)w) & 15u) == 0 && (N + TN - 1) / TN <= 65535) {
+        static bool configured = false;
+        if (!configured) {
+            configured = cudaFuncSetAttribute(gemm_tf32x3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T_SMEM_BYTES) ==
+                         cudaSuccess;
+            cudaGetLastError();
+        }
+        if (configured) {
+            KernelTimer timer__("gemm_tf32x3");
+            dim3 gridt((unsigned)((M + TM - 1) / TM), (unsigned)((N + TN - 1) / TN));
+            gemm_tf32x3_kernel<<<gridt, 256, T_SMEM_BYTES, stream>>>((const float *)a, lda, (const float *)w, ldw, bias,
+                                                                      (float *)c, ldc, M, N, K);
+            count_launch();
+            return true;
+        }
+    }
     dim3 grid((unsigned)((M + GT - 1) / GT), (unsigned)((N + GT - 1) / GT));
     if (grid.y > 65535) return false;
     KernelTimer timer__("gemm_generic");

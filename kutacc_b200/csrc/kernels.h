@@ -67,6 +67,11 @@ bool launch_pair_bias(cudaStream_t stream, ElemType t, const void *z, const void
 
 // ---- global attention (bf16, C = 64) ---------------------------------------------------------------
 // scratch: qk [B, H, 64] fp32-sized slots and wa [B, 64]; see global_attention.cu
+// fp32 attention core on tensor cores (error-compensated tf32), head size 32; false for other shapes.
+bool launch_attn_f32(cudaStream_t stream, const void *q, const void *k, const void *v, const void *gate, const void *bias,
+                     int64_t bias_stride0, const void *nb, int64_t nb_stride_h, int64_t nb_stride_q, void *avg, int B,
+                     int S, int H, int D, float scale);
+
 // LayerNorm of every row of a [rows, size] bf16 matrix (strides in elements); fp32 gamma and beta.
 bool launch_layernorm_rows(cudaStream_t stream, const void *x, const float *gamma, const float *beta, void *out,
                            int64_t rows, int64_t size, int64_t x_stride, int64_t out_stride, float eps);
