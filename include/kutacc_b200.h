@@ -11,7 +11,7 @@
  * strides, dtype} (reference: src/tensor/tensor.h:21-51). The library never owns tensor data.
  * data pointers may be CUDA device pointers (no copies are made) or host pointers (the library
  * stages them through device memory on every call). Strides are in elements for compute
- * operators and in bytes for kutacc_af2_all_gather, as in the reference.
+ * operators and in bytes for kutacc_af2_all_gather and kutacc_af2_transpose, as in the reference.
  *
  * Errors: operators return void. A failed check prints one line
  *   "KUTACC_CHECK fail in <func> at <file>:<line> , <message>"
@@ -105,6 +105,12 @@ KUTACC_B200_API void kutacc_comm_fini(void);
  * dim 1 when data.sizes[0] == out.sizes[0], else dim 0; block(x) = ceil(x / world_size),
  * chunk(x) = min(block(x), x - rank * block(x)). */
 KUTACC_B200_API void kutacc_af2_all_gather(kutacc_tensor_h data, kutacc_tensor_h out);
+
+/* replaces include/kutacc.h:58-65 (src/comm/transpose.cpp:21-100): re-shards a byte matrix between "rows
+ * split over the ranks" and "columns split over the ranks". data is [chunk(m), n, len] and out [m, chunk(n),
+ * len], or data [m, chunk(n), len] and out [chunk(m), n, len]; len and all strides are BYTES; element (i, j)
+ * moves from the rank that owns row i to the rank that owns column j. One group of ncclSend/ncclRecv. */
+KUTACC_B200_API void kutacc_af2_transpose(kutacc_tensor_h data, kutacc_tensor_h out);
 
 /* replaces include/kutacc.h:297-300 (src/attention/gating_attention.cpp:160-200).
  *   input            [batch*seq_len, nchannels]

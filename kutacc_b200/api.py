@@ -23,7 +23,7 @@ DTYPE_INT64, DTYPE_BF16, DTYPE_FP32 = 0, 1, 2
 
 EXPORTS = [
     # part 1: the reference's interface for this path
-    "kutacc_get_version", "kutacc_comm_init", "kutacc_comm_fini", "kutacc_af2_all_gather",
+    "kutacc_get_version", "kutacc_comm_init", "kutacc_comm_fini", "kutacc_af2_all_gather", "kutacc_af2_transpose",
     "kutacc_af2_gating_attention", "kutacc_af2_global_attention", "kutacc_af2_linear",
     "kutacc_af2_linear_weight_prepack", "kutacc_af2_gemm_pack_get_size", "kutacc_af2_layernorm",
     # part 2: additions
@@ -78,6 +78,8 @@ def lib() -> C.CDLL:
     L.kutacc_comm_fini.restype = None
     L.kutacc_af2_all_gather.argtypes = [vp, vp]
     L.kutacc_af2_all_gather.restype = None
+    L.kutacc_af2_transpose.argtypes = [vp, vp]
+    L.kutacc_af2_transpose.restype = None
     L.kutacc_af2_gating_attention.argtypes = [vp, C.POINTER(AttentionInputs), vp, vp, C.POINTER(AttentionWeights), vp, i64]
     L.kutacc_af2_gating_attention.restype = None
     L.kutacc_af2_global_attention.argtypes = [C.POINTER(AttentionInputs), vp, vp, C.POINTER(AttentionWeights), vp]
@@ -302,6 +304,13 @@ def linear(act, weight, bias_ptr: Optional[int], result, beta: int = 0, check: b
 
 def pair_bias(z, wb, nb, check: bool = True) -> None:
     lib().kutacc_b200_pair_bias(_h(z), _h(wb), _h(nb))
+    if check:
+        raise_if_error()
+
+
+def transpose(data, out, check: bool = True) -> None:
+    """Re-shard between row-split and column-split byte matrices (kutacc_af2_transpose)."""
+    lib().kutacc_af2_transpose(_h(data), _h(out))
     if check:
         raise_if_error()
 

@@ -35,6 +35,10 @@ struct NcclApi {
     ncclResult_t (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int) = nullptr;
     ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
     ncclResult_t (*AllGather)(const void *, void *, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*Send)(const void *, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*Recv)(void *, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*GroupStart)() = nullptr;
+    ncclResult_t (*GroupEnd)() = nullptr;
     const char *(*GetErrorString)(ncclResult_t) = nullptr;
 };
 NcclApi g_nccl;
@@ -57,10 +61,14 @@ bool load_nccl()
     KUTACC_SYM(CommInitRank, "ncclCommInitRank");
     KUTACC_SYM(CommDestroy, "ncclCommDestroy");
     KUTACC_SYM(AllGather, "ncclAllGather");
+    KUTACC_SYM(Send, "ncclSend");
+    KUTACC_SYM(Recv, "ncclRecv");
+    KUTACC_SYM(GroupStart, "ncclGroupStart");
+    KUTACC_SYM(GroupEnd, "ncclGroupEnd");
     KUTACC_SYM(GetErrorString, "ncclGetErrorString");
 #undef KUTACC_SYM
     const bool ok = g_nccl.GetUniqueId && g_nccl.CommInitRank && g_nccl.CommDestroy && g_nccl.AllGather &&
-                    g_nccl.GetErrorString;
+                    g_nccl.Send && g_nccl.Recv && g_nccl.GroupStart && g_nccl.GroupEnd && g_nccl.GetErrorString;
     KUTACC_CHECK(ok, "libnccl lacks a required symbol");
     return ok;
 }
@@ -297,6 +305,96 @@ void kutacc_af2_all_gather(kutacc_tensor_h data_h, kutacc_tensor_h out_h)
             copy_rows(stream, recv + (size_t)r * slot, other * len, len, (uint8_t *)d_out.dev + r * block * os_a, os_a,
                       os_o, have, other, len);
         }
+    }
+    finish_out(d_out);
+    end_of_call();
+}
+
+// Re-shard a byte matrix between "rows split over the ranks" and "columns split over the ranks"
+// (replaces src/comm/transpose.cpp:21-100, include/kutacc.h:58-65): data [chunk(m), n, len] -> out
+// [m, chunk(n), len], or data [m, chunk(n), len] -> out [chunk(m), n, len]; block(x) = ceil(x / world),
+// chunk_r(x) = min(block, x - r * block). Element (i, j) moves from the rank that owns row i to the rank that
+// owns column j. Here: the block for every peer is packed into the library's workspace, the blocks are
+// exchanged with one group of ncclSend/ncclRecv, and the received blocks are scattered into out; the block
+// that stays on this rank is copied directly. buffer_size (the reference's shared-memory window) is not used.
+void kutacc_af2_transpose(kutacc_tensor_h data_h, kutacc_tensor_h out_h)
+{
+    using namespace kutacc;
+    if (data_h == nullptr || out_h == nullptr) {  // transpose.cpp:92-96
+        KUTACC_CHECK(data_h != nullptr, "transpose: data is null");
+        KUTACC_CHECK(out_h != nullptr, "transpose: out is null");
+        return;
+    }
+    if (kutacc_check_err_set) return;
+    Tensor &data = *as_tensor(data_h), &out = *as_tensor(out_h);
+    KUTACC_CHECK(data.dim() == 3 && out.dim() == 3 && data.data_ptr() && out.data_ptr(),
+                 "transpose: [m, n, len] byte tensors expected");
+    if (kutacc_check_err_set) return;
+    KUTACC_CHECK(data.strides()[2] == 1, data.strides()[2]);  // transpose.cpp:38-39
+    KUTACC_CHECK(out.strides()[2] == 1, out.strides()[2]);
+    if (kutacc_check_err_set) return;
+    // local copies of the views; when data holds the whole of dim 0 the roles of dims 0 and 1 swap (:27-33)
+    int64_t dsz[2] = {data.sizes()[0], data.sizes()[1]}, dst_[2] = {data.strides()[0], data.strides()[1]};
+    int64_t osz[2] = {out.sizes()[0], out.sizes()[1]}, ost[2] = {out.strides()[0], out.strides()[1]};
+    int64_t m = std::max(dsz[0], osz[0]), n = std::max(dsz[1], osz[1]);
+    const int64_t len = data.sizes()[2];
+    KUTACC_CHECK(m > 0 && n > 0 && len > 0 && out.sizes()[2] == len, "transpose: shape invalid");
+    if (kutacc_check_err_set) return;
+    const size_t data_bytes = (size_t)((dsz[0] - 1) * dst_[0] + (dsz[1] - 1) * dst_[1] + len);
+    const size_t out_bytes = (size_t)((osz[0] - 1) * ost[0] + (osz[1] - 1) * ost[1] + len);
+    if (dsz[0] == m) {
+        std::swap(m, n);
+        std::swap(dsz[0], dsz[1]);
+        std::swap(dst_[0], dst_[1]);
+        std::swap(osz[0], osz[1]);
+        std::swap(ost[0], ost[1]);
+    }
+    // now: data [chunk(m), n], out [m, chunk(n)]
+    const int64_t bm = (m + world_size - 1) / world_size, bn = (n + world_size - 1) / world_size;
+    auto chunk_m = [&](int64_t r) { return std::max<int64_t>(0, std::min(bm, m - r * bm)); };
+    auto chunk_n = [&](int64_t r) { return std::max<int64_t>(0, std::min(bn, n - r * bn)); };
+    KUTACC_CHECK(dsz[0] >= chunk_m(rank) && dsz[1] == n && osz[0] == m && osz[1] >= chunk_n(rank),
+                 "transpose: shapes do not match this rank's chunks");
+    if (kutacc_check_err_set) return;
+
+    Runtime &rt = runtime();
+    cudaStream_t stream = (cudaStream_t)rt.stream;
+    if (!rt.reserve_stage(staged_bytes_needed(data.data_ptr(), data_bytes) + staged_bytes_needed(out.data_ptr(), out_bytes)))
+        return;
+    DeviceArg d_in = resolve_in(data.data_ptr(), data_bytes);
+    // a strided host output keeps the bytes around its elements: bring it in before it is copied back whole
+    const bool out_dense = ost[1] == len && ost[0] == osz[1] * len;
+    DeviceArg d_out = out_dense ? resolve_out(out.data_ptr(), out_bytes) : resolve_in(out.data_ptr(), out_bytes);
+    if (kutacc_check_err_set) return;
+    const uint8_t *src = (const uint8_t *)d_in.dev;
+    uint8_t *dst = (uint8_t *)d_out.dev;
+    const int64_t my_m = chunk_m(rank), my_n = chunk_n(rank);
+    // the block that stays: rows of this rank, columns of this rank
+    copy_rows(stream, src + rank * bn * dst_[1], dst_[0], dst_[1], dst + rank * bm * ost[0], ost[0], ost[1], my_m, my_n, len);
+    if (world_size > 1) {
+        KUTACC_CHECK(g_comm != nullptr, "transpose: kutacc_comm_init has not built a communicator");
+        if (kutacc_check_err_set) return;
+        const size_t slot = (size_t)bm * bn * len;
+        if (!rt.reserve_workspace((size_t)2 * world_size * (slot + 256))) return;
+        uint8_t *send = (uint8_t *)rt.take_workspace((size_t)world_size * slot);
+        uint8_t *recv = (uint8_t *)rt.take_workspace((size_t)world_size * slot);
+        if (kutacc_check_err_set) return;
+        for (int64_t p = 0; p < world_size; ++p)
+            if (p != rank)
+                copy_rows(stream, src + p * bn * dst_[1], dst_[0], dst_[1], send + p * slot, chunk_n(p) * len, len, my_m,
+                          chunk_n(p), len);
+        KUTACC_NCCL(g_nccl.GroupStart());
+        for (int64_t p = 0; p < world_size; ++p) {
+            if (p == rank) continue;
+            const size_t ns = (size_t)my_m * chunk_n(p) * len, nr = (size_t)chunk_m(p) * my_n * len;
+            if (ns) KUTACC_NCCL(g_nccl.Send(send + p * slot, ns, ncclUint8, (int)p, g_comm, stream));
+            if (nr) KUTACC_NCCL(g_nccl.Recv(recv + p * slot, nr, ncclUint8, (int)p, g_comm, stream));
+        }
+        KUTACC_NCCL(g_nccl.GroupEnd());
+        for (int64_t p = 0; p < world_size; ++p)
+            if (p != rank)
+                copy_rows(stream, recv + p * slot, my_n * len, len, dst + p * bm * ost[0], ost[0], ost[1], chunk_m(p), my_n,
+                          len);
     }
     finish_out(d_out);
     end_of_call();

@@ -127,6 +127,20 @@ def linear_exact(act, w, bias, beta=0, result=None):
     return res
 
 
+def transpose_bytes(shards, m, n):
+    """shards[r]: uint8 [chunk_r(m), n, len] (rows split over the ranks) -> list of uint8 [m, chunk_r(n), len]."""
+    world = len(shards)
+    ln = shards[0].shape[2]
+    bn = (n + world - 1) // world
+    shards = [np.ascontiguousarray(s_, dtype=np.uint8) for s_ in shards]
+    outs = [np.zeros((m, max(0, min(bn, n - r * bn)), ln), dtype=np.uint8) for r in range(world)]
+    keep = [o if o.size else np.zeros(1, dtype=np.uint8) for o in outs]
+    src = (C.c_void_p * world)(*[s_.ctypes.data if s_.size else 0 for s_ in shards])
+    dst = (C.c_void_p * world)(*[o.ctypes.data for o in keep])
+    lib().orc_transpose_bytes(src, dst, C.c_int64(world), C.c_int64(m), C.c_int64(n), C.c_int64(ln))
+    return outs
+
+
 def layernorm_bf16(x, gamma, beta, eps):
     """x [rows, size] u16 (bf16 bits), gamma/beta [size] f32; returns [rows, size] u16."""
     x = np.ascontiguousarray(x, dtype=np.uint16)

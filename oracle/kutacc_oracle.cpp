@@ -543,6 +543,28 @@ void orc_all_gather_bytes(const uint8_t *const *shards, int64_t world, int64_t d
 }
 
 // ------------------------------------------------------------------------------------------------
+// Transpose (re-shard) over simulated ranks. Follows src/comm/transpose.cpp:21-86 in its normalised form
+// (after the swap of :27-33): rank r holds data [chunk_r(m), n, len] and receives out [m, chunk_r(n), len];
+// the element at local row bmi of rank s, column bni + d*block_n goes to rank d, row bmi + s*block_m, column
+// bni (:52-57 for the part that stays, :46-51 and :70-77 for the part that travels through the window).
+//   data[r] : dense [chunk_r(m)][n][len] bytes        out[r] : dense [m][chunk_r(n)][len] bytes
+// ------------------------------------------------------------------------------------------------
+void orc_transpose_bytes(const uint8_t *const *data, uint8_t *const *out, int64_t world, int64_t m, int64_t n, int64_t len)
+{
+    const int64_t bm = (m + world - 1) / world, bn = (n + world - 1) / world;
+    for (int64_t s = 0; s < world; ++s) {
+        const int64_t cm = std::max<int64_t>(0, std::min(bm, m - s * bm));
+        for (int64_t d = 0; d < world; ++d) {
+            const int64_t cn = std::max<int64_t>(0, std::min(bn, n - d * bn));
+            for (int64_t bmi = 0; bmi < cm; ++bmi)
+                for (int64_t bni = 0; bni < cn; ++bni)
+                    std::memcpy(out[d] + ((bmi + s * bm) * cn + bni) * len, data[s] + (bmi * n + bni + d * bn) * len,
+                                (size_t)len);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
 // LayerNorm of each row. Follows src/normalization/layernorm_kernel.h:22-53 (one row per call there):
 // sums of (x - x[0]) accumulated per vector lane (16 fp32 lanes) and then across the lanes, mean = sum/n +
 // x[0], var = max((sum2 - sum*sum/n)/n, 0), rstd = 1/sqrt(var + eps), y = fma(fma(x, rstd, -rstd*mean),

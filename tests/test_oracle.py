@@ -191,3 +191,33 @@ def test_layernorm_oracle_against_textbook_formula():
     x = np.full((1, 64), 3.0, dtype=np.float32)
     out = as_f32(O.layernorm_bf16(bf16_bits(x), np.ones(64, np.float32), np.full(64, 0.5, np.float32), 1e-5))
     assert np.array_equal(out, np.full((1, 64), 0.5, dtype=np.float32))
+
+
+def _transpose_golden(world, m, n):
+    """The closed-form byte grids of the reference's own test (test/functest/comm/transpose_test.cpp:19-81):
+    rank r holds an m x n byte grid counting up from 32*r; after the re-shard rank d holds column block d."""
+    data = [((np.arange(m * n) + 32 * r) % 256).astype(np.uint8).reshape(m, n, 1) for r in range(world)]
+    bn = (n + world - 1) // world
+    full = np.concatenate(data, axis=0)                        # [world*m, n, 1]
+    expect = [full[:, d * bn:min(n, (d + 1) * bn)] for d in range(world)]
+    return data, expect
+
+
+def test_transpose_oracle_reproduces_the_reference_golden_grid():
+    # transpose_test.cpp: world 2, m = 5 rows per rank, n = 6, len = 1, out [10, 3]; expect_data_0 counts
+    # 0,1,2 | 6,7,8 | ... with a jump to 32 at row 5, expect_data_1 the other three columns
+    data, expect = _transpose_golden(2, 5, 6)
+    got = O.transpose_bytes(data, 10, 6)
+    exp0 = np.array([[0, 1, 2], [6, 7, 8], [12, 13, 14], [18, 19, 20], [24, 25, 26],
+                     [32, 33, 34], [38, 39, 40], [44, 45, 46], [50, 51, 52], [56, 57, 58]], dtype=np.uint8)
+    assert np.array_equal(got[0][:, :, 0], exp0)
+    assert np.array_equal(got[1][:, :, 0], exp0 + 3)
+    for d in range(2):
+        assert np.array_equal(got[d], expect[d])
+    # ragged: 7 rows and 5 columns over 3 ranks (the last rank is short in both directions), 4-byte elements
+    rng = np.random.default_rng(3)
+    full = rng.integers(0, 255, (7, 5, 4), dtype=np.uint8)
+    shards = [full[r * 3:min(7, r * 3 + 3)] for r in range(3)]
+    outs = O.transpose_bytes(shards, 7, 5)
+    for d in range(3):
+        assert np.array_equal(outs[d], full[:, d * 2:min(5, d * 2 + 2)])
