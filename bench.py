@@ -358,14 +358,17 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    # Device-resident timing uses the library's enqueue-only mode (kutacc_b200_set_async): the call returns
+    # when its kernels are queued and the CUDA events bracket device time only. The synchronous default of the
+    # C ABI (what a caller of the reference sees) is what the end-to-end figure below measures.
+    api.set_async(True)
     for _ in range(args.warmup):
         case.run()
     barrier()
     launches0 = api.launch_count()
-    api.set_profile(True)
-    api.profile_read()
-    step_ms = []
-    with ClockSampler(local_rank) as clocks:
+
+    def timed_steps():
+        out_ms = []
         for _ in range(args.steps):
             flush.zero_()                                             # evict L2 between timed steps
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -373,11 +376,26 @@ def main():
             case.run()
             e1.record()
             e1.synchronize()
-            step_ms.append(e0.elapsed_time(e1))
+            out_ms.append(e0.elapsed_time(e1))
+        return out_ms
+
+    with ClockSampler(local_rank) as clocks:
+        step_ms = timed_steps()
         barrier()
+    launches = api.launch_count() - launches0
+    api.synchronize()
+    api.raise_if_error()
+    # Per-kernel CUDA events cost about 7 % of a step of this size, so the timed region above runs without
+    # them; the same K steps are repeated right away with the events on for the kernel breakdown.
+    api.set_profile(True)
+    api.profile_read()
+    timed_steps()
+    barrier()
     prof = api.profile_read()
     api.set_profile(False)
-    launches = api.launch_count() - launches0
+    api.synchronize()
+    api.raise_if_error()
+    api.set_async(False)
     total_ms = float(sum(step_ms))
     if world > 1:
         t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
@@ -395,6 +413,8 @@ def main():
     kshare = {n: sum(v) / max(sum(sum(x) for x in per_kernel.values()), 1e-9) for n, v in per_kernel.items()}
     peaks = measured_peaks()
     roofline = None
+    if kname == "attn_core" and kname not in per_kernel and "attn_f32" in per_kernel:
+        kname = "attn_f32"            # the fp32 shape runs the error-compensated tf32 kernel (three products per multiply)
     if kname == "global_fused" and kname not in per_kernel:
         kname = "global_out"          # shapes the one-pass kernel does not cover run the three-kernel path
     if kname in per_kernel:
@@ -406,6 +426,8 @@ def main():
                     "frac": achieved / peak, "traffic": NCU_TRAFFIC.get(args.workload) if args.rows <= 0 else None,
                     "peak_source": f"{peaks['source']} ({'burst bf16' if bound == 'tensor' else 'copy'})",
                     "kernel_ms_per_step": k_ms, "launches_per_step": launches_per_step,
+                    "measured": "CUDA events around every kernel on its stream, in a second pass of the same K steps "
+                                "directly after the timed region (the events themselves cost about 7 % of a step)",
                     "time_share": {n: round(s, 4) for n, s in kshare.items()}}
 
     # end to end: every tensor in pinned host memory, copies inside the library call
@@ -445,6 +467,8 @@ def main():
             "config": {"workload": args.workload, "B_per_gpu": w.B, "S": w.S, "H": w.H, "D": w.D, "C": w.C,
                        "pair_bias": w.has_nb, "gflop_per_call": w.flops() / 1e9,
                        "l2": "flushed between timed steps (256 MiB memset)",
+                       "call_mode": "value: enqueue-only calls (kutacc_b200_set_async), device time by CUDA events; "
+                                    "e2e: the synchronous default with host buffers",
                        "parallelism": f"rows sharded over {world} GPU(s), no collective"},
             "frac_of_bf16_peak": value / world / peaks["bf16_tflops"],
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches),

@@ -110,6 +110,7 @@ DeviceArg resolve_in(const void *p, size_t bytes);                     // copies
 DeviceArg resolve_out(void *p, size_t bytes);                          // no copy in
 void finish_out(const DeviceArg &a);                                    // device -> host when staged
 void end_of_call();                                                    // stream sync unless async
+void sync_and_check();                                                 // stream sync + device-side timeout report
 
 // Two extra non-blocking streams and a pool of events for calls that overlap host<->device copies with
 // compute on the runtime stream (created on first use, reused afterwards).

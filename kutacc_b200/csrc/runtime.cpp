@@ -178,14 +178,19 @@ void end_of_call()
 {
     cudaError_t e = cudaGetLastError();
     KUTACC_CHECK(e == cudaSuccess, "kernel launch failed: ", cudaGetErrorString(e));
-    if (!runtime().async) {
-        KUTACC_CUDA(cudaStreamSynchronize((cudaStream_t)runtime().stream));
-        dev::KernelErrorWord &ew = dev::kernel_error_word();
-        if (ew.host && *ew.host != 0) {
-            const int code = *ew.host;
-            *ew.host = 0;
-            KUTACC_CHECK(false, "a device-side wait ran out of time (site ", code, "); the result is invalid");
-        }
+    if (!runtime().async) sync_and_check();
+}
+
+// Wait for the runtime stream and report a device-side wait that ran out of time (the kernels write the
+// site into a host-visible word instead of hanging).
+void sync_and_check()
+{
+    KUTACC_CUDA(cudaStreamSynchronize((cudaStream_t)runtime().stream));
+    dev::KernelErrorWord &ew = dev::kernel_error_word();
+    if (ew.host && *ew.host != 0) {
+        const int code = *ew.host;
+        *ew.host = 0;
+        KUTACC_CHECK(false, "a device-side wait ran out of time (site ", code, "); the result is invalid");
     }
 }
 
@@ -196,7 +201,7 @@ extern "C" {
 void kutacc_b200_set_stream(void *cuda_stream) { kutacc::runtime().stream = cuda_stream; }
 void kutacc_b200_set_async(int enabled) { kutacc::runtime().async = enabled != 0; }
 void kutacc_b200_set_sm_margin(int sms) { kutacc::runtime().sm_margin = sms < 0 ? 0 : (sms > 64 ? 64 : sms); }
-void kutacc_b200_synchronize(void) { KUTACC_CUDA(cudaStreamSynchronize((cudaStream_t)kutacc::runtime().stream)); }
+void kutacc_b200_synchronize(void) { kutacc::sync_and_check(); }
 
 void *kutacc_b200_device_malloc(size_t bytes)
 {
