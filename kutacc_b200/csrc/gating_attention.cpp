@@ -84,6 +84,15 @@ static void gating_attention_impl(Tensor &input, int64_t batch, int64_t seq_len,
     const bool out_host = staged_bytes_needed(out.data_ptr(), out_bytes) != 0;
     const bool pipelined = x_host && out_host && B >= 8 && x_bytes >= ((size_t)4 << 20);
 
+    if (pipelined) {
+        // the copy streams may start as soon as the previous work on the runtime stream is done: mark that
+        // point before the small uploads below are queued, so that the first chunk travels beside them
+        CopyPipeline &cp0 = copy_pipeline(1);
+        if (kutacc_check_err_set) return;
+        KUTACC_CUDA(cudaEventRecord((cudaEvent_t)cp0.start, stream));
+        KUTACC_CUDA(cudaStreamWaitEvent((cudaStream_t)cp0.in, (cudaEvent_t)cp0.start, 0));
+        KUTACC_CUDA(cudaStreamWaitEvent((cudaStream_t)cp0.out, (cudaEvent_t)cp0.start, 0));
+    }
     DeviceArg d_x = pipelined ? resolve_out(input.data_ptr(), x_bytes) : resolve_in(input.data_ptr(), x_bytes);
     DeviceArg d_bias = resolve_in(bias.data_ptr(), bias_bytes);
     DeviceArg d_nb = has_nb ? resolve_in(nonbatched_bias.data_ptr(), nb_bytes) : DeviceArg{};
@@ -204,10 +213,6 @@ static void gating_attention_impl(Tensor &input, int64_t batch, int64_t seq_len,
         CopyPipeline &cp = copy_pipeline(nchunks);
         if (kutacc_check_err_set) return;
         cudaStream_t s_in = (cudaStream_t)cp.in, s_out = (cudaStream_t)cp.out;
-        // uploads must not start before the staging buffers are free of the previous call's work
-        KUTACC_CUDA(cudaEventRecord((cudaEvent_t)cp.start, stream));
-        KUTACC_CUDA(cudaStreamWaitEvent(s_in, (cudaEvent_t)cp.start, 0));
-        KUTACC_CUDA(cudaStreamWaitEvent(s_out, (cudaEvent_t)cp.start, 0));
         const size_t row_bytes = (size_t)S * C * es;
         for (int i = 0; i < nchunks && ok; ++i) {
             const int64_t b0 = chunk_begin[i], nbr = chunk_begin[i + 1] - b0;
