@@ -84,6 +84,26 @@ typedef struct kutacc_af2_attention_inputs {
     kutacc_tensor_h avg;
 } kutacc_af2_attention_inputs_t;
 
+/* replaces include/kutacc.h:194-202: weights of the transition operator. linear1_w is stored [c_i][c_o],
+ * linear2_w [c_o][c_i] (W[out][in]); the biases are fp32 vectors. */
+typedef struct kutacc_af2_trans_weights {
+    int64_t c_o;
+    int64_t c_i;
+    kutacc_tensor_h linear1_w;
+    kutacc_tensor_h linear1_b;
+    kutacc_tensor_h linear2_w;
+    kutacc_tensor_h linear2_b;
+} kutacc_af2_trans_weights_t;
+
+/* replaces include/kutacc.h:208-214: input_act is [batch, n_res, c_o] bf16 dense; intermediate_act is the
+ * reference's [batch, n_res, c_i] scratch, which this library does not write (it may be null). */
+typedef struct kutacc_af2_trans_act_inputs {
+    int64_t batch;
+    int64_t n_res;
+    kutacc_tensor_h input_act;
+    kutacc_tensor_h intermediate_act;
+} kutacc_af2_trans_act_inputs_t;
+
 #endif /* KUTACC_H */
 
 /* replaces include/kutacc.h:47 (src/version/version.cpp:28-35) */
@@ -142,6 +162,12 @@ KUTACC_B200_API void kutacc_af2_linear(kutacc_tensor_h act, kutacc_tensor_h weig
  * the element type as uint16_t bit patterns so that the header is plain C. */
 KUTACC_B200_API void kutacc_af2_linear_weight_prepack(const uint16_t *weight, uint16_t *result, int64_t n, int64_t k,
                                                       int64_t ldb, int64_t num_threads);
+
+/* replaces include/kutacc.h:321-322 (src/attention/transition.cpp:21-61): out = relu(input_act . linear1_w^T +
+ * linear1_b) . linear2_w^T + linear2_b, bf16 with fp32 accumulation and one bf16 rounding of the intermediate
+ * and of out; out is [batch, n_res, c_o] dense. */
+KUTACC_B200_API void kutacc_af2_transition(kutacc_af2_trans_act_inputs_t *trans_inputs_ptr,
+                                           kutacc_af2_trans_weights_t *trans_weights_ptr, kutacc_tensor_h out);
 
 /* replaces include/kutacc.h:334 (src/normalization/layernorm.cpp:17-20, layernorm_kernel.h:22-53): LayerNorm
  * of ONE row of `size` bf16 channels, out = bf16(fma(fma(x, rstd, -rstd * mean), gamma, beta)) with the

@@ -25,7 +25,7 @@ EXPORTS = [
     # part 1: the reference's interface for this path
     "kutacc_get_version", "kutacc_comm_init", "kutacc_comm_fini", "kutacc_af2_all_gather", "kutacc_af2_transpose",
     "kutacc_af2_gating_attention", "kutacc_af2_global_attention", "kutacc_af2_linear",
-    "kutacc_af2_linear_weight_prepack", "kutacc_af2_gemm_pack_get_size", "kutacc_af2_layernorm",
+    "kutacc_af2_linear_weight_prepack", "kutacc_af2_gemm_pack_get_size", "kutacc_af2_layernorm", "kutacc_af2_transition",
     # part 2: additions
     "kutacc_b200_tensor_create", "kutacc_b200_tensor_destroy", "kutacc_b200_error_set", "kutacc_b200_last_error",
     "kutacc_b200_clear_error", "kutacc_b200_set_stream", "kutacc_b200_set_async", "kutacc_b200_set_sm_margin", "kutacc_b200_synchronize",
@@ -51,6 +51,15 @@ class AttentionWeights(C.Structure):
     _fields_ = [("nchannels", C.c_int64), ("nheads", C.c_int64), ("head_size", C.c_int64),
                 ("query_w", C.c_void_p), ("key_w", C.c_void_p), ("value_w", C.c_void_p), ("gating_w", C.c_void_p),
                 ("gating_b", C.c_void_p), ("output_w", C.c_void_p), ("output_b", C.c_void_p)]
+
+
+class TransWeights(C.Structure):
+    _fields_ = [("c_o", C.c_int64), ("c_i", C.c_int64), ("linear1_w", C.c_void_p), ("linear1_b", C.c_void_p),
+                ("linear2_w", C.c_void_p), ("linear2_b", C.c_void_p)]
+
+
+class TransInputs(C.Structure):
+    _fields_ = [("batch", C.c_int64), ("n_res", C.c_int64), ("input_act", C.c_void_p), ("intermediate_act", C.c_void_p)]
 
 
 class AttentionInputs(C.Structure):
@@ -128,6 +137,8 @@ def lib() -> C.CDLL:
     L.kutacc_b200_global_attention_noalloc.restype = C.c_int
     L.kutacc_b200_pair_bias.argtypes = [vp, vp, vp]
     L.kutacc_b200_pair_bias.restype = None
+    L.kutacc_af2_transition.argtypes = [C.POINTER(TransInputs), C.POINTER(TransWeights), vp]
+    L.kutacc_af2_transition.restype = None
     L.kutacc_af2_layernorm.argtypes = [vp, vp, vp, C.c_int64, C.c_float, vp]
     L.kutacc_af2_layernorm.restype = None
     L.kutacc_b200_layernorm_rows.argtypes = [vp, vp, vp, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_float, vp]
@@ -304,6 +315,15 @@ def linear(act, weight, bias_ptr: Optional[int], result, beta: int = 0, check: b
 
 def pair_bias(z, wb, nb, check: bool = True) -> None:
     lib().kutacc_b200_pair_bias(_h(z), _h(wb), _h(nb))
+    if check:
+        raise_if_error()
+
+
+def transition(batch: int, n_res: int, c_o: int, c_i: int, input_act, w1, b1, w2, b2, out, check: bool = True) -> None:
+    """out = relu(input_act . w1^T + b1) . w2^T + b2 (kutacc_af2_transition); arguments are api.Tensor objects."""
+    wts = TransWeights(c_o, c_i, _h(w1), _h(b1), _h(w2), _h(b2))
+    ins = TransInputs(batch, n_res, _h(input_act), None)
+    lib().kutacc_af2_transition(C.byref(ins), C.byref(wts), _h(out))
     if check:
         raise_if_error()
 

@@ -69,6 +69,7 @@ struct GemmParams {
     int heads;
     int K;
     int S, B;
+    int relu;               // non-zero: max(0, .) after the bias, before the bf16 rounding
     int *err;
 };
 
@@ -221,15 +222,27 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p)
 #pragma unroll
                     for (int j4 = 0; j4 < 8; ++j4) {
                         const float4 bv = __ldg(reinterpret_cast<const float4 *>(bias + n) + j4);
-                        packed[2 * j4] = pack_bf16x2(__uint_as_float(r[c][4 * j4]) + bv.x,
-                                                     __uint_as_float(r[c][4 * j4 + 1]) + bv.y);
-                        packed[2 * j4 + 1] = pack_bf16x2(__uint_as_float(r[c][4 * j4 + 2]) + bv.z,
-                                                         __uint_as_float(r[c][4 * j4 + 3]) + bv.w);
+                        float y0 = __uint_as_float(r[c][4 * j4]) + bv.x, y1 = __uint_as_float(r[c][4 * j4 + 1]) + bv.y;
+                        float y2 = __uint_as_float(r[c][4 * j4 + 2]) + bv.z, y3 = __uint_as_float(r[c][4 * j4 + 3]) + bv.w;
+                        if (p.relu) {
+                            y0 = fmaxf(y0, 0.f);
+                            y1 = fmaxf(y1, 0.f);
+                            y2 = fmaxf(y2, 0.f);
+                            y3 = fmaxf(y3, 0.f);
+                        }
+                        packed[2 * j4] = pack_bf16x2(y0, y1);
+                        packed[2 * j4 + 1] = pack_bf16x2(y2, y3);
                     }
                 } else {
 #pragma unroll
-                    for (int j = 0; j < 16; ++j)
-                        packed[j] = pack_bf16x2(__uint_as_float(r[c][2 * j]), __uint_as_float(r[c][2 * j + 1]));
+                    for (int j = 0; j < 16; ++j) {
+                        float y0 = __uint_as_float(r[c][2 * j]), y1 = __uint_as_float(r[c][2 * j + 1]);
+                        if (p.relu) {
+                            y0 = fmaxf(y0, 0.f);
+                            y1 = fmaxf(y1, 0.f);
+                        }
+                        packed[j] = pack_bf16x2(y0, y1);
+                    }
                 }
                 // staging tile: row = lane, 64 bytes per row, 16-byte chunks swizzled as the 64-byte TMA mode
                 const uint32_t stg = stg0 + (uint32_t)c * STG_BYTES;
@@ -364,12 +377,13 @@ bool tcgen05_proj_qkvg_bf16(cudaStream_t stream, const void *x, const void *wq, 
     p.K = C;
     p.S = S;
     p.B = B;
+    p.relu = 0;
     p.err = ew.device;
     return launch(stream, maps, p, "proj_qkvg");
 }
 
 bool tcgen05_linear_bias_bf16(cudaStream_t stream, const void *a, const void *w, const float *bias, void *out,
-                              int64_t out_row_stride, int B, int S, int N, int K)
+                              int64_t out_row_stride, int B, int S, int N, int K, bool relu)
 {
     if (N % 128 != 0 || K % 64 != 0 || out_row_stride % 8 != 0 || ((uintptr_t)out & 15u) || ((uintptr_t)a & 15u) ||
         ((uintptr_t)w & 15u) || ((uintptr_t)bias & 15u))
@@ -398,8 +412,9 @@ bool tcgen05_linear_bias_bf16(cudaStream_t stream, const void *a, const void *w,
     p.K = K;
     p.S = S;
     p.B = B;
+    p.relu = relu ? 1 : 0;
     p.err = ew.device;
-    return launch(stream, maps, p, "linear_bias");
+    return launch(stream, maps, p, relu ? "linear_bias_relu" : "linear_bias");
 }
 
 }  // namespace dev

@@ -469,7 +469,22 @@ bool launch_pair_bias_mma(cudaStream_t stream, const void *z, const void *wb, vo
     return true;
 }
 
+__global__ void relu_bf16_kernel(__nv_bfloat16 *x, int64_t n)
+{
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+        if (__bfloat162float(x[i]) < 0.f) x[i] = __float2bfloat16_rn(0.f);
+}
+
 }  // namespace
+
+// max(0, .) over a dense bf16 buffer (fallback of the transition operator when the fused epilogue is not available)
+bool launch_relu_bf16(cudaStream_t stream, void *x, int64_t n)
+{
+    if (n <= 0) return true;
+    relu_bf16_kernel<<<(unsigned)std::min<int64_t>((n + 255) / 256, 148 * 16), 256, 0, stream>>>((__nv_bfloat16 *)x, n);
+    count_launch();
+    return true;
+}
 
 bool launch_gemm_generic(cudaStream_t stream, ElemType t, const void *a, int64_t lda, const void *w, int64_t ldw,
                          const float *bias, float beta, void *c, int64_t ldc, int64_t M, int64_t N, int64_t K)

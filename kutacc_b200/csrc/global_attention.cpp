@@ -61,6 +61,14 @@ extern "C" void kutacc_af2_global_attention(kutacc_af2_attention_inputs_t *q_bas
     // chunks with upload, kernels and download overlapped on three streams (as in the gated attention).
     const bool pipelined = staged_bytes_needed(x.data_ptr(), x_bytes) != 0 && staged_bytes_needed(o.data_ptr(), out_bytes) != 0 &&
                            B >= 8 && x_bytes >= ((size_t)4 << 20) && out_rs == C;
+    if (pipelined) {
+        // the copy streams may start once the previous work on the runtime stream is done, beside the small uploads
+        CopyPipeline &cp0 = copy_pipeline(1);
+        if (kutacc_check_err_set) return;
+        KUTACC_CUDA(cudaEventRecord((cudaEvent_t)cp0.start, stream));
+        KUTACC_CUDA(cudaStreamWaitEvent((cudaStream_t)cp0.in, (cudaEvent_t)cp0.start, 0));
+        KUTACC_CUDA(cudaStreamWaitEvent((cudaStream_t)cp0.out, (cudaEvent_t)cp0.start, 0));
+    }
     DeviceArg d_x = pipelined ? resolve_out(x.data_ptr(), x_bytes) : resolve_in(x.data_ptr(), x_bytes);
     DeviceArg d_m = resolve_in(mask.data_ptr(), m_bytes);
     DeviceArg d_wq = resolve_in(wq.data_ptr(), wcc), d_wk = resolve_in(wk.data_ptr(), wdc),
@@ -107,9 +115,6 @@ extern "C" void kutacc_af2_global_attention(kutacc_af2_attention_inputs_t *q_bas
         CopyPipeline &cp = copy_pipeline(nchunks);
         if (kutacc_check_err_set) return;
         cudaStream_t s_in = (cudaStream_t)cp.in, s_out = (cudaStream_t)cp.out;
-        KUTACC_CUDA(cudaEventRecord((cudaEvent_t)cp.start, stream));
-        KUTACC_CUDA(cudaStreamWaitEvent(s_in, (cudaEvent_t)cp.start, 0));
-        KUTACC_CUDA(cudaStreamWaitEvent(s_out, (cudaEvent_t)cp.start, 0));
         const size_t col_bytes = (size_t)S * C * 2;
         for (int i = 0; i < nchunks && ok; ++i) {
             const int64_t b0 = chunk_begin[i], nb = chunk_begin[i + 1] - b0;

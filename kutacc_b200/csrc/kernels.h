@@ -31,7 +31,7 @@ bool tcgen05_proj_qkvg_bf16(cudaStream_t stream, const void *x, const void *wq, 
                             const void *wg, const float *bg, void *q, void *k, void *v, void *gate, int B, int S,
                             int H, int D, bool v_transposed, int64_t v_pitch);
 bool tcgen05_linear_bias_bf16(cudaStream_t stream, const void *a, const void *w, const float *bias, void *out,
-                              int64_t out_row_stride, int B, int S, int N, int K);
+                              int64_t out_row_stride, int B, int S, int N, int K, bool relu = false);
 
 // ---- fused attention core ------------------------------------------------------------------------
 // avg[b, s, h*D + d] = sigmoid(gate[b, s, h*D + d]) * softmax_k(bf16(q.k)*scale + bias[b,k] + nb[h,s,k]) . v
@@ -53,6 +53,7 @@ bool tcgen05_attn_core_bf16(cudaStream_t stream, const void *q, const void *k, c
 // ldw, c row stride ldc.
 bool launch_gemm_generic(cudaStream_t stream, ElemType t, const void *a, int64_t lda, const void *w, int64_t ldw,
                          const float *bias, float beta, void *c, int64_t ldc, int64_t M, int64_t N, int64_t K);
+bool launch_relu_bf16(cudaStream_t stream, void *x, int64_t n);
 // Attention core on [B, S, C]-shaped q/k/v/gate (head h at channel offset h*D); scale applied here.
 bool launch_attn_generic(cudaStream_t stream, ElemType t, const void *q, const void *k, const void *v,
                          const void *gate, const void *bias, int64_t bias_stride0, const void *nb,

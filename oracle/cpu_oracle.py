@@ -127,6 +127,20 @@ def linear_exact(act, w, bias, beta=0, result=None):
     return res
 
 
+def transition_bf16(x, w1, b1, w2, b2):
+    """Transition MLP as src/attention/transition.cpp:31-38 runs it: two addmm calls with a row bias, the first
+    with ReLU, the intermediate stored as bf16. x [M, c_o] u16, w1 [c_i, c_o] u16, w2 [c_o, c_i] u16, biases f32.
+    (Where the closed GEMM applies the ReLU relative to its bf16 rounding cannot be seen; the two orders agree.)"""
+    hid = linear_bf16(x, w1, b1)
+    hid = np.where(hid & 0x8000, np.uint16(0), hid).astype(np.uint16)       # relu on bf16 bits (-0 -> +0)
+    return linear_bf16(hid, w2, b2)
+
+
+def transition_exact(x, w1, b1, w2, b2):
+    hid = np.maximum(linear_exact(x, w1, b1), 0.0).astype(np.float32)
+    return linear_exact(hid, w2, b2)
+
+
 def transpose_bytes(shards, m, n):
     """shards[r]: uint8 [chunk_r(m), n, len] (rows split over the ranks) -> list of uint8 [m, chunk_r(n), len]."""
     world = len(shards)

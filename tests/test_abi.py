@@ -41,7 +41,7 @@ def test_library_exports_every_declared_symbol(kutacc_lib):
     assert hasattr(kutacc_lib, "_ZN6kutacc13TensorWrapperC1EPvOSt6vectorIlSaIlEES5_lNS_14TensorDataTypeE")
     assert hasattr(kutacc_lib, "_ZN6kutacc13TensorWrapperD1Ev")
     # entry points of the reference outside this path still resolve (they report "not built")
-    for name in ("kutacc_af2_transition",
+    for name in ("kutacc_af2_outer_product_mean_chunk",
                  "kutacc_af2_invariant_point", "kutacc_af2_triangle_multiplication_last"):
         assert hasattr(kutacc_lib, name)
 
@@ -139,8 +139,12 @@ def test_error_flag_is_sticky_and_clearable(kutacc_lib):
 
 
 def test_not_built_entry_points_report(kutacc_lib):
-    kutacc_lib.kutacc_af2_transition()
+    kutacc_lib.kutacc_af2_triangle_multiplication_last()
     assert api.error_set() and "not part of" in api.last_error()
+    api.clear_error()
+    # null arguments of a built operator are reported in the reference's words, nothing is dereferenced
+    kutacc_lib.kutacc_af2_transition(None, None, None)
+    assert api.error_set() and "nullptr" in api.last_error()
 
 
 def test_tensor_descriptor_checks(kutacc_lib):
