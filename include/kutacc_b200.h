@@ -254,6 +254,13 @@ KUTACC_B200_API int kutacc_b200_global_attention_noalloc(const void *q_data, con
                                                          int64_t batch, int64_t seq_len, int64_t nheads,
                                                          int64_t head_size, void *cuda_stream);
 
+/* Self-test of the failure-detection path: launches a one-warp kernel that waits, for at most
+ * limit_microseconds (1..100000), on a barrier nothing arrives on. The wait gives up, the kernel returns
+ * normally, and the usual error convention reports "a device-side wait ran out of time" at the next
+ * synchronisation (at once in synchronous mode). Returns 0 when the kernel was launched. No GPU fault is
+ * involved; the context stays usable. */
+KUTACC_B200_API int kutacc_b200_selftest_wait_timeout(int64_t limit_microseconds);
+
 /* Pair-bias projection written directly in the layout the attention operator consumes:
  * nb[h, q, k] = z[q, k, :] . wb[h, :]   with z [rows, n_k, c_z], wb [nheads, c_z], nb
  * [nheads, rows, n_k] (row stride of head h = nb_head_stride elements). Same arithmetic as

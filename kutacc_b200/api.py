@@ -32,7 +32,7 @@ EXPORTS = [
     "kutacc_b200_device_malloc", "kutacc_b200_device_free", "kutacc_b200_memcpy_h2d", "kutacc_b200_memcpy_d2h",
     "kutacc_b200_workspace_bytes", "kutacc_b200_release_workspace", "kutacc_b200_launch_count",
     "kutacc_b200_set_profile", "kutacc_b200_profile_read", "kutacc_b200_comm_unique_id", "kutacc_b200_comm_init_with_id", "kutacc_b200_pair_bias",
-    "kutacc_b200_global_attention_noalloc", "kutacc_b200_layernorm_rows",
+    "kutacc_b200_global_attention_noalloc", "kutacc_b200_layernorm_rows", "kutacc_b200_selftest_wait_timeout",
 ]
 EXPORTED_DATA = ["world_size", "rank"]
 
@@ -137,6 +137,8 @@ def lib() -> C.CDLL:
     L.kutacc_b200_global_attention_noalloc.restype = C.c_int
     L.kutacc_b200_pair_bias.argtypes = [vp, vp, vp]
     L.kutacc_b200_pair_bias.restype = None
+    L.kutacc_b200_selftest_wait_timeout.argtypes = [C.c_int64]
+    L.kutacc_b200_selftest_wait_timeout.restype = C.c_int
     L.kutacc_af2_transition.argtypes = [C.POINTER(TransInputs), C.POINTER(TransWeights), vp]
     L.kutacc_af2_transition.restype = None
     L.kutacc_af2_layernorm.argtypes = [vp, vp, vp, C.c_int64, C.c_float, vp]

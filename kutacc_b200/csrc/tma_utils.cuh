@@ -59,18 +59,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
         : "memory");
     return ok != 0;
 }
-// Bounded wait. `code` identifies the wait site in the error word.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int *err, int code)
+// Bounded wait. `code` identifies the wait site in the error word; `limit` is in SM clocks.
+__device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, int *err, int code, long long limit)
 {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     while (!mbar_try_wait(bar, parity)) {
-        if (clock64() - t0 > 4000000000LL) {  // ~2 s at 1.9 GHz
+        if (clock64() - t0 > limit) {
             if (err) atomicCAS(err, 0, code);
             return false;
         }
     }
     return true;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int *err, int code)
+{
+    return mbar_wait_limit(bar, parity, err, code, 4000000000LL);  // ~2 s at 1.9 GHz
 }
 
 // The same wait for a whole warp. Lanes can leave the polling loop at different iterations; the vote at
