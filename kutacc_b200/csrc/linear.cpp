@@ -2,6 +2,7 @@
 // Replaces src/linear/linear.cpp:21-50, src/linear/mm.cpp:94-110, src/utils/blas.cpp:93-98.
 #include <cuda_runtime.h>
 
+#include <climits>
 #include <cstring>
 
 #include "common.h"
@@ -49,7 +50,13 @@ extern "C" void kutacc_af2_linear(kutacc_tensor_h act_h, kutacc_tensor_h weight_
     const dev::ElemType et = dt == kFP32 ? dev::kElemF32 : dev::kElemBF16;
     bool ok = false;
     const bool a16 = (((uintptr_t)d_a.dev | (uintptr_t)d_w.dev) & 15u) == 0;
-    if (dt == kBF16 && beta == 0 && a16 && k % 64 == 0 && n % 64 == 0 && lda % 8 == 0 && ldw == k) {
+    if (dt == kBF16 && beta == 0 && a16 && k % 64 == 0 && n % 128 == 0 && lda == k && ldw == k && m <= INT32_MAX) {
+        // the tcgen05 projection kernel on the [1, m, k] view of the activations
+        ok = dev::tcgen05_linear_bias_bf16(stream, d_a.dev, d_w.dev, (const float *)d_b.dev, d_r.dev, n, 1, (int)m, (int)n,
+                                           (int)k);
+        if (kutacc_check_err_set) return;
+    }
+    if (!ok && dt == kBF16 && beta == 0 && a16 && k % 64 == 0 && n % 64 == 0 && lda % 8 == 0 && ldw == k) {
         ok = dev::launch_linear_bias_bf16(stream, d_a.dev, lda, d_w.dev, (const float *)d_b.dev, d_r.dev, n, m, (int)n,
                                           (int)k);
     } else if (beta == 0 && bias_data == nullptr && n <= 16 && lda == k && ldw == k && k <= INT32_MAX) {

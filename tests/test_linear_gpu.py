@@ -16,7 +16,7 @@ def _bf16_cuda(a):
     return torch.from_numpy(W.bf16_bits(a).view(np.int16)).view(torch.bfloat16).to(DEV)
 
 
-@pytest.mark.parametrize("M,N,K,bias,beta", [(300, 128, 128, True, 0), (1000, 4, 128, False, 0), (77, 8, 64, False, 0),
+@pytest.mark.parametrize("M,N,K,bias,beta", [(300, 128, 128, True, 0), (513, 256, 192, False, 0), (1000, 4, 128, False, 0), (77, 8, 64, False, 0),
                                              (50, 24, 40, True, 0), (64, 64, 64, True, 1), (33, 5, 17, False, 2)])
 def test_linear_bf16(kutacc_lib, M, N, K, bias, beta):
     rng = np.random.default_rng(M + N)
