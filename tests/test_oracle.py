@@ -221,3 +221,18 @@ def test_transpose_oracle_reproduces_the_reference_golden_grid():
     outs = O.transpose_bytes(shards, 7, 5)
     for d in range(3):
         assert np.array_equal(outs[d], full[:, d * 2:min(5, d * 2 + 2)])
+
+
+def test_new_operator_oracles_against_committed_vectors():
+    # regression vectors of the oracle itself (tests/golden/make_golden.py) plus the reference's re-shard grid
+    from kutacc_b200.workloads import as_f32
+    g = np.load(os.path.join(GOLD, "transpose_grid.npz"))
+    outs = O.transpose_bytes([g["data0"], g["data1"]], 10, 6)
+    assert np.array_equal(outs[0], g["expect0"]) and np.array_equal(outs[1], g["expect1"])
+    ln = np.load(os.path.join(GOLD, "layernorm_small.npz"))
+    assert np.array_equal(O.layernorm_bf16(ln["x"], ln["gamma"], ln["beta"], float(ln["eps"])), ln["faithful"])
+    assert np.allclose(O.layernorm_exact(as_f32(ln["x"]), ln["gamma"], ln["beta"], float(ln["eps"])), ln["exact"], rtol=0, atol=1e-6)
+    tr = np.load(os.path.join(GOLD, "transition_small.npz"))
+    assert np.array_equal(O.transition_bf16(tr["x"], tr["w1"], tr["b1"], tr["w2"], tr["b2"]), tr["faithful"])
+    assert np.allclose(O.transition_exact(as_f32(tr["x"]), as_f32(tr["w1"]), tr["b1"], as_f32(tr["w2"]), tr["b2"]), tr["exact"],
+                       rtol=0, atol=1e-5)
