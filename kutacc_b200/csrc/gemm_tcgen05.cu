@@ -46,6 +46,7 @@ constexpr int STAGE_BYTES = 2 * SLAB_BYTES;
 constexpr int EPI_WARPS = 8;                            // two per TMEM lane quarter, 64 columns each
 constexpr int STG_BYTES = 32 * 32 * 2;                  // one 32 x 32 bf16 staging tile
 constexpr int STG_PER_WARP = 2;
+static_assert(STG_PER_WARP == 2, "the epilogue writes its two 32-column halves into staging tiles 0 and 1 of its warp");
 constexpr int STG_OFF = NSTAGE * STAGE_BYTES;
 constexpr int BAR_OFF = STG_OFF + EPI_WARPS * STG_PER_WARP * STG_BYTES;
 constexpr int NBARS = 2 * NSTAGE + 2 * ACC_STAGES;
