@@ -196,9 +196,15 @@ def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return 0
+    # torchrun gives every rank OMP_NUM_THREADS=1; rank 0 alone runs the CPU arm and may use every host core
+    # (the OpenMP runtime reads the variable when the oracle library is loaded, below)
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
     from kutacc_b200 import workloads as W
     from oracle import cpu_oracle as O
     from tests import helpers
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        O.set_num_threads(os.cpu_count() or 1)
     name = args.workload
     kind, dtype, B, S, H, D, c_z, seed = W.spec(name)
     run = (lambda ww: helpers.oracle_exact(ww)) if dtype == "fp32" else (lambda ww: helpers.oracle_faithful(ww))

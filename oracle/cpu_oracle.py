@@ -32,6 +32,10 @@ def num_threads() -> int:
     return int(lib().orc_num_threads())
 
 
+def set_num_threads(n: int) -> None:
+    lib().orc_set_num_threads(C.c_int(int(n)))
+
+
 def f32_to_bf16(a: np.ndarray) -> np.ndarray:
     a = np.ascontiguousarray(a, dtype=np.float32)
     out = np.empty(a.shape, dtype=np.uint16)

@@ -121,6 +121,16 @@ void widen(const uint16_t *src, int64_t n, std::vector<float> &dst)
 
 extern "C" {
 
+// number of OpenMP threads later parallel regions use (a launcher may have exported OMP_NUM_THREADS=1)
+void orc_set_num_threads(int n)
+{
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int orc_num_threads()
 {
 #ifdef _OPENMP
