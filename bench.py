@@ -3,18 +3,25 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
 
-A "step" is one call of kutacc_af2_gating_attention (or kutacc_af2_global_attention) on one batch of
-seeded synthetic input of the named shape. Rank 0 prints one JSON line:
+Default workload: ``triangle_end_1024`` (triangle attention around the ending node, 1024 x 1024 pair
+representation, 723 GFLOP per call). A "step" is ONE such problem: the pair-bias projection of the rows of z,
+kutacc_af2_gating_attention on them, and with N > 1 (launched by torch.distributed.run, one rank per GPU)
+the two collectives of the sharded flow: the rows are split over the ranks, each rank projects the pair bias
+of its rows, the ranks all-gather the bias [4, 1024, 1024] and, after the attention, the output rows
+(kutacc_af2_all_gather over NCCL). Total work is fixed as N grows (strong scaling). Rank 0 prints one JSON line:
 
   value / ms_per_step  whole-job TFLOP/s (algorithmic FLOPs, 2 per multiply-add) with inputs resident
-                       in HBM, timed with CUDA events on the launching stream, max over ranks
-  e2e                  the same call with every tensor in pinned HOST memory: the library's own
-                       host->device and device->host copies are inside the timed region
-  roofline             the dominant kernel of the call, timed live with CUDA events
+                       in HBM, timed with CUDA events on the launching stream, max over ranks per step
+  e2e                  the same problem with each rank's rows of z and of the mask in pinned HOST memory and its
+                       output rows delivered to pinned host memory: copies inside the timed region
+  roofline             the dominant kernel (the fused attention core), timed live with CUDA events
+  compute_only         the same step with the output rows left sharded (the state the reference operator leaves)
+  phases_ms            pair-bias projection, bias all-gather, attention, exposed part of the output gather
   cpu_baseline         the CPU restatement of the reference on the host cores (rank 0, N = 1 only)
+  global_attention     N = 1 only: the extra-MSA global column attention (its one-pass kernel against the HBM copy)
 
-With N > 1 (launched by torch.distributed.run, one rank per GPU) every rank processes its own batch
-of rows of the same shape: rows are independent problems, nothing is exchanged (weak scaling).
+Other workloads (``--workload``) that are not triangle shapes, and ``--scaling weak``, run every rank on its
+own batch of rows with no collective (weak scaling).
 
 --impl reference times the CPU restatement of the reference's algorithm on the host cores (the
 reference's own ARM SVE sources do not compile on this x86 host) on a bounded sample of the same
@@ -35,7 +42,8 @@ sys.path.insert(0, ROOT)
 
 import numpy as np  # noqa: E402
 
-DEFAULT_WORKLOAD = "triangle_start_384"
+DEFAULT_WORKLOAD = "triangle_end_1024"
+TRIANGLE = ("triangle_start_384", "triangle_end_1024")
 METRIC = "gated_attention_tflops"
 UNIT = "TFLOP/s"
 
@@ -111,13 +119,31 @@ class ClockSampler:
                 "reasons": sorted(self.reasons), "samples": len(self.samples)}
 
 
-def dominant_kernel(workload):
+def config_for(name, world, scaling, slabs=None):
+    """The `config` object of the JSON line: the same for both arms (`--impl ours` and `--impl reference`)."""
+    from kutacc_b200 import workloads as W
+    kind, dtype, B, S, H, D, c_z, seed = W.spec(name)
+    if scaling == "strong":
+        par = (f"rows of one problem over {world} GPU(s)"
+               + ("; NCCL all-gather of the projected pair bias and of the output rows, output gather overlapped "
+                  "slab by slab" if world > 1 else "; single GPU, no collective"))
+    else:
+        par = f"every rank runs the whole workload on its own rows ({world} GPU(s)), no collective"
+    probe = W.Workload(name=name, kind=kind, dtype=dtype, B=B, S=S, H=H, D=D, seed=seed, c_z=c_z,
+                       has_nb=bool(c_z) and kind == "gating")
+    return {"workload": name, "B": B, "S": S, "H": H, "D": D, "C": H * D, "pair_bias": probe.has_nb,
+            "gflop_per_call": probe.flops() / 1e9, "l2": "flushed between timed steps (256 MiB memset)",
+            "parallelism": par}
+
+
+def dominant_kernel(workload, rows=None):
     """(kernel name in the library's profile record, bound, algorithmic work per call, unit)."""
+    B = workload.B if rows is None else rows
     if workload.kind == "gating":
         # Q.K^T and P.V: 4*B*S^2*C FLOPs, all inside the fused attention core
-        return "attn_core", "tensor", 4.0 * workload.B * workload.S * workload.S * workload.C, "TFLOP/s"
+        return "attn_core", "tensor", 4.0 * B * workload.S * workload.S * workload.C, "TFLOP/s"
     # global attention: one kernel reads x once and writes out once: bandwidth bound
-    return "global_fused", "hbm", 2.0 * workload.B * workload.S * workload.C * 2, "GB/s"
+    return "global_fused", "hbm", 2.0 * B * workload.S * workload.C * 2, "GB/s"
 
 
 def torch_cpu_gating(w, reps: int = 3):
@@ -150,15 +176,15 @@ def torch_cpu_gating(w, reps: int = 3):
             run()
             times.append(time.perf_counter() - t0)
     t = min(times)
-    return {"value": w.flops() / t / 1e12, "unit": UNIT, "threads": torch.get_num_threads(), "ms_per_pass": t * 1e3,
-            "sample_rows": w.B}
+    return {"value": w.flops(pair_bias=False) / t / 1e12, "unit": UNIT, "threads": torch.get_num_threads(),
+            "ms_per_pass": t * 1e3, "sample_rows": w.B}
 
 
 def cpu_baseline(name: str, budget_s: float = 12.0):
-    """CPU restatement of the reference on a bounded sample (a subset of the batch rows)."""
+    """CPU restatement of the reference on a bounded sample (a subset of the batch rows). The pair bias is an
+    input of the reference operator, so its projection is outside both the timed pass and the FLOP count."""
     from kutacc_b200 import workloads as W
     from oracle import cpu_oracle as O
-    sys.path.insert(0, os.path.join(ROOT, "tests"))
     from tests import helpers
     kind, dtype, B, S, H, D, c_z, seed = W.spec(name)
     rows = min(B, 8)
@@ -184,7 +210,7 @@ def cpu_baseline(name: str, budget_s: float = 12.0):
             torch_cpu = torch_cpu_gating(w)
         except Exception as exc:                                       # a second opinion only: never fatal
             torch_cpu = {"error": str(exc)[:200]}
-    return {"value": w.flops() / t / 1e12, "unit": UNIT, "cores": O.num_threads(), "kind": "port",
+    return {"value": w.flops(pair_bias=False) / t / 1e12, "unit": UNIT, "cores": O.num_threads(), "kind": "port",
             "torch_cpu": torch_cpu,
             "sample": f"{w.B} of {B} batch rows of {name} (full sequence length {S}), best of {len(times)} runs, "
                       f"{t * 1e3:.1f} ms per pass",
@@ -194,16 +220,17 @@ def cpu_baseline(name: str, budget_s: float = 12.0):
 def run_reference_arm(args):
     """The reference's CPU implementation, as restated in oracle/ (the ARM sources do not compile here)."""
     rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
     if rank != 0:
         return 0
     # torchrun gives every rank OMP_NUM_THREADS=1; rank 0 alone runs the CPU arm and may use every host core
     # (the OpenMP runtime reads the variable when the oracle library is loaded, below)
-    if int(os.environ.get("WORLD_SIZE", "1")) > 1:
+    if world > 1:
         os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
     from kutacc_b200 import workloads as W
     from oracle import cpu_oracle as O
     from tests import helpers
-    if int(os.environ.get("WORLD_SIZE", "1")) > 1:
+    if world > 1:
         O.set_num_threads(os.cpu_count() or 1)
     name = args.workload
     kind, dtype, B, S, H, D, c_z, seed = W.spec(name)
@@ -214,7 +241,7 @@ def run_reference_arm(args):
     t_row = (time.perf_counter() - t0) / probe.B
     total_steps = args.steps + args.warmup
     rows = int(max(1, min(B, 150.0 / max(total_steps, 1) / max(t_row, 1e-6))))
-    w = W.make(name, rows=rows)
+    w = W.make(name, rows=rows) if rows != probe.B else probe
     for _ in range(args.warmup):
         run(w)
     times = []
@@ -223,14 +250,17 @@ def run_reference_arm(args):
         run(w)
         times.append(time.perf_counter() - t0)
     t = sum(times) / len(times)
-    val = w.flops() / t / 1e12
+    val = w.flops(pair_bias=False) / t / 1e12
     sample = f"{rows} of {B} batch rows of {name} per step (full sequence length {S})"
+    scaling = resolve_scaling(args, name)
     line = {
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "weak",
+        "warmup": args.warmup, "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": scaling,
         "vs_baseline": None, "dtype": dtype, "data": "synthetic (seeded numpy, AlphaFold2 model shapes)",
-        "config": {"workload": name, "B": B, "S": S, "H": H, "D": D, "C": H * D, "sample_rows": rows,
-                   "note": "CPU restatement of the reference algorithm (oracle/), host cores only"},
+        "config": config_for(name, max(world, args.gpus, 1), scaling),
+        "note": "CPU restatement of the reference algorithm (oracle/), host cores only; ms_per_step is the time of the "
+                "sampled rows, value is per-row throughput and does not depend on the sample size",
+        "ms_full_call_est": t * 1e3 * B / rows,
         "cpu_baseline": {"value": val, "unit": UNIT, "cores": O.num_threads(), "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -239,12 +269,57 @@ def run_reference_arm(args):
     return 0
 
 
-def run_strong_scaling(args, torch, dist, api, W, dev, world, rank, local_rank):
+def resolve_scaling(args, name):
+    if args.scaling != "auto":
+        return args.scaling
+    return "strong" if name in TRIANGLE else "weak"
+
+
+def _events(torch):
+    return torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+
+def global_attention_extra(torch, api, W, runner, dev, peaks, steps=10):
+    """The extra-MSA global column attention (one launch of the one-pass kernel) on this GPU: device time per
+    call and the achieved fraction of the measured HBM copy bandwidth."""
+    g = W.make("extra_msa_global")
+    case = runner.DeviceCase(g, device=dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    api.set_async(True)
+    try:
+        for _ in range(3):
+            case.run()
+        torch.cuda.synchronize()
+        ms = []
+        for _ in range(steps):
+            flush.zero_()
+            e0, e1 = _events(torch)
+            e0.record()
+            case.run()
+            e1.record()
+            e1.synchronize()
+            ms.append(e0.elapsed_time(e1))
+        api.synchronize()
+        api.raise_if_error()
+    finally:
+        api.set_async(False)
+    t = sum(ms) / len(ms)
+    nbytes = 2.0 * g.B * g.S * g.C * 2
+    gbs = nbytes / (t * 1e-3) / 1e9
+    del case, flush
+    torch.cuda.empty_cache()
+    return {"workload": "extra_msa_global", "ms_per_call": t, "value": g.flops() / (t * 1e-3) / 1e12, "unit": UNIT,
+            "roofline": {"kernel": "global_fused", "bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": gbs / peaks["hbm_gbs"], "peak_source": f"{peaks['source']} (copy)",
+                         "algorithmic_bytes": nbytes}}
+
+
+def run_strong_scaling(args, torch, dist, api, W, runner, dev, world, rank, local_rank):
     """One triangle-attention problem split over the ranks: pair-bias projection, bias all-gather, attention
     on this rank's rows, output all-gather (kutacc_b200/sharding.py). Total work is fixed as N grows."""
     from kutacc_b200 import sharding
-    w = W.make(args.workload)
-    if not (w.kind == "gating" and w.has_nb and "z" in w.arrays and w.B == w.S):
+    w = W.make(args.workload, with_nb=False)
+    if not (w.kind == "gating" and "wb" in w.arrays and w.B == w.S):
         raise SystemExit("--scaling strong needs a triangle workload (triangle_start_384, triangle_end_1024)")
     if world > 1:
         uid = torch.zeros(128, dtype=torch.uint8, device=dev)
@@ -252,8 +327,10 @@ def run_strong_scaling(args, torch, dist, api, W, dev, world, rank, local_rank):
             uid = torch.tensor(list(api.comm_unique_id()), dtype=torch.uint8, device=dev)
         dist.broadcast(uid, 0)
         api.comm_init(world, rank, 0, bytes(uid.cpu().tolist()))
-    op = sharding.ShardedTriangleAttention(w, rank, world, args.slabs, dev, sm_margin=args.sm_margin)
+    slabs = args.slabs if world > 1 else 1
+    op = sharding.ShardedTriangleAttention(w, rank, world, slabs, dev, sm_margin=args.sm_margin)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    rows_per_rank = w.B // world
 
     def barrier():
         torch.cuda.synchronize()
@@ -261,44 +338,155 @@ def run_strong_scaling(args, torch, dist, api, W, dev, world, rank, local_rank):
             dist.barrier()
         torch.cuda.synchronize()
 
+    def max_over_ranks(values):
+        t = torch.tensor(values, dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.tolist()
+
+    def timed(n, gather):
+        out_ms, phases = [], []
+        for _ in range(n):
+            flush.zero_()
+            barrier()                                                 # ranks enter the step together
+            e0, e1 = _events(torch)
+            e0.record()
+            op.step(gather_output=gather)
+            e1.record()
+            e1.synchronize()
+            out_ms.append(e0.elapsed_time(e1))
+            phases.append(op.phase_ms())
+        return out_ms, phases
+
     for _ in range(args.warmup):
         op.step(gather_output=not args.leave_sharded)
     barrier()
     launches0 = api.launch_count()
-    step_ms = []
     with ClockSampler(local_rank) as clocks:
-        for _ in range(args.steps):
-            flush.zero_()
-            barrier()                                                 # ranks enter the step together
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            op.step(gather_output=not args.leave_sharded)
-            e1.record()
-            e1.synchronize()
-            step_ms.append(e0.elapsed_time(e1))
+        step_ms, phases = timed(args.steps, not args.leave_sharded)
         barrier()
     launches = api.launch_count() - launches0
-    t = torch.tensor(step_ms, dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)                      # per step, the slowest rank
-    ms_per_step = float(t.sum().item()) / args.steps
+    api.synchronize()
+    api.raise_if_error()
+    step_ms = max_over_ranks(step_ms)                                  # per step, the slowest rank
+    ms_per_step = sum(step_ms) / args.steps
     value = w.flops() / (ms_per_step * 1e-3) / 1e12
+    names = list(phases[0])
+    ph = max_over_ranks([sum(p[k] for p in phases) / len(phases) for k in names])
+    phases_ms = {k: round(v, 4) for k, v in zip(names, ph)}
+
+    # the same step with the output rows left sharded (what the reference operator itself leaves behind)
+    n_co = max(3, min(args.steps, 10))
+    co_ms, _ = timed(n_co, False)
+    co = sum(max_over_ranks(co_ms)) / n_co
+    compute_only = {"ms_per_step": co, "value": w.flops() / (co * 1e-3) / 1e12, "unit": UNIT,
+                    "note": "output rows left sharded over the ranks (no output all-gather)"}
+
+    # per-kernel CUDA events (they cost a few per cent of a step, so they run in a pass of their own)
+    api.set_profile(True)
+    api.profile_read()
+    n_prof = max(3, min(args.steps, 10))
+    timed(n_prof, not args.leave_sharded)
+    barrier()
+    prof = api.profile_read()
+    api.set_profile(False)
+    api.synchronize()
+    api.raise_if_error()
+    per_kernel = {}
+    for n, ms in prof:
+        per_kernel.setdefault(n, []).append(ms)
+    peaks = measured_peaks()
+    roofline = None
+    if "attn_core" in per_kernel:
+        k_ms = max_over_ranks([sum(per_kernel["attn_core"]) / n_prof])[0]      # the slowest rank's kernel time per step
+        work = 4.0 * rows_per_rank * w.S * w.S * w.C
+        achieved = work / (k_ms * 1e-3) / 1e12
+        tot = max(sum(sum(v) for v in per_kernel.values()), 1e-9)
+        traffic = NCU_TRAFFIC.get(args.workload)
+        roofline = {"kernel": "attn_core", "bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"],
+                    "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
+                    "traffic": traffic * rows_per_rank / w.B if traffic else None,
+                    "peak_source": f"{peaks['source']} (burst bf16)", "kernel_ms_per_step": k_ms,
+                    "launches_per_step": len(per_kernel["attn_core"]) / n_prof,
+                    "algorithmic_flops_per_step_per_gpu": work,
+                    "measured": "CUDA events around every kernel on its stream, per rank (slowest rank reported), in a "
+                                "pass of the same steps directly after the timed region",
+                    "time_share": {n: round(sum(v) / tot, 4) for n, v in per_kernel.items()}}
     checksum = float(op.out_full.float().abs().mean().item())
+    del op
+    torch.cuda.empty_cache()
+
+    # end to end: this rank's rows of z and of the mask bias start in pinned host memory, its output rows end there
+    e2e = None
+    if not args.no_e2e:
+        host = sharding.HostShardedTriangleAttention(w, rank, world, dev)
+        for _ in range(2):
+            host.step()
+        barrier()
+        e_ms = []
+        for _ in range(max(3, min(args.steps, 10))):
+            barrier()
+            e0, e1 = _events(torch)
+            e0.record()
+            host.step()
+            e1.record()
+            e1.synchronize()
+            e_ms.append(e0.elapsed_time(e1))
+        api.synchronize()
+        api.raise_if_error()
+        e_ms = max_over_ranks(e_ms)
+        em = sum(e_ms) / len(e_ms)
+        # host<->device copies alone, per rank, so that a host-side limit shows when N grows
+        c_up, c_dn = [], []
+        for _ in range(3):
+            barrier()
+            e0, e1 = _events(torch)
+            e0.record()
+            host.x.copy_(host.hx, non_blocking=True)
+            e1.record()
+            e1.synchronize()
+            c_up.append(e0.elapsed_time(e1))
+            barrier()
+            e0, e1 = _events(torch)
+            e0.record()
+            host.hout.copy_(host.x, non_blocking=True)
+            e1.record()
+            e1.synchronize()
+            c_dn.append(e0.elapsed_time(e1))
+        up, dn = max_over_ranks([min(c_up)])[0], max_over_ranks([min(c_dn)])[0]
+        e2e = {"value": w.flops() / (em * 1e-3) / 1e12, "unit": UNIT,
+               "h2d_bytes_per_step": host.h2d_bytes() * world, "d2h_bytes_per_step": host.d2h_bytes() * world,
+               "ms_per_step": em, "result_mean_abs": float(host.hout.float().abs().mean()),
+               "copies_alone_ms": {"h2d_rows": up, "d2h_rows": dn,
+                                   "h2d_gbs_per_gpu": host.hx.numel() * 2 / (up * 1e-3) / 1e9,
+                                   "d2h_gbs_per_gpu": host.hout.numel() * 2 / (dn * 1e-3) / 1e9},
+               "note": "bytes are the whole job's (all ranks); every rank moves its own rows; the output rows stay "
+                       "sharded in the node's host memory (nothing is gathered on the way out)"}
+        del host
+        torch.cuda.empty_cache()
     if world > 1:
         api.comm_fini()
+
+    cpu = glob = None
+    if rank == 0 and world == 1:
+        if not args.no_cpu_baseline:
+            cpu = cpu_baseline(args.workload)
+        if not args.no_global:
+            glob = global_attention_extra(torch, api, W, runner, dev, peaks)
     if rank == 0:
-        peaks = measured_peaks()
+        cfg = config_for(args.workload, world, "strong")
         print(json.dumps({
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": w.dtype, "data": "synthetic (seeded numpy, AlphaFold2 model shapes)",
-            "config": {"workload": args.workload, "B": w.B, "S": w.S, "H": w.H, "D": w.D, "C": w.C, "pair_bias": True,
-                       "gflop_per_call": w.flops() / 1e9, "slabs": args.slabs, "sm_margin": op.sm_margin, "output_gathered": not args.leave_sharded,
-                       "l2": "flushed between timed steps (256 MiB memset)",
-                       "parallelism": f"rows of one problem over {world} GPU(s); NCCL all-gather of the projected "
-                                      f"pair bias and of the output rows, output gather overlapped slab by slab"},
+            "config": cfg,
+            "details": {"slabs": slabs, "sm_margin": args.sm_margin if world > 1 else 0,
+                        "output_gathered": (not args.leave_sharded) and world > 1, "rows_per_gpu": rows_per_rank,
+                        "call_mode": "value: enqueue-only calls (kutacc_b200_set_async), device time by CUDA events; "
+                                     "e2e: host rows in, host rows out"},
             "frac_of_bf16_peak": value / world / peaks["bf16_tflops"],
-            "roofline": None, "cpu_baseline": None, "e2e": None, "gpu_launches": int(launches),
+            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches),
+            "compute_only": compute_only, "phases_ms": phases_ms, "global_attention": glob,
             "result_mean_abs": checksum, "clocks": clocks.summary(),
         }))
     return 0
@@ -307,25 +495,27 @@ def run_strong_scaling(args, torch, dist, api, W, dev, world, rank, local_rank):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-global", action="store_true", help="skip the extra global-attention measurement (N = 1)")
     ap.add_argument("--rows", type=int, default=0,
-                    help="profiling aid: run only this many of the workload's batch rows (0 = all); the JSON "
-                         "line then describes that smaller case and is not a benchmark result")
-    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
-                    help="weak (default): every rank runs the whole workload on its own rows, no collective; "
-                         "strong: one triangle workload split over the ranks with the two all-gathers")
-    ap.add_argument("--sm-margin", type=int, default=8, help="strong scaling: SMs the kernels leave to NCCL")
+                    help="profiling aid (weak mode): run only this many of the workload's batch rows (0 = all); the "
+                         "JSON line then describes that smaller case and is not a benchmark result")
+    ap.add_argument("--scaling", default="auto", choices=["auto", "weak", "strong"],
+                    help="strong: one triangle workload split over the ranks with the two all-gathers (default for the "
+                         "triangle workloads); weak: every rank runs the whole workload on its own rows, no "
+                         "collective (default for the others)")
+    ap.add_argument("--sm-margin", type=int, default=0, help="strong scaling: SMs the kernels leave to NCCL")
     ap.add_argument("--leave-sharded", action="store_true",
-                    help="strong scaling: skip the all-gather of the output rows (compute-only scaling, the state the "
-                         "reference operator itself leaves)")
+                    help="strong scaling: skip the all-gather of the output rows in the headline figure too")
     ap.add_argument("--slabs", type=int, default=2, help="strong scaling: slabs the output gather is pipelined in")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    args.steps = max(args.steps, 1)
 
     if args.impl == "reference":
         return run_reference_arm(args)
@@ -348,8 +538,9 @@ def main():
         build.build()
     api.lib()
 
-    if args.scaling == "strong":
-        rc = run_strong_scaling(args, torch, dist, api, W, dev, world, rank, local_rank)
+    scaling = resolve_scaling(args, args.workload)
+    if scaling == "strong" and args.rows <= 0:
+        rc = run_strong_scaling(args, torch, dist, api, W, runner, dev, world, rank, local_rank)
         if world > 1:
             dist.destroy_process_group()
         return rc
@@ -377,7 +568,7 @@ def main():
         out_ms = []
         for _ in range(args.steps):
             flush.zero_()                                             # evict L2 between timed steps
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0, e1 = _events(torch)
             e0.record()
             case.run()
             e1.record()
@@ -391,8 +582,8 @@ def main():
     launches = api.launch_count() - launches0
     api.synchronize()
     api.raise_if_error()
-    # Per-kernel CUDA events cost about 7 % of a step of this size, so the timed region above runs without
-    # them; the same K steps are repeated right away with the events on for the kernel breakdown.
+    # Per-kernel CUDA events cost a few per cent of a step, so the timed region above runs without them; the
+    # same K steps are repeated right away with the events on for the kernel breakdown.
     api.set_profile(True)
     api.profile_read()
     timed_steps()
@@ -408,7 +599,8 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         total_ms = float(t.item())
     ms_per_step = total_ms / args.steps
-    flops_job = w.flops() * world
+    # the pair bias is an input of this call (projected beforehand), so its projection is not counted
+    flops_job = w.flops(pair_bias=False) * world
     value = flops_job / (ms_per_step * 1e-3) / 1e12
 
     # dominant kernel, timed live inside the same steps
@@ -428,12 +620,14 @@ def main():
         k_ms = sum(per_kernel[kname]) / args.steps                    # all launches of that kernel in one step
         achieved = work / (k_ms * 1e-3) / (1e12 if bound == "tensor" else 1e9)
         peak = peaks["bf16_tflops"] if bound == "tensor" else peaks["hbm_gbs"]
+        traffic = NCU_TRAFFIC.get(args.workload)
+        _, _, Bfull = W.spec(args.workload)[:3]
         roofline = {"kernel": kname, "bound": bound, "achieved": achieved, "peak": peak, "unit": runit,
-                    "frac": achieved / peak, "traffic": NCU_TRAFFIC.get(args.workload) if args.rows <= 0 else None,
+                    "frac": achieved / peak, "traffic": traffic * w.B / Bfull if traffic else None,
                     "peak_source": f"{peaks['source']} ({'burst bf16' if bound == 'tensor' else 'copy'})",
                     "kernel_ms_per_step": k_ms, "launches_per_step": launches_per_step,
                     "measured": "CUDA events around every kernel on its stream, in a second pass of the same K steps "
-                                "directly after the timed region (the events themselves cost about 7 % of a step)",
+                                "directly after the timed region (the events themselves cost a few per cent of a step)",
                     "time_share": {n: round(s, 4) for n, s in kshare.items()}}
 
     # end to end: every tensor in pinned host memory, copies inside the library call
@@ -445,7 +639,7 @@ def main():
         barrier()
         e_ms = []
         for _ in range(max(3, min(args.steps, 10))):
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0, e1 = _events(torch)
             e0.record()
             host.run()
             e1.record()
@@ -462,20 +656,21 @@ def main():
         e2e["result_mean_abs"] = checksum
 
     cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+    if rank == 0 and world == 1 and not args.no_cpu_baseline and args.rows <= 0:
         cpu = cpu_baseline(args.workload)
 
     if rank == 0:
+        cfg = config_for(args.workload, world, "weak")
+        if args.rows > 0:
+            cfg["rows_run"] = w.B
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": w.dtype, "data": "synthetic (seeded numpy, AlphaFold2 model shapes)",
-            "config": {"workload": args.workload, "B_per_gpu": w.B, "S": w.S, "H": w.H, "D": w.D, "C": w.C,
-                       "pair_bias": w.has_nb, "gflop_per_call": w.flops() / 1e9,
-                       "l2": "flushed between timed steps (256 MiB memset)",
-                       "call_mode": "value: enqueue-only calls (kutacc_b200_set_async), device time by CUDA events; "
-                                    "e2e: the synchronous default with host buffers",
-                       "parallelism": f"rows sharded over {world} GPU(s), no collective"},
+            "config": cfg,
+            "details": {"call_mode": "value: enqueue-only calls (kutacc_b200_set_async), device time by CUDA events; "
+                                     "e2e: the synchronous default with host buffers",
+                        "flops": "the pair bias is an input of the timed call: its projection is neither run nor counted"},
             "frac_of_bf16_peak": value / world / peaks["bf16_tflops"],
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches),
             "clocks": clocks.summary(),

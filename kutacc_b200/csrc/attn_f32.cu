@@ -262,7 +262,7 @@ bool launch_attn_f32(cudaStream_t stream, const void *q, const void *k, const vo
     const int n_qt = (S + AQ - 1) / AQ;
     const int64_t items = (int64_t)B * H * n_qt;
     if (items > 0x7fffffff) return false;
-    KernelTimer timer__("attn_f32");
+    KernelTimer timer__("attn_f32", stream);
     attn_f32_kernel<<<(unsigned)items, A_THREADS, 0, stream>>>(
         (const float *)q, (const float *)k, (const float *)v, (const float *)gate, (const float *)bias, bias_stride0,
         (const float *)nb, nb_stride_h, nb_stride_q, (float *)avg, S, H, n_qt, scale);

@@ -473,7 +473,7 @@ bool launch_one(cudaStream_t stream, const CUtensorMap &tq, const CUtensorMap &t
         configured = true;
     }
     const unsigned grid = (unsigned)std::min<int64_t>(p.n_items, 2 * std::max(1, sm_count_attn() - runtime().sm_margin));
-    KernelTimer timer__("attn_core");
+    KernelTimer timer__("attn_core", stream);
     attn_tc_kernel<HAS_NB><<<grid, THREADS, SMEM_BYTES, stream>>>(tq, tk, tvt, tnb, p);
     count_launch();
     return true;

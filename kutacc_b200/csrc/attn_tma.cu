@@ -329,7 +329,7 @@ bool launch_one(cudaStream_t stream, const CUtensorMap &tq, const CUtensorMap &t
         configured = true;
     }
     dim3 grid((unsigned)((p.S + C::BM - 1) / C::BM), (unsigned)p.H, (unsigned)B);
-    KernelTimer timer__("attn_core");
+    KernelTimer timer__("attn_core", stream);
     attn_core_kernel<D, HAS_NB><<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(tq, tk, tv, tnb, p);
     count_launch();
     return true;

@@ -5,11 +5,13 @@
 // not need the library at all.
 #include <cuda_runtime.h>
 #include <dlfcn.h>
+#include <fcntl.h>
 #include <nccl.h>
 #include <sys/stat.h>
 #include <unistd.h>
 
 #include <algorithm>
+#include <cerrno>
 #include <chrono>
 #include <cstdio>
 #include <cstdlib>
@@ -32,7 +34,10 @@ namespace {
 struct NcclApi {
     void *handle = nullptr;
     ncclResult_t (*GetUniqueId)(ncclUniqueId *) = nullptr;
-    ncclResult_t (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int) = nullptr;
+    ncclResult_t (*CommInitRankConfig)(ncclComm_t *, int, ncclUniqueId, int, ncclConfig_t *) = nullptr;
+    ncclResult_t (*CommGetAsyncError)(ncclComm_t, ncclResult_t *) = nullptr;
+    ncclResult_t (*CommAbort)(ncclComm_t) = nullptr;
+    ncclResult_t (*CommFinalize)(ncclComm_t) = nullptr;
     ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
     ncclResult_t (*AllGather)(const void *, void *, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
     ncclResult_t (*Send)(const void *, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
@@ -48,17 +53,22 @@ std::string g_id_file;
 bool load_nccl()
 {
     if (g_nccl.handle) return true;
-    const char *names[] = {"libnccl.so.2", "libnccl.so"};
+    // KUTACC_NCCL_LIB names another library with the NCCL interface (the tests use it to put a stand-in there)
+    const char *override_name = std::getenv("KUTACC_NCCL_LIB");
+    const char *names[] = {override_name && *override_name ? override_name : "libnccl.so.2", "libnccl.so"};
     for (const char *n : names) {
         g_nccl.handle = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
-        if (g_nccl.handle) break;
+        if (g_nccl.handle || (override_name && *override_name)) break;
     }
     KUTACC_CHECK(g_nccl.handle != nullptr, "cannot load libnccl.so.2: ", dlerror());
     if (!g_nccl.handle) return false;
 #define KUTACC_SYM(field, name) \
     g_nccl.field = reinterpret_cast<decltype(g_nccl.field)>(dlsym(g_nccl.handle, name))
     KUTACC_SYM(GetUniqueId, "ncclGetUniqueId");
-    KUTACC_SYM(CommInitRank, "ncclCommInitRank");
+    KUTACC_SYM(CommInitRankConfig, "ncclCommInitRankConfig");
+    KUTACC_SYM(CommGetAsyncError, "ncclCommGetAsyncError");
+    KUTACC_SYM(CommAbort, "ncclCommAbort");
+    KUTACC_SYM(CommFinalize, "ncclCommFinalize");
     KUTACC_SYM(CommDestroy, "ncclCommDestroy");
     KUTACC_SYM(AllGather, "ncclAllGather");
     KUTACC_SYM(Send, "ncclSend");
@@ -67,18 +77,51 @@ bool load_nccl()
     KUTACC_SYM(GroupEnd, "ncclGroupEnd");
     KUTACC_SYM(GetErrorString, "ncclGetErrorString");
 #undef KUTACC_SYM
-    const bool ok = g_nccl.GetUniqueId && g_nccl.CommInitRank && g_nccl.CommDestroy && g_nccl.AllGather &&
+    const bool ok = g_nccl.GetUniqueId && g_nccl.CommInitRankConfig && g_nccl.CommGetAsyncError && g_nccl.CommAbort &&
+                    g_nccl.CommDestroy && g_nccl.AllGather &&
                     g_nccl.Send && g_nccl.Recv && g_nccl.GroupStart && g_nccl.GroupEnd && g_nccl.GetErrorString;
     KUTACC_CHECK(ok, "libnccl lacks a required symbol");
     return ok;
 }
 
+double env_seconds(const char *name, double dflt)
+{
+    const char *v = std::getenv(name);
+    return v && *v ? std::atof(v) : dflt;
+}
+
+// The communicator is non-blocking (ncclCommInitRankConfig with blocking = 0), so that a rank that never
+// arrives cannot park this process inside NCCL: a call may answer ncclInProgress, and the host then polls
+// ncclCommGetAsyncError under a time limit (KUTACC_COMM_TIMEOUT_S, 120 s by default). When the limit runs out the
+// communicator is aborted and the failure goes through the usual error flag.
+ncclResult_t settle(ncclResult_t r)
+{
+    if (r != ncclInProgress || g_comm == nullptr) return r;
+    const double limit = env_seconds("KUTACC_COMM_TIMEOUT_S", 120.0);
+    const auto t0 = std::chrono::steady_clock::now();
+    for (;;) {
+        ncclResult_t state = ncclSuccess;
+        const ncclResult_t q = g_nccl.CommGetAsyncError(g_comm, &state);
+        if (q != ncclSuccess) return q;
+        if (state != ncclInProgress) return state;
+        if (std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count() > limit) {
+            g_nccl.CommAbort(g_comm);
+            g_comm = nullptr;
+            return ncclSystemError;
+        }
+        std::this_thread::sleep_for(std::chrono::microseconds(50));
+    }
+}
+
 #define KUTACC_NCCL(call)                                                                                   \
     do {                                                                                                    \
-        ncclResult_t r__ = (call);                                                                          \
+        ncclResult_t r__ = settle(call);                                                                    \
         KUTACC_CHECK(r__ == ncclSuccess, "NCCL error: ", g_nccl.GetErrorString(r__), " (", #call, ")");    \
     } while (0)
 
+// Name of the file through which rank 0 hands the NCCL id to the other ranks when the caller gives none.
+// The default name carries the user id and what identifies the job (MASTER_ADDR, MASTER_PORT and the launcher's
+// run id), so that two jobs or two users on one machine do not meet in the same file.
 std::string rendezvous_path()
 {
     const char *name = std::getenv("KUTACC_RENDEZVOUS");
@@ -87,8 +130,12 @@ std::string rendezvous_path()
     if (name && *name) {
         base = name;
     } else {
-        const char *port = std::getenv("MASTER_PORT");
-        base = std::string("kutacc_nccl_") + (port ? port : "default");
+        const char *addr = std::getenv("MASTER_ADDR"), *port = std::getenv("MASTER_PORT"),
+                   *run = std::getenv("TORCHELASTIC_RUN_ID");
+        base = "kutacc_nccl_u" + std::to_string((long long)getuid()) + "_" + (addr ? addr : "local") + "_" +
+               (port ? port : "default") + "_" + (run ? run : "norun");
+        for (char &c : base)
+            if (c == '/' || c == ' ') c = '_';
     }
     if (base.find('/') != std::string::npos) return base;
     return "/dev/shm/" + base + ".ncclid";
@@ -100,7 +147,11 @@ struct IdRecord {
     int64_t world;
 };
 
-// rank 0 publishes the id through a file (write + rename), the others poll for a fresh record
+// Rank 0 publishes the id through a file that it creates itself (O_EXCL, no symlink followed, mode 0600) and
+// renames into place; the others poll for a record that is owned by this user, has the right world size and was
+// written no earlier than KUTACC_RENDEZVOUS_SLACK_S (60 s) before this rank began to wait: an id left by a job
+// that crashed, or by the previous job of a back-to-back pair, is refused. The poll gives up after
+// KUTACC_RENDEZVOUS_TIMEOUT_S (120 s).
 bool exchange_id(int64_t nranks, int64_t me, ncclUniqueId &id)
 {
     using clock = std::chrono::system_clock;
@@ -110,31 +161,36 @@ bool exchange_id(int64_t nranks, int64_t me, ncclUniqueId &id)
         KUTACC_NCCL(g_nccl.GetUniqueId(&id));
         if (kutacc_check_err_set) return false;
         IdRecord rec;
+        std::memset(&rec, 0, sizeof(rec));
         rec.id = id;
         rec.stamp = now;
         rec.world = nranks;
-        const std::string tmp = g_id_file + ".tmp";
-        std::remove(g_id_file.c_str());
-        FILE *f = std::fopen(tmp.c_str(), "wb");
-        KUTACC_CHECK(f != nullptr, "cannot write rendezvous file ", tmp);
-        if (!f) return false;
-        const size_t w = std::fwrite(&rec, sizeof(rec), 1, f);
-        std::fclose(f);
-        KUTACC_CHECK(w == 1 && std::rename(tmp.c_str(), g_id_file.c_str()) == 0, "cannot publish rendezvous file ",
-                     g_id_file);
+        const std::string tmp = g_id_file + ".tmp" + std::to_string((long long)getpid());
+        ::unlink(g_id_file.c_str());
+        ::unlink(tmp.c_str());
+        const int fd = ::open(tmp.c_str(), O_WRONLY | O_CREAT | O_EXCL | O_NOFOLLOW | O_CLOEXEC, 0600);
+        KUTACC_CHECK(fd >= 0, "cannot create rendezvous file ", tmp, ": ", std::strerror(errno));
+        if (fd < 0) return false;
+        const ssize_t w = ::write(fd, &rec, sizeof(rec));
+        ::close(fd);
+        KUTACC_CHECK(w == (ssize_t)sizeof(rec) && std::rename(tmp.c_str(), g_id_file.c_str()) == 0,
+                     "cannot publish rendezvous file ", g_id_file);
+        if (kutacc_check_err_set) ::unlink(tmp.c_str());
         return !kutacc_check_err_set;
     }
-    const char *to = std::getenv("KUTACC_RENDEZVOUS_TIMEOUT_S");
-    const double timeout_s = to ? std::atof(to) : 120.0;
+    const double timeout_s = env_seconds("KUTACC_RENDEZVOUS_TIMEOUT_S", 120.0);
+    const int64_t slack = (int64_t)env_seconds("KUTACC_RENDEZVOUS_SLACK_S", 60.0);
     const auto t0 = std::chrono::steady_clock::now();
     for (;;) {
-        FILE *f = std::fopen(g_id_file.c_str(), "rb");
-        if (f) {
+        const int fd = ::open(g_id_file.c_str(), O_RDONLY | O_NOFOLLOW | O_CLOEXEC);
+        if (fd >= 0) {
             IdRecord rec;
-            const size_t r = std::fread(&rec, sizeof(rec), 1, f);
-            std::fclose(f);
-            // a record older than this process's start (minus slack) belongs to an earlier job
-            if (r == 1 && rec.world == nranks && rec.stamp >= now - 300) {
+            struct stat st;
+            const bool mine = ::fstat(fd, &st) == 0 && S_ISREG(st.st_mode) && st.st_uid == getuid() &&
+                              (st.st_mode & (S_IWGRP | S_IWOTH)) == 0;
+            const ssize_t r = mine ? ::read(fd, &rec, sizeof(rec)) : -1;
+            ::close(fd);
+            if (r == (ssize_t)sizeof(rec) && rec.world == nranks && rec.stamp >= now - slack) {
                 id = rec.id;
                 return true;
             }
@@ -195,7 +251,21 @@ static void init_common(int64_t nranks, int64_t me, int64_t bufsz, const ncclUni
     } else if (!exchange_id(nranks, me, id)) {
         return;
     }
-    KUTACC_NCCL(g_nccl.CommInitRank(&g_comm, (int)nranks, id, (int)me));
+    ncclConfig_t config = NCCL_CONFIG_INITIALIZER;
+    config.blocking = 0;
+    const ncclResult_t r = g_nccl.CommInitRankConfig(&g_comm, (int)nranks, id, (int)me, &config);
+    if (r != ncclSuccess && r != ncclInProgress) {
+        KUTACC_CHECK(false, "NCCL error: ", g_nccl.GetErrorString(r), " (ncclCommInitRankConfig)");
+        g_comm = nullptr;
+        return;
+    }
+    const ncclResult_t done = settle(ncclInProgress);
+    KUTACC_CHECK(done == ncclSuccess, "kutacc_comm_init: the communicator of ", nranks, " ranks was not built (",
+                 g_comm == nullptr ? "set-up ran out of time and was aborted" : g_nccl.GetErrorString(done), ")");
+    if (done != ncclSuccess && g_comm != nullptr) {
+        g_nccl.CommAbort(g_comm);
+        g_comm = nullptr;
+    }
 }
 
 }  // namespace kutacc
@@ -232,7 +302,12 @@ void kutacc_comm_fini(void)
     using namespace kutacc;
     if (g_comm) {
         cudaStreamSynchronize((cudaStream_t)runtime().stream);
-        KUTACC_NCCL(g_nccl.CommDestroy(g_comm));
+        // a non-blocking communicator is finalized (polled to completion) before it is destroyed
+        if (g_nccl.CommFinalize) KUTACC_NCCL(g_nccl.CommFinalize(g_comm));
+        if (g_comm) {                                       // still there: the poll did not have to abort it
+            const ncclResult_t r = g_nccl.CommDestroy(g_comm);
+            KUTACC_CHECK(r == ncclSuccess || r == ncclInProgress, "NCCL error: ", g_nccl.GetErrorString(r), " (ncclCommDestroy)");
+        }
         g_comm = nullptr;
     }
     if (rank == 0 && !g_id_file.empty()) std::remove(g_id_file.c_str());
@@ -281,8 +356,10 @@ void kutacc_af2_all_gather(kutacc_tensor_h data_h, kutacc_tensor_h out_h)
     if (!rt.reserve_stage(staged_bytes_needed(data.data_ptr(), data_bytes) + staged_bytes_needed(out.data_ptr(), out_bytes)))
         return;
     DeviceArg d_in = data_bytes ? resolve_in(data.data_ptr(), data_bytes) : DeviceArg{};
-    // a staged (host) output is rebuilt whole on the device and copied back
-    DeviceArg d_out = resolve_out(out.data_ptr(), out_bytes);
+    // a staged (host) output is rebuilt whole on the device and copied back; one whose strides leave gaps is
+    // brought in first, so that the bytes between its elements come back unchanged
+    const bool out_dense = out.strides()[1] == len && out.strides()[0] == n * len;
+    DeviceArg d_out = out_dense ? resolve_out(out.data_ptr(), out_bytes) : resolve_in(out.data_ptr(), out_bytes);
     if (kutacc_check_err_set) return;
 
     const bool dense_dim0 = !dim1 && ds_o == len && ds_a == other * len && os_o == len && os_a == other * len;

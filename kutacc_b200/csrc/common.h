@@ -90,11 +90,13 @@ bool is_device_pointer(const void *p);
 void count_launch(int n = 1);
 
 // Optional per-kernel timing (kutacc_b200_set_profile): a launcher wraps each launch in a
-// KernelTimer, which brackets it with CUDA events on the runtime stream.
+// KernelTimer, which brackets it with CUDA events on the stream of the launch.
 struct KernelTimer {
-    explicit KernelTimer(const char *name);
+    // `cuda_stream` is the stream the kernel is launched on
+    KernelTimer(const char *name, void *cuda_stream);
     ~KernelTimer();
     int slot;
+    void *stream;
 };
 
 // A tensor argument resolved to device memory: either the caller's own device pointer or a staged
@@ -109,6 +111,10 @@ size_t staged_bytes_needed(const void *p, size_t bytes);               // 0 when
 DeviceArg resolve_in(const void *p, size_t bytes);                     // copies host -> device when staged
 DeviceArg resolve_out(void *p, size_t bytes);                          // no copy in
 void finish_out(const DeviceArg &a);                                    // device -> host when staged
+// Device -> host copy of `rows` rows of `width` bytes that are `pitch` bytes apart in both buffers. Only the
+// `width` bytes of a row are written, so a host tensor whose row stride leaves gaps keeps what lies between
+// its rows (the reference writes through the row stride and touches nothing else).
+void copy_rows_d2h(void *host, const void *dev, size_t rows, size_t width, size_t pitch, void *cuda_stream);
 void end_of_call();                                                    // stream sync unless async
 void sync_and_check();                                                 // stream sync + device-side timeout report
 

@@ -77,12 +77,13 @@ static void gating_attention_impl(Tensor &input, int64_t batch, int64_t seq_len,
     const size_t v_bytes = std::max(x_bytes, (size_t)B * C * s_pad8 * es);   // v may be stored key-major with padded rows
     if (!rt.reserve_workspace(4 * (x_bytes + 256) + v_bytes + 256 + nb_pad_bytes + 256)) return;
 
-    // When both the activations and the result live in host memory, the batch rows (independent problems)
-    // are processed in chunks so that the upload of chunk i+1, the kernels of chunk i and the download of
-    // chunk i-1 overlap on three streams. Otherwise the call is a single chunk on the runtime stream.
+    // When the result lives in host memory, the batch rows (independent problems) are processed in chunks so
+    // that the upload of chunk i+1 (when the activations are in host memory too), the kernels of chunk i and
+    // the download of chunk i-1 overlap on three streams. Otherwise the call is a single chunk on the runtime
+    // stream.
     const bool x_host = staged_bytes_needed(input.data_ptr(), x_bytes) != 0;
     const bool out_host = staged_bytes_needed(out.data_ptr(), out_bytes) != 0;
-    const bool pipelined = x_host && out_host && B >= 8 && x_bytes >= ((size_t)4 << 20);
+    const bool pipelined = out_host && B >= 8 && x_bytes >= ((size_t)4 << 20);
 
     if (pipelined) {
         // the copy streams may start as soon as the previous work on the runtime stream is done: mark that
@@ -193,7 +194,8 @@ static void gating_attention_impl(Tensor &input, int64_t batch, int64_t seq_len,
     bool ok = true;
     if (!pipelined) {
         ok = run_rows(0, B);
-        finish_out(d_out);
+        if (d_out.staged)
+            copy_rows_d2h((char *)d_out.host, (const char *)d_out.dev, (size_t)M, (size_t)C * es, (size_t)out_rs * es, stream);
     } else {
         // about 8 MiB of activations per chunk on average, between 2 and 12 chunks of at least 4 rows
         int nchunks = (int)std::max<int64_t>(2, std::min<int64_t>(12, (int64_t)((x_bytes + ((size_t)4 << 20)) >> 23)));
@@ -217,17 +219,20 @@ static void gating_attention_impl(Tensor &input, int64_t batch, int64_t seq_len,
         for (int i = 0; i < nchunks && ok; ++i) {
             const int64_t b0 = chunk_begin[i], nbr = chunk_begin[i + 1] - b0;
             if (nbr <= 0) continue;
-            KUTACC_CUDA(cudaMemcpyAsync((char *)d_x.dev + b0 * row_bytes, (const char *)input.data_ptr() + b0 * row_bytes,
-                                        (size_t)nbr * row_bytes, cudaMemcpyHostToDevice, s_in));
-            KUTACC_CUDA(cudaEventRecord((cudaEvent_t)cp.uploaded[i], s_in));
-            KUTACC_CUDA(cudaStreamWaitEvent(stream, (cudaEvent_t)cp.uploaded[i], 0));
+            if (x_host) {
+                KUTACC_CUDA(cudaMemcpyAsync((char *)d_x.dev + b0 * row_bytes, (const char *)input.data_ptr() + b0 * row_bytes,
+                                            (size_t)nbr * row_bytes, cudaMemcpyHostToDevice, s_in));
+                KUTACC_CUDA(cudaEventRecord((cudaEvent_t)cp.uploaded[i], s_in));
+                KUTACC_CUDA(cudaStreamWaitEvent(stream, (cudaEvent_t)cp.uploaded[i], 0));
+            }
             ok = run_rows(b0, nbr);
             KUTACC_CUDA(cudaEventRecord((cudaEvent_t)cp.computed[i], stream));
             KUTACC_CUDA(cudaStreamWaitEvent(s_out, (cudaEvent_t)cp.computed[i], 0));
+            // only the C elements of each row travel back: a host `out` whose row stride leaves gaps keeps
+            // the bytes between its rows (the reference writes through strides()[1] and touches nothing else)
             const size_t o_off = (size_t)b0 * S * out_rs * es;
-            const size_t o_len = std::min(out_bytes - o_off, (size_t)nbr * S * out_rs * es);
-            KUTACC_CUDA(cudaMemcpyAsync((char *)out.data_ptr() + o_off, (const char *)d_out.dev + o_off, o_len,
-                                        cudaMemcpyDeviceToHost, s_out));
+            copy_rows_d2h((char *)out.data_ptr() + o_off, (const char *)d_out.dev + o_off, (size_t)nbr * S, (size_t)C * es,
+                          (size_t)out_rs * es, s_out);
         }
         KUTACC_CUDA(cudaStreamSynchronize(s_out));
     }

@@ -209,7 +209,7 @@ bool launch_gemm(cudaStream_t stream, const void *A, int64_t lda, const WeightSe
         configured = true;
     }
     dim3 grid((unsigned)((M + BM - 1) / BM), (unsigned)(N / BN));
-    KernelTimer timer__(Epi::name());
+    KernelTimer timer__(Epi::name(), stream);
     gemm_bf16_tn_kernel<BN, Epi><<<grid, GEMM_THREADS, smem, stream>>>((const __nv_bfloat16 *)A, lda, ws, M, K, epi);
     count_launch();
     return true;

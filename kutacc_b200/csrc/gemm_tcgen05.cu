@@ -331,7 +331,7 @@ bool launch(cudaStream_t stream, const GemmMaps &maps, const GemmParams &p, cons
     const int s_tiles = (p.S + BM - 1) / BM;
     const int64_t tiles = (int64_t)p.B * s_tiles * (p.seg_n / BN) * p.nseg;
     const unsigned grid = (unsigned)std::min<int64_t>(tiles, 2 * std::max(1, sm_count() - runtime().sm_margin));
-    KernelTimer timer__(name);
+    KernelTimer timer__(name, stream);
     gemm_tcgen05_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(maps, p);
     count_launch();
     return true;

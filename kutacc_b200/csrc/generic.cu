@@ -498,7 +498,7 @@ bool launch_gemm_generic(cudaStream_t stream, ElemType t, const void *a, int64_t
             cudaGetLastError();
         }
         if (configured) {
-            KernelTimer timer__("gemm_tf32x3");
+            KernelTimer timer__("gemm_tf32x3", stream);
             dim3 gridt((unsigned)((M + TM - 1) / TM), (unsigned)((N + TN - 1) / TN));
             gemm_tf32x3_kernel<<<gridt, 256, T_SMEM_BYTES, stream>>>((const float *)a, lda, (const float *)w, ldw, bias,
                                                                       (float *)c, ldc, M, N, K);
@@ -508,7 +508,7 @@ bool launch_gemm_generic(cudaStream_t stream, ElemType t, const void *a, int64_t
     }
     dim3 grid((unsigned)((M + GT - 1) / GT), (unsigned)((N + GT - 1) / GT));
     if (grid.y > 65535) return false;
-    KernelTimer timer__("gemm_generic");
+    KernelTimer timer__("gemm_generic", stream);
     if (t == kElemF32)
         gemm_generic_kernel<float><<<grid, 256, 0, stream>>>((const float *)a, lda, (const float *)w, ldw, bias, beta,
                                                             (float *)c, ldc, M, N, K);
@@ -527,7 +527,7 @@ static bool launch_attn_generic_t(cudaStream_t stream, const void *q, const void
 {
     const int64_t rows = (int64_t)B * H * S;
     const unsigned grid = (unsigned)((rows + 3) / 4);
-    KernelTimer timer__("attn_generic");
+    KernelTimer timer__("attn_generic", stream);
 #define KUTACC_ATTN_GENERIC(DMAX)                                                                                  \
     attn_generic_kernel<T, DMAX><<<grid, 128, 0, stream>>>((const T *)q, (const T *)k, (const T *)v, (const T *)gate, \
                                                            (const T *)bias, bias_stride0, (const T *)nb, nb_stride_h, \
@@ -560,7 +560,7 @@ bool launch_pair_bias(cudaStream_t stream, ElemType t, const void *z, const void
                       int64_t nb_head_stride, int64_t pos_stride, int64_t R, int64_t Nk, int Cz, int H)
 {
     if (H > 16 || (size_t)H * Cz * 4 > 48 * 1024) return false;
-    KernelTimer timer__("pair_bias");
+    KernelTimer timer__("pair_bias", stream);
     const int64_t pos = R * Nk;
     const unsigned grid = (unsigned)std::min<int64_t>((pos + 7) / 8, 148 * 16);
     const size_t smem = (size_t)H * Cz * 4;

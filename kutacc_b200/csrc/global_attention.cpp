@@ -133,6 +133,7 @@ extern "C" void kutacc_af2_global_attention(kutacc_af2_attention_inputs_t *q_bas
     }
     if (kutacc_check_err_set) return;
     KUTACC_CHECK(ok, "global_attention: no device kernel for nheads=", H, " head_size=", D, " out row stride ", out_rs);
-    if (!pipelined) finish_out(d_out);
+    if (!pipelined && d_out.staged)   // only the C elements of each row: gaps of a strided host `out` stay untouched
+        copy_rows_d2h(d_out.host, d_out.dev, (size_t)M, (size_t)C * 2, (size_t)out_rs * 2, stream);
     end_of_call();
 }

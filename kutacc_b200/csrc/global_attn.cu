@@ -548,12 +548,12 @@ void run_global(cudaStream_t stream, const void *x, const void *mask, const void
         const int nb = std::min(pl.group, B - b0);
         dim3 g1((unsigned)pl.nsplit, (unsigned)nb);
         {
-            KernelTimer timer__("global_pool");
+            KernelTimer timer__("global_pool", stream);
         global_pool_kernel<<<g1, POOL_THREADS, 0, stream>>>((const __nv_bfloat16 *)x, (const __nv_bfloat16 *)mask, sc,
                                                             b0, S, pl.rows_per_split);
         }
         {
-            KernelTimer timer__("global_core");
+            KernelTimer timer__("global_core", stream);
         if (H == 8 && D == 8)
             global_core_mma_kernel<<<g1, CORE_THREADS, 0, stream>>>(
                 (const __nv_bfloat16 *)x, (const __nv_bfloat16 *)mask, (const __nv_bfloat16 *)wq,
@@ -566,7 +566,7 @@ void run_global(cudaStream_t stream, const void *x, const void *mask, const void
         const int out_tiles = (S + OUT_ROWS - 1) / OUT_ROWS;
         dim3 g3((unsigned)((out_tiles + 3) / 4), (unsigned)nb);
         {
-            KernelTimer timer__("global_out");
+            KernelTimer timer__("global_out", stream);
         global_out_kernel<H, D><<<g3, 256, 0, stream>>>((const __nv_bfloat16 *)x, (const __nv_bfloat16 *)wg, bg,
                                                         (const __nv_bfloat16 *)wo, bo, (__nv_bfloat16 *)out,
                                                         out_row_stride, sc, b0, S);

@@ -745,7 +745,7 @@ bool launch_fused(cudaStream_t stream, const void *x, const void *out, int64_t o
                                  (uint64_t)a.S * (uint64_t)out_row_stride, FC, CH_ROWS, 128))
         return false;
     {
-        KernelTimer timer__("global_fused");
+        KernelTimer timer__("global_fused", stream);
         const cudaError_t e = cudaLaunchKernelEx(&cfg, global_fused_kernel<K>, xmap, omap, a);
         KUTACC_CHECK(e == cudaSuccess, "global_fused_kernel launch failed: ", cudaGetErrorString(e));
         if (e != cudaSuccess) return false;

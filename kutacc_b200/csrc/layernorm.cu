@@ -154,7 +154,7 @@ bool launch_layernorm_rows(cudaStream_t stream, const void *x, const float *gamm
                            int64_t rows, int64_t size, int64_t x_stride, int64_t out_stride, float eps)
 {
     if (rows <= 0 || size <= 0) return false;
-    KernelTimer timer__("layernorm");
+    KernelTimer timer__("layernorm", stream);
     const int64_t blocks_needed = (rows + 7) / 8;
     const unsigned grid = (unsigned)std::min<int64_t>(blocks_needed, 148 * 16);
     const bool vec = (size % 8) == 0 && size <= 32 * 8 * LN_MAX_VEC && (x_stride % 8) == 0 && (out_stride % 8) == 0 &&

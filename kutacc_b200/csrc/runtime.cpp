@@ -22,19 +22,19 @@ bool g_profile = false;
 std::vector<ProfRecord> g_prof;
 }  // namespace
 
-KernelTimer::KernelTimer(const char *name) : slot(-1)
+KernelTimer::KernelTimer(const char *name, void *cuda_stream) : slot(-1), stream(cuda_stream)
 {
     if (!g_profile) return;
     ProfRecord r;
     r.name = name;
     if (cudaEventCreate(&r.start) != cudaSuccess || cudaEventCreate(&r.stop) != cudaSuccess) return;
-    cudaEventRecord(r.start, (cudaStream_t)runtime().stream);
+    cudaEventRecord(r.start, (cudaStream_t)stream);
     g_prof.push_back(r);
     slot = (int)g_prof.size() - 1;
 }
 KernelTimer::~KernelTimer()
 {
-    if (slot >= 0) cudaEventRecord(g_prof[(size_t)slot].stop, (cudaStream_t)runtime().stream);
+    if (slot >= 0) cudaEventRecord(g_prof[(size_t)slot].stop, (cudaStream_t)stream);
 }
 
 Runtime &runtime()
@@ -149,6 +149,16 @@ void finish_out(const DeviceArg &a)
 {
     if (a.staged && a.dev && a.host)
         KUTACC_CUDA(cudaMemcpyAsync(a.host, a.dev, a.bytes, cudaMemcpyDeviceToHost, (cudaStream_t)runtime().stream));
+}
+
+void copy_rows_d2h(void *host, const void *dev, size_t rows, size_t width, size_t pitch, void *cuda_stream)
+{
+    if (rows == 0 || width == 0) return;
+    if (width == pitch) {
+        KUTACC_CUDA(cudaMemcpyAsync(host, dev, rows * width, cudaMemcpyDeviceToHost, (cudaStream_t)cuda_stream));
+        return;
+    }
+    KUTACC_CUDA(cudaMemcpy2DAsync(host, pitch, dev, pitch, width, rows, cudaMemcpyDeviceToHost, (cudaStream_t)cuda_stream));
 }
 
 CopyPipeline &copy_pipeline(int nchunks)

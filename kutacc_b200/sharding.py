@@ -59,7 +59,7 @@ class ShardedTriangleAttention:
         import torch
         from . import api
         from .runner import _to_torch
-        assert w.kind == "gating" and w.has_nb and "z" in w.arrays and w.B == w.S, "needs a full triangle workload"
+        assert w.kind == "gating" and "wb" in w.arrays and w.B == w.S, "needs a full triangle workload"
         self.w, self.rank, self.world, self.device = w, rank, world, device
         self.sm_margin = sm_margin if world > 1 else 0      # SMs left to the collective that runs beside the kernels
         self.api = api
@@ -108,6 +108,16 @@ class ShardedTriangleAttention:
         self.compute = torch.cuda.current_stream(device)
         self.comm = torch.cuda.Stream(device=device)
         self.events = [torch.cuda.Event() for _ in self.parts]
+        # phase marks of the last step, all on the compute stream
+        self.marks = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
+
+    def phase_ms(self):
+        """Device time of the phases of the last ``step()`` (synchronise first): pair-bias projection, bias
+        all-gather, attention (all slabs, with the overlapped output gathers beside it), and the part of the
+        output gather that was still running when the last attention kernel had finished."""
+        m = self.marks
+        return {"bias_projection": m[0].elapsed_time(m[1]), "bias_all_gather": m[1].elapsed_time(m[2]),
+                "attention": m[2].elapsed_time(m[3]), "exposed_output_gather": m[3].elapsed_time(m[4])}
 
     def step(self, block_size: int = 128, gather_output: bool = True):
         api = self.api
@@ -115,11 +125,14 @@ class ShardedTriangleAttention:
         api.set_sm_margin(self.sm_margin)
         try:
             api.set_stream(self.compute.cuda_stream)
+            self.marks[0].record(self.compute)
             for p in self.parts:
                 api.pair_bias(p["t_z"], self.t_wb, p["t_nb_rows"])
+            self.marks[1].record(self.compute)
             if self.world > 1:
                 for p in self.parts:
                     api.all_gather(p["g_nb_src"], p["g_nb_dst"])
+            self.marks[2].record(self.compute)
             for p, ev in zip(self.parts, self.events):
                 api.set_stream(self.compute.cuda_stream)
                 api.gating_attention(p["t_x"], p["inputs"], p["t_bias"], self.t_nb, self.weights, p["t_out_rows"],
@@ -129,9 +142,86 @@ class ShardedTriangleAttention:
                     self.comm.wait_event(ev)
                     api.set_stream(self.comm.cuda_stream)
                     api.all_gather(p["g_out_src"], p["g_out_dst"])
+            self.marks[3].record(self.compute)
             self.compute.wait_stream(self.comm)
+            self.marks[4].record(self.compute)
         finally:
             api.set_stream(self.compute.cuda_stream)
             api.set_async(False)
             api.set_sm_margin(0)
         return self.out_full
+
+
+class HostShardedTriangleAttention:
+    """The same flow for a caller whose activations and result live in host memory: one rank's rows of z and of
+    the mask bias are in pinned host buffers, its rows of the output land in a pinned host buffer.
+
+    ``step()`` copies the rows to the device, projects their pair bias, all-gathers the bias (world > 1) and calls
+    the gated attention with a HOST ``out``: the library then runs the batch rows in chunks and overlaps the
+    download of chunk i with the kernels of chunk i + 1. Every rank ends with its own rows in host memory (the
+    ranks of one node share that memory, so nothing is gathered). Rank r owns the contiguous block r.
+    """
+
+    def __init__(self, w, rank: int, world: int, device):
+        import numpy as np
+        import torch
+        from . import api
+        from .runner import _to_torch
+        assert w.kind == "gating" and "wb" in w.arrays and w.B == w.S, "needs a full triangle workload"
+        self.w, self.rank, self.world, self.device, self.api = w, rank, world, device, api
+        N, S, C, H = w.B, w.S, w.C, w.H
+        r0, n = row_range(N, world, rank)
+        assert n > 0 and N % world == 0, "rows must split evenly over the ranks"
+        self.rows = (r0, n)
+        A = w.arrays
+        dt = api.DTYPE_BF16 if w.dtype == "bf16" else api.DTYPE_FP32
+        esz = 2 if w.dtype == "bf16" else 4
+        tdt = torch.bfloat16 if w.dtype == "bf16" else torch.float32
+        self.hx = _to_torch(A["x"][r0:r0 + n], w.dtype, "cpu", pin=True)
+        self.hbias = _to_torch(A["bias"][r0:r0 + n], w.dtype, "cpu", pin=True)
+        self.hout = torch.zeros((n, S, C), dtype=tdt).pin_memory()
+        self.x = torch.empty((n, S, C), dtype=tdt, device=device)
+        self.bias = torch.empty((n, S), dtype=tdt, device=device)
+        f = lambda a: _to_torch(a, w.dtype, device)
+        f32 = lambda a: _to_torch(a, "fp32", device)
+        self.wq, self.wk, self.wv, self.wg, self.wo = (f(A[k]) for k in ("wq", "wk", "wv", "wg", "wo"))
+        self.bg, self.bo = f32(A["bg"]), f32(A["bo"])
+        self.wb = f(np.ascontiguousarray(A["wb"].T))
+        self.nb_full = torch.zeros((H, S, S), dtype=tdt, device=device)
+        self.weights = api.make_weights(C, H, w.D, self.wq, self.wk, self.wv, self.wg, self.bg, self.wo, self.bo)
+        self.inputs = api.make_inputs(n, S)
+        self.t_wb = api.tensor(self.wb)
+        self.t_nb = api.tensor(self.nb_full)
+        self.t_x = api.tensor(self.x, sizes=[n * S, C], strides=[C, 1])
+        self.t_z = api.tensor(self.x)
+        self.t_bias = api.tensor(self.bias)
+        self.t_out = api.tensor(self.hout)
+        nb_rows = self.nb_full[:, r0:r0 + n, :]
+        self.t_nb_rows = api.Tensor(nb_rows.data_ptr(), [H, n, S], [S * S, S, 1], dt, keep=self.nb_full)
+        self.g_nb_src = api.Tensor(nb_rows.data_ptr(), [H, n, S * esz], [S * S * esz, S * esz, 1], api.DTYPE_BF16,
+                                   keep=self.nb_full)
+        self.g_nb_dst = api.Tensor(self.nb_full.data_ptr(), [H, N, S * esz], [S * S * esz, S * esz, 1], api.DTYPE_BF16,
+                                   keep=self.nb_full)
+        self.compute = torch.cuda.current_stream(device)
+
+    def h2d_bytes(self) -> int:
+        return int(self.hx.numel() * self.hx.element_size() + self.hbias.numel() * self.hbias.element_size())
+
+    def d2h_bytes(self) -> int:
+        return int(self.hout.numel() * self.hout.element_size())
+
+    def step(self, block_size: int = 128):
+        api = self.api
+        api.set_async(True)
+        try:
+            api.set_stream(self.compute.cuda_stream)
+            self.x.copy_(self.hx, non_blocking=True)
+            self.bias.copy_(self.hbias, non_blocking=True)
+            api.pair_bias(self.t_z, self.t_wb, self.t_nb_rows)
+            if self.world > 1:
+                api.all_gather(self.g_nb_src, self.g_nb_dst)
+            # returns when the last chunk of `out` has landed in host memory
+            api.gating_attention(self.t_x, self.inputs, self.t_bias, self.t_nb, self.weights, self.t_out, block_size)
+        finally:
+            api.set_async(False)
+        return self.hout

@@ -18,12 +18,16 @@ import numpy as np
 def bf16_bits(a: np.ndarray) -> np.ndarray:
     """fp32 -> bf16 bit pattern, round to nearest even (NaN kept quiet)."""
     a = np.ascontiguousarray(a, dtype=np.float32)
-    u = a.view(np.uint32).astype(np.uint64)
-    lsb = (u >> 16) & 1
-    r = ((u + 0x7FFF + lsb) >> 16).astype(np.uint16)
+    u = a.view(np.uint32)
+    r = u >> 16                       # in-place uint32 arithmetic: the only bit patterns whose rounding sum would
+    r &= 1                            # wrap are negative NaNs, and NaNs are patched below
+    r += 0x7FFF
+    r += u
+    r >>= 16
+    r = r.astype(np.uint16)
     nan = np.isnan(a)
     if nan.any():
-        r[nan] = ((a.view(np.uint32)[nan] >> 16) | 0x40).astype(np.uint16)
+        r[nan] = ((u[nan] >> 16) | 0x40).astype(np.uint16)
     return r
 
 
@@ -54,12 +58,14 @@ class Workload:
         return bf16_bits(self.arrays[key])
 
     # ---- algorithmic work (2 FLOPs per multiply-add; exp/softmax/sigmoid not counted) ----
-    def flops(self, rows: Optional[int] = None) -> float:
+    def flops(self, rows: Optional[int] = None, pair_bias: bool = True) -> float:
+        """``pair_bias=False`` leaves out the projection of the pair bias from z (callers that are handed the
+        projected bias as an input do not run it)."""
         B = self.B if rows is None else rows
         S, C, H, D = self.S, self.C, self.H, self.D
         if self.kind == "gating":
             f = 10.0 * B * S * C * C + 4.0 * B * S * S * C
-            if self.has_nb and self.c_z:
+            if pair_bias and self.c_z and (self.has_nb or "wb" in self.arrays):
                 f += 2.0 * S * S * self.c_z * H
             return f
         # global: pool, q, k, v, gate, logits, PV, out
@@ -94,9 +100,11 @@ def spec(name: str):
     return _SPECS[name]
 
 
-def make(name: str, rows: Optional[int] = None, seq: Optional[int] = None) -> Workload:
+def make(name: str, rows: Optional[int] = None, seq: Optional[int] = None, with_nb: bool = True) -> Workload:
     """Build a workload. ``rows`` keeps only the first ``rows`` batch rows (cheap sub-sample with the
-    same per-row distribution); ``seq`` overrides the sequence length (tests on reduced shapes)."""
+    same per-row distribution); ``seq`` overrides the sequence length (tests on reduced shapes);
+    ``with_nb=False`` leaves out the projected pair bias ``nb`` (callers that project it themselves from
+    ``z`` and ``wb``, as the sharded flow does, save the host-side product)."""
     kind, dtype, B, S, H, D, c_z, seed = _SPECS[name]
     if seq is not None:
         S = int(seq)
@@ -143,11 +151,12 @@ def make(name: str, rows: Optional[int] = None, seq: Optional[int] = None) -> Wo
         zc = z.shape[-1]
         wb = rnd(rng.standard_normal((zc, H), dtype=np.float32) / np.sqrt(zc))
         A["wb"] = wb
-        zr = rnd(z)
+        zr = A["x"] if (pair_input and Bgen == S) else rnd(z)
         A["z"] = zr
-        nb = (zr.reshape(S * S, zc).astype(np.float32) @ wb).reshape(S, S, H)
-        A["nb"] = rnd(np.ascontiguousarray(nb.transpose(2, 0, 1)))      # [H, S_q, S_k]
-        w.has_nb = True
+        if with_nb:
+            nb = (zr.reshape(S * S, zc).astype(np.float32) @ wb).reshape(S, S, H)
+            A["nb"] = rnd(np.ascontiguousarray(nb.transpose(2, 0, 1)))      # [H, S_q, S_k]
+            w.has_nb = True
 
     # masks
     if name == "msa_row_fp32" or name == "triangle_end_1024":
