@@ -70,7 +70,7 @@ class ClockSampler:
 
     def __init__(self, index: int, period_s: float = 0.02):
         self.index, self.period = index, period_s
-        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self.samples, self.mem_samples, self.reasons, self.max_mhz = [], [], set(), None
         self._stop = threading.Event()
         self._thread = None
         try:
@@ -93,6 +93,7 @@ class ClockSampler:
         while not self._stop.is_set():
             try:
                 self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                self.mem_samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_MEM))
                 r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
                 for k, bit in names.items():
                     if r & bit:
@@ -116,7 +117,28 @@ class ClockSampler:
         if not self.samples:
             return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": 0}
         return {"sm_mhz": statistics.median(self.samples), "sm_max_mhz": self.max_mhz,
+                "mem_mhz": statistics.median(self.mem_samples) if self.mem_samples else None,
                 "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def hbm_copy_gbs(torch, dev, n_bytes=1 << 30, reps=5):
+    """Read + write bandwidth of a plain device copy on this GPU right now (the quantity the measured HBM peak
+    was taken with): lets a reader tell a slow kernel from a slow box."""
+    a = torch.empty(n_bytes, dtype=torch.uint8, device=dev)
+    b = torch.empty_like(a)
+    b.copy_(a)
+    best = None
+    for _ in range(reps):
+        e0, e1 = _events(torch)
+        e0.record()
+        b.copy_(a)
+        e1.record()
+        e1.synchronize()
+        ms = e0.elapsed_time(e1)
+        best = ms if best is None else min(best, ms)
+    del a, b
+    torch.cuda.empty_cache()
+    return 2.0 * n_bytes / (best * 1e-3) / 1e9
 
 
 def config_for(name, world, scaling, slabs=None):
@@ -467,6 +489,7 @@ def run_strong_scaling(args, torch, dist, api, W, runner, dev, world, rank, loca
     if world > 1:
         api.comm_fini()
 
+    copy_now = hbm_copy_gbs(torch, dev) if rank == 0 else None
     cpu = glob = None
     if rank == 0 and world == 1:
         if not args.no_cpu_baseline:
@@ -487,7 +510,7 @@ def run_strong_scaling(args, torch, dist, api, W, runner, dev, world, rank, loca
             "frac_of_bf16_peak": value / world / peaks["bf16_tflops"],
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches),
             "compute_only": compute_only, "phases_ms": phases_ms, "global_attention": glob,
-            "result_mean_abs": checksum, "clocks": clocks.summary(),
+            "result_mean_abs": checksum, "clocks": clocks.summary(), "hbm_copy_gbs_now": copy_now,
         }))
     return 0
 
@@ -673,7 +696,7 @@ def main():
                         "flops": "the pair bias is an input of the timed call: its projection is neither run nor counted"},
             "frac_of_bf16_peak": value / world / peaks["bf16_tflops"],
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches),
-            "clocks": clocks.summary(),
+            "clocks": clocks.summary(), "hbm_copy_gbs_now": hbm_copy_gbs(torch, dev),
         }
         print(json.dumps(line))
     if world > 1:

@@ -22,6 +22,7 @@
 #define KUTACC_B200_H
 
 #include <stddef.h>
+#include <stdbool.h>
 #include <stdint.h>
 
 #ifdef __cplusplus
@@ -169,6 +170,62 @@ KUTACC_B200_API void kutacc_af2_linear_weight_prepack(const uint16_t *weight, ui
 KUTACC_B200_API void kutacc_af2_transition(kutacc_af2_trans_act_inputs_t *trans_inputs_ptr,
                                            kutacc_af2_trans_weights_t *trans_weights_ptr, kutacc_tensor_h out);
 
+/* Triangle multiplication (replaces include/kutacc.h:154-189, 426-456; src/attention/triangle_multiplication.cpp).
+ * The operator is exported as four steps, as in the reference; the caller runs LayerNorm and the permute between
+ * them. All tensors bf16, biases fp32. */
+typedef struct kutacc_af2_tm_proj_weights {     /* include/kutacc.h:154-162 */
+    int64_t c_o;                                /* channels of input_act */
+    int64_t c_i;                                /* channels of the projections */
+    kutacc_tensor_h proj_w;                     /* [c_i, c_o] */
+    kutacc_tensor_h proj_b;                     /* [c_i] fp32 */
+    kutacc_tensor_h gate_w;                     /* [c_i, c_o] */
+    kutacc_tensor_h gate_b;                     /* [c_i] fp32 */
+} kutacc_af2_tm_proj_weights_t;
+
+typedef struct kutacc_af2_tm_act_inputs {       /* include/kutacc.h:168-175 */
+    int64_t n_res;
+    int64_t n_res_gather;
+    kutacc_tensor_h proj_act;                   /* [c_i, n_res, n_res_gather], unit last stride (output) */
+    kutacc_tensor_h input_act;                  /* [n_res, n_res_gather, c_o] dense */
+    kutacc_tensor_h proj_act_gate;              /* [c_i, n_res, n_res_gather] (output: the gate before the sigmoid) */
+} kutacc_af2_tm_act_inputs_t;
+
+typedef struct kutacc_af2_tm_linear_weights {   /* include/kutacc.h:181-189 */
+    int64_t c_o;
+    int64_t c_i;
+    kutacc_tensor_h gating_w;                   /* [c_o, c_o] */
+    kutacc_tensor_h gating_b;                   /* [c_o] fp32 */
+    kutacc_tensor_h output_proj_w;              /* [c_o, c_i] */
+    kutacc_tensor_h output_proj_b;              /* [c_o] fp32 */
+} kutacc_af2_tm_linear_weights_t;
+
+/* replaces include/kutacc.h:426-429 (triangle_multiplication.cpp:25-70): proj_act = bf16(input_act . proj_w^T +
+ * proj_b), proj_act_gate = bf16(input_act . gate_w^T + gate_b), both stored channel-major, then in place
+ * proj_act = bf16((proj_act * mask) * sigmoid(proj_act_gate)); mask [n_res, n_res_gather]. input_prepack is
+ * accepted and ignored (the packed image of a matrix is the matrix). */
+KUTACC_B200_API void kutacc_af2_triangle_multiplication_calc_proj(kutacc_af2_tm_act_inputs_t *tm_acts_ptr,
+                                                                  kutacc_tensor_h mask,
+                                                                  kutacc_af2_tm_proj_weights_t *tm_weights_ptr,
+                                                                  bool input_prepack);
+
+/* replaces include/kutacc.h:436-439 (triangle_multiplication.cpp:75-104): per channel c of left_proj_act.sizes[0],
+ * center[c] = left[c] . right[c]^T (is_incoming false) or right[c]^T . left[c] (is_incoming true), all
+ * [c_i, n_res_gather, n_res_gather] with unit last stride. */
+KUTACC_B200_API void kutacc_af2_triangle_multiplication_equation(kutacc_tensor_h center_act, kutacc_tensor_h left_proj_act,
+                                                                 kutacc_tensor_h right_proj_act, int64_t n_res_gather,
+                                                                 bool is_incoming);
+
+/* replaces include/kutacc.h:446-448 (triangle_multiplication.cpp:109-133): gate = input_act . gating_w^T + gating_b
+ * and out = center_act . output_proj_w^T + output_proj_b, rows = n_res * n_res_gather; gate, out and center_act are
+ * [n_res, n_res_gather, channels] with row stride strides[1]. */
+KUTACC_B200_API void kutacc_af2_triangle_multiplication_gate_and_out_linear(
+    kutacc_tensor_h gate, kutacc_tensor_h out, kutacc_af2_tm_act_inputs_t *tm_acts_ptr, kutacc_tensor_h center_act,
+    kutacc_af2_tm_linear_weights_t *tm_weights_ptr, bool input_prepack);
+
+/* replaces include/kutacc.h:455-456 (triangle_multiplication.cpp:138-158): out = bf16(out * sigmoid(gate)) */
+KUTACC_B200_API void kutacc_af2_triangle_multiplication_last(kutacc_tensor_h out, kutacc_tensor_h gate, int64_t n_res,
+                                                             int64_t n_res_gather, int64_t c_o);
+
 /* replaces include/kutacc.h:334 (src/normalization/layernorm.cpp:17-20, layernorm_kernel.h:22-53): LayerNorm
  * of ONE row of `size` bf16 channels, out = bf16(fma(fma(x, rstd, -rstd * mean), gamma, beta)) with the
  * reference's shifted-data statistics. Host or device pointers. A launch per row is what this signature
@@ -202,7 +259,13 @@ KUTACC_B200_API void kutacc_b200_clear_error(void);
 
 /* Device selection (default: current CUDA device) and stream (default: the legacy default
  * stream). Operators are synchronous unless kutacc_b200_set_async(1) was called, in which case
- * calls with device-resident tensors only enqueue work on the stream. */
+ * calls with device-resident tensors only enqueue work on the stream.
+ * The library has ONE workspace and ONE staging pool, handed out from their start on every call; only the
+ * order of work on a stream protects them. In enqueue-only mode a caller that switches streams between calls
+ * must therefore order the streams itself (an event from the old stream that the new one waits for) unless the
+ * second call uses neither pool. Calls that use neither: kutacc_af2_all_gather on device tensors whose per-rank
+ * rows form one dense slab of the output (it gathers in place), and kutacc_b200_global_attention_noalloc. Every
+ * other operator uses the workspace. */
 KUTACC_B200_API void kutacc_b200_set_stream(void *cuda_stream);
 KUTACC_B200_API void kutacc_b200_set_async(int enabled);
 /* The persistent kernels (projections, attention core) normally fill every SM. A caller that runs a

@@ -17,7 +17,7 @@ from typing import Optional, Sequence
 import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libkutacc.so")
+LIB_PATH = os.environ.get("KUTACC_B200_LIB") or os.path.join(_HERE, "libkutacc.so")
 
 DTYPE_INT64, DTYPE_BF16, DTYPE_FP32 = 0, 1, 2
 
@@ -26,6 +26,8 @@ EXPORTS = [
     "kutacc_get_version", "kutacc_comm_init", "kutacc_comm_fini", "kutacc_af2_all_gather", "kutacc_af2_transpose",
     "kutacc_af2_gating_attention", "kutacc_af2_global_attention", "kutacc_af2_linear",
     "kutacc_af2_linear_weight_prepack", "kutacc_af2_gemm_pack_get_size", "kutacc_af2_layernorm", "kutacc_af2_transition",
+    "kutacc_af2_triangle_multiplication_calc_proj", "kutacc_af2_triangle_multiplication_equation",
+    "kutacc_af2_triangle_multiplication_gate_and_out_linear", "kutacc_af2_triangle_multiplication_last",
     # part 2: additions
     "kutacc_b200_tensor_create", "kutacc_b200_tensor_destroy", "kutacc_b200_error_set", "kutacc_b200_last_error",
     "kutacc_b200_clear_error", "kutacc_b200_set_stream", "kutacc_b200_set_async", "kutacc_b200_set_sm_margin", "kutacc_b200_synchronize",
@@ -60,6 +62,24 @@ class TransWeights(C.Structure):
 
 class TransInputs(C.Structure):
     _fields_ = [("batch", C.c_int64), ("n_res", C.c_int64), ("input_act", C.c_void_p), ("intermediate_act", C.c_void_p)]
+
+
+class TmProjWeights(C.Structure):
+    """kutacc_af2_tm_proj_weights_t (include/kutacc.h:154-162)."""
+    _fields_ = [("c_o", C.c_int64), ("c_i", C.c_int64), ("proj_w", C.c_void_p), ("proj_b", C.c_void_p),
+                ("gate_w", C.c_void_p), ("gate_b", C.c_void_p)]
+
+
+class TmActInputs(C.Structure):
+    """kutacc_af2_tm_act_inputs_t (include/kutacc.h:168-175)."""
+    _fields_ = [("n_res", C.c_int64), ("n_res_gather", C.c_int64), ("proj_act", C.c_void_p), ("input_act", C.c_void_p),
+                ("proj_act_gate", C.c_void_p)]
+
+
+class TmLinearWeights(C.Structure):
+    """kutacc_af2_tm_linear_weights_t (include/kutacc.h:181-189)."""
+    _fields_ = [("c_o", C.c_int64), ("c_i", C.c_int64), ("gating_w", C.c_void_p), ("gating_b", C.c_void_p),
+                ("output_proj_w", C.c_void_p), ("output_proj_b", C.c_void_p)]
 
 
 class AttentionInputs(C.Structure):
@@ -99,6 +119,15 @@ def lib() -> C.CDLL:
     L.kutacc_af2_linear_weight_prepack.restype = None
     L.kutacc_af2_gemm_pack_get_size.argtypes = [C.c_char, C.c_char, C.c_char, C.c_int, C.c_int, C.c_int]
     L.kutacc_af2_gemm_pack_get_size.restype = C.c_size_t
+    L.kutacc_af2_triangle_multiplication_calc_proj.argtypes = [C.POINTER(TmActInputs), vp, C.POINTER(TmProjWeights), C.c_bool]
+    L.kutacc_af2_triangle_multiplication_calc_proj.restype = None
+    L.kutacc_af2_triangle_multiplication_equation.argtypes = [vp, vp, vp, i64, C.c_bool]
+    L.kutacc_af2_triangle_multiplication_equation.restype = None
+    L.kutacc_af2_triangle_multiplication_gate_and_out_linear.argtypes = [vp, vp, C.POINTER(TmActInputs), vp,
+                                                                         C.POINTER(TmLinearWeights), C.c_bool]
+    L.kutacc_af2_triangle_multiplication_gate_and_out_linear.restype = None
+    L.kutacc_af2_triangle_multiplication_last.argtypes = [vp, vp, i64, i64, i64]
+    L.kutacc_af2_triangle_multiplication_last.restype = None
     L.kutacc_b200_tensor_create.argtypes = [vp, i64, C.POINTER(i64), C.POINTER(i64), C.c_int]
     L.kutacc_b200_tensor_create.restype = vp
     L.kutacc_b200_tensor_destroy.argtypes = [vp]
@@ -326,6 +355,55 @@ def transition(batch: int, n_res: int, c_o: int, c_i: int, input_act, w1, b1, w2
     wts = TransWeights(c_o, c_i, _h(w1), _h(b1), _h(w2), _h(b2))
     ins = TransInputs(batch, n_res, _h(input_act), None)
     lib().kutacc_af2_transition(C.byref(ins), C.byref(wts), _h(out))
+    if check:
+        raise_if_error()
+
+
+# ---- triangle multiplication (include/kutacc.h:426-456) ------------------------------------------
+def make_tm_acts(n_res: int, n_res_gather: int, proj_act, input_act, proj_act_gate) -> TmActInputs:
+    ts = [None if t is None else tensor(t) for t in (proj_act, input_act, proj_act_gate)]
+    a = TmActInputs(n_res, n_res_gather, *[(t.handle if t is not None else None) for t in ts])
+    a._keep = ts
+    return a
+
+
+def make_tm_proj_weights(c_o: int, c_i: int, proj_w, proj_b, gate_w, gate_b) -> TmProjWeights:
+    ts = [tensor(t) for t in (proj_w, proj_b, gate_w, gate_b)]
+    w = TmProjWeights(c_o, c_i, *[t.handle for t in ts])
+    w._keep = ts
+    return w
+
+
+def make_tm_linear_weights(c_o: int, c_i: int, gating_w, gating_b, output_proj_w, output_proj_b) -> TmLinearWeights:
+    ts = [tensor(t) for t in (gating_w, gating_b, output_proj_w, output_proj_b)]
+    w = TmLinearWeights(c_o, c_i, *[t.handle for t in ts])
+    w._keep = ts
+    return w
+
+
+def tm_calc_proj(acts: TmActInputs, mask, weights: TmProjWeights, input_prepack: bool = False, check: bool = True) -> None:
+    lib().kutacc_af2_triangle_multiplication_calc_proj(C.byref(acts), _h(mask), C.byref(weights), bool(input_prepack))
+    if check:
+        raise_if_error()
+
+
+def tm_equation(center_act, left_proj_act, right_proj_act, n_res_gather: int, is_incoming: bool, check: bool = True) -> None:
+    lib().kutacc_af2_triangle_multiplication_equation(_h(center_act), _h(left_proj_act), _h(right_proj_act),
+                                                      int(n_res_gather), bool(is_incoming))
+    if check:
+        raise_if_error()
+
+
+def tm_gate_and_out_linear(gate, out, acts: TmActInputs, center_act, weights: TmLinearWeights, input_prepack: bool = False,
+                           check: bool = True) -> None:
+    lib().kutacc_af2_triangle_multiplication_gate_and_out_linear(_h(gate), _h(out), C.byref(acts), _h(center_act),
+                                                                 C.byref(weights), bool(input_prepack))
+    if check:
+        raise_if_error()
+
+
+def tm_last(out, gate, n_res: int, n_res_gather: int, c_o: int, check: bool = True) -> None:
+    lib().kutacc_af2_triangle_multiplication_last(_h(out), _h(gate), int(n_res), int(n_res_gather), int(c_o))
     if check:
         raise_if_error()
 

@@ -151,7 +151,7 @@ static void gating_attention_impl(Tensor &input, int64_t batch, int64_t seq_len,
             if (D == 32) {
                 ok = dev::tcgen05_proj_qkvg_bf16(stream, x_c, d_wq.dev, d_wk.dev, d_wv.dev, d_wg.dev,
                                                  (const float *)d_bg.dev, q_c, k_c, v_km, g_c, (int)nbr, (int)S, (int)H,
-                                                 (int)D, true, s_pad8);
+                                                 (int)D, true, s_pad8, /*gate_sigmoid=*/true);
                 v_key_major = ok;
             }
             if (!ok)
@@ -163,7 +163,7 @@ static void gating_attention_impl(Tensor &input, int64_t batch, int64_t seq_len,
                                                 (int)D, 1.0f);
             if (ok && v_key_major)
                 ok = dev::tcgen05_attn_core_bf16(stream, q_c, k_c, v_km, s_pad8, g_c, bias_c, bias_s0, nb_dev, nb_sh,
-                                                 nb_sq, a_c, (int)nbr, (int)S, (int)H, (int)D, scale);
+                                                 nb_sq, a_c, (int)nbr, (int)S, (int)H, (int)D, scale, /*gate_is_sigmoid=*/true);
             else
                 ok = ok && dev::launch_attn_core_bf16(stream, q_c, k_c, v_c, g_c, bias_c, bias_s0, nb_dev, nb_sh, nb_sq,
                                                       a_c, (int)nbr, (int)S, (int)H, (int)D, scale);

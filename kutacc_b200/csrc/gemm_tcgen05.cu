@@ -67,10 +67,14 @@ struct GemmParams {
     int head_dim;           // > 0: segment output is [B*H][S][D] (coords d, s, b*H + h); 0: [B][S][N_seg]
     int head_layout_mask;   // bit i set: segment i uses the head layout
     int transposed_mask;    // bit i set: segment i is stored transposed, [B*H][D][S] (coords s, d, b*H + h)
+    int chanmajor_mask;     // bit i set: segment i is stored transposed and channel-major, [N_seg][B][S] (coords s, b, n)
+    int w_batched;          // non-zero: W is [B][N_seg][K], one matrix per batch row (coords k, n, b)
     int heads;
     int K;
     int S, B;
     int relu;               // non-zero: max(0, .) after the bias, before the bf16 rounding
+    int sigmoid_mask;       // bit i set: segment i stores bf16(sigmoid(bf16(y))) (the gate of the attention, whose
+                            // reference rounds the gate to bf16 before the sigmoid: gating_attention.cpp:62-66,134-147)
     int *err;
 };
 
@@ -90,6 +94,13 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr)
 // instruction descriptor: D fp32, A and B bf16, both K-major, N = 128, M = 128
 constexpr uint32_t kInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 
+// 1 / (1 + exp(-g)) of the bf16-rounded g, in fp32
+__device__ __forceinline__ float sigmoid_of_bf16(float y)
+{
+    const float g = round_to_bf16_f32(y);
+    return 1.0f / (1.0f + ex2_approx(-g * 1.4426950408889634f));
+}
+
 __global__ void __launch_bounds__(THREADS, 2)
 gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p)
 {
@@ -104,10 +115,10 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p)
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int s_tiles = (p.S + BM - 1) / BM;
-    const int n_tiles_seg = p.seg_n / BN;
+    const int n_tiles_seg = (p.seg_n + BN - 1) / BN;    // a ragged last tile is zero-filled on load and clipped on store
     const int n_tiles = n_tiles_seg * p.nseg;
     const int num_tiles = p.B * s_tiles * n_tiles;
-    const int nk = p.K / BK;
+    const int nk = (p.K + BK - 1) / BK;                 // columns past K are zero-filled by TMA
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < NSTAGE; ++s) {
@@ -150,7 +161,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p)
                     const uint32_t st = smem + (uint32_t)s * STAGE_BYTES;
                     mbar_arrive_expect_tx(full_bar(s), STAGE_BYTES);
                     tma_load_3d(st, &maps.a, full_bar(s), kc * BK, s0, b);
-                    tma_load_3d(st + SLAB_BYTES, wmap, full_bar(s), kc * BK, n0, 0);
+                    tma_load_3d(st + SLAB_BYTES, wmap, full_bar(s), kc * BK, n0, p.w_batched ? b : 0);
                 }
             }
         }
@@ -207,7 +218,9 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p)
             tc_fence_after();
             const float *bias = p.bias[seg];
             const bool head_layout = (p.head_layout_mask >> seg) & 1;
-            const bool transposed = (p.transposed_mask >> seg) & 1;
+            const bool chanmajor = (p.chanmajor_mask >> seg) & 1;
+            const bool transposed = ((p.transposed_mask >> seg) & 1) || chanmajor;
+            const bool sigmoid = (p.sigmoid_mask >> seg) & 1;
             const CUtensorMap *omap = &maps.out[seg];
             const int row0 = s0 + quad * 32;                  // first row of this warp inside the batch row
             uint32_t r[2][32];
@@ -230,6 +243,12 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p)
                             y1 = fmaxf(y1, 0.f);
                             y2 = fmaxf(y2, 0.f);
                             y3 = fmaxf(y3, 0.f);
+                        }
+                        if (sigmoid) {
+                            y0 = sigmoid_of_bf16(y0);
+                            y1 = sigmoid_of_bf16(y1);
+                            y2 = sigmoid_of_bf16(y2);
+                            y3 = sigmoid_of_bf16(y3);
                         }
                         packed[2 * j4] = pack_bf16x2(y0, y1);
                         packed[2 * j4 + 1] = pack_bf16x2(y2, y3);
@@ -266,8 +285,12 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p)
                     fence_proxy_async();
                     __syncwarp();
                     if (lane == 0) {
-                        const int hh = n / p.head_dim, d0 = n - hh * p.head_dim;
-                        tma_store_3d(omap, stg, row0, d0, b * p.heads + hh);
+                        if (chanmajor) {
+                            tma_store_3d(omap, stg, row0, b, n);
+                        } else {
+                            const int hh = n / p.head_dim, d0 = n - hh * p.head_dim;
+                            tma_store_3d(omap, stg, row0, d0, b * p.heads + hh);
+                        }
                         tma_store_commit();
                     }
                     ++nstore;
@@ -329,7 +352,7 @@ bool launch(cudaStream_t stream, const GemmMaps &maps, const GemmParams &p, cons
         configured = true;
     }
     const int s_tiles = (p.S + BM - 1) / BM;
-    const int64_t tiles = (int64_t)p.B * s_tiles * (p.seg_n / BN) * p.nseg;
+    const int64_t tiles = (int64_t)p.B * s_tiles * ((p.seg_n + BN - 1) / BN) * p.nseg;
     const unsigned grid = (unsigned)std::min<int64_t>(tiles, 2 * std::max(1, sm_count() - runtime().sm_margin));
     KernelTimer timer__(name, stream);
     gemm_tcgen05_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(maps, p);
@@ -341,7 +364,7 @@ bool launch(cudaStream_t stream, const GemmMaps &maps, const GemmParams &p, cons
 
 bool tcgen05_proj_qkvg_bf16(cudaStream_t stream, const void *x, const void *wq, const void *wk, const void *wv,
                             const void *wg, const float *bg, void *q, void *k, void *v, void *gate, int B, int S,
-                            int H, int D, bool v_transposed, int64_t v_pitch)
+                            int H, int D, bool v_transposed, int64_t v_pitch, bool gate_sigmoid)
 {
     const int C = H * D;
     if (C % 128 != 0 || (D != 32 && D != 64) || C > 256 * 64 || ((uintptr_t)bg & 15u)) return false;
@@ -374,25 +397,30 @@ bool tcgen05_proj_qkvg_bf16(cudaStream_t stream, const void *x, const void *wq, 
     p.head_dim = D;
     p.head_layout_mask = 0x7;
     p.transposed_mask = v_transposed ? 0x4 : 0;
+    p.chanmajor_mask = 0;
+    p.w_batched = 0;
     p.heads = H;
     p.K = C;
     p.S = S;
     p.B = B;
     p.relu = 0;
+    p.sigmoid_mask = gate_sigmoid ? 0x8 : 0;
     p.err = ew.device;
     return launch(stream, maps, p, "proj_qkvg");
 }
 
 bool tcgen05_linear_bias_bf16(cudaStream_t stream, const void *a, const void *w, const float *bias, void *out,
-                              int64_t out_row_stride, int B, int S, int N, int K, bool relu)
+                              int64_t out_row_stride, int B, int S, int N, int K, bool relu, int64_t a_row_stride)
 {
-    if (N % 128 != 0 || K % 64 != 0 || out_row_stride % 8 != 0 || ((uintptr_t)out & 15u) || ((uintptr_t)a & 15u) ||
-        ((uintptr_t)w & 15u) || ((uintptr_t)bias & 15u))
+    if (a_row_stride <= 0) a_row_stride = K;
+    if (N % 128 != 0 || K % 64 != 0 || out_row_stride % 8 != 0 || a_row_stride % 8 != 0 || a_row_stride < K ||
+        ((uintptr_t)out & 15u) || ((uintptr_t)a & 15u) || ((uintptr_t)w & 15u) || ((uintptr_t)bias & 15u))
         return false;
     KernelErrorWord &ew = kernel_error_word();
     if (ew.device == nullptr) return false;
     GemmMaps maps;
-    if (!make_tensor_map_bf16_3d(&maps.a, a, K, S, B, K, (uint64_t)S * K, BK, BM, 128)) return false;
+    if (!make_tensor_map_bf16_3d(&maps.a, a, K, S, B, (uint64_t)a_row_stride, (uint64_t)S * a_row_stride, BK, BM, 128))
+        return false;
     if (!make_tensor_map_bf16_3d(&maps.w[0], w, K, N, 1, K, (uint64_t)N * K, BK, BN, 128)) return false;
     if (!make_tensor_map_bf16_3d(&maps.out[0], out, N, S, B, (uint64_t)out_row_stride, (uint64_t)S * out_row_stride, 32,
                                  32, 64))
@@ -409,13 +437,106 @@ bool tcgen05_linear_bias_bf16(cudaStream_t stream, const void *a, const void *w,
     p.head_dim = 0;
     p.head_layout_mask = 0;
     p.transposed_mask = 0;
+    p.chanmajor_mask = 0;
+    p.w_batched = 0;
     p.heads = 1;
     p.K = K;
     p.S = S;
     p.B = B;
     p.relu = relu ? 1 : 0;
+    p.sigmoid_mask = 0;
     p.err = ew.device;
     return launch(stream, maps, p, relu ? "linear_bias_relu" : "linear_bias");
+}
+
+// Two projections of x [B, S, K] with row biases, both stored channel-major: out_i[n, b, s] = x[b, s, :] . w_i[n, :]
+// + bias_i[n] (out strides in elements: out_c_stride between channels, out_b_stride between batch rows). The
+// projection and gate products of the triangle multiplication (src/attention/triangle_multiplication.cpp:38-49).
+bool tcgen05_proj2_chanmajor_bf16(cudaStream_t stream, const void *x, const void *w0, const float *bias0, const void *w1,
+                                  const float *bias1, void *out0, void *out1, int64_t out_c_stride, int64_t out_b_stride,
+                                  int B, int S, int N, int K)
+{
+    if (N % 128 != 0 || K % 64 != 0 || out_c_stride % 8 != 0 || out_b_stride % 8 != 0 || out_b_stride < S ||
+        ((((uintptr_t)x | (uintptr_t)w0 | (uintptr_t)w1 | (uintptr_t)out0 | (uintptr_t)out1 | (uintptr_t)bias0 |
+           (uintptr_t)bias1) & 15u) != 0))
+        return false;
+    KernelErrorWord &ew = kernel_error_word();
+    if (ew.device == nullptr) return false;
+    GemmMaps maps;
+    const void *w[2] = {w0, w1};
+    void *o[2] = {out0, out1};
+    if (!make_tensor_map_bf16_3d(&maps.a, x, K, S, B, K, (uint64_t)S * K, BK, BM, 128)) return false;
+    for (int i = 0; i < 2; ++i) {
+        if (!make_tensor_map_bf16_3d(&maps.w[i], w[i], K, N, 1, K, (uint64_t)N * K, BK, BN, 128)) return false;
+        // [N][B][S]: dims (s, b, n), one 32 (s) x 1 x 32 (n) box per staging tile
+        if (!make_tensor_map_bf16_3d(&maps.out[i], o[i], S, B, N, (uint64_t)out_b_stride, (uint64_t)out_c_stride, 32, 1, 64, 32))
+            return false;
+    }
+    for (int i = 2; i < 4; ++i) {
+        maps.w[i] = maps.w[0];
+        maps.out[i] = maps.out[0];
+    }
+    GemmParams p;
+    p.bias[0] = bias0;
+    p.bias[1] = bias1;
+    p.bias[2] = p.bias[3] = nullptr;
+    p.seg_n = N;
+    p.nseg = 2;
+    p.head_dim = 0;
+    p.head_layout_mask = 0;
+    p.transposed_mask = 0;
+    p.chanmajor_mask = 0x3;
+    p.w_batched = 0;
+    p.heads = 1;
+    p.K = K;
+    p.S = S;
+    p.B = B;
+    p.relu = 0;
+    p.sigmoid_mask = 0;
+    p.err = ew.device;
+    return launch(stream, maps, p, "tm_proj");
+}
+
+// Batched product with one right-hand matrix per batch: out[b, m, n] = sum_k a[b, m, k] * w[b, n, k]
+// (a, w, out with row and batch strides in elements). The per-channel products of the triangle multiplication
+// (src/attention/triangle_multiplication.cpp:75-104).
+bool tcgen05_batched_nt_bf16(cudaStream_t stream, const void *a, int64_t a_row_stride, int64_t a_batch_stride,
+                             const void *w, int64_t w_row_stride, int64_t w_batch_stride, void *out,
+                             int64_t out_row_stride, int64_t out_batch_stride, int B, int M, int N, int K)
+{
+    if ((a_row_stride | a_batch_stride | w_row_stride | w_batch_stride | out_row_stride | out_batch_stride) % 8 != 0 ||
+        a_row_stride < K || w_row_stride < K || out_row_stride < N ||
+        ((((uintptr_t)a | (uintptr_t)w | (uintptr_t)out) & 15u) != 0))
+        return false;
+    KernelErrorWord &ew = kernel_error_word();
+    if (ew.device == nullptr) return false;
+    GemmMaps maps;
+    if (!make_tensor_map_bf16_3d(&maps.a, a, K, M, B, (uint64_t)a_row_stride, (uint64_t)a_batch_stride, BK, BM, 128)) return false;
+    if (!make_tensor_map_bf16_3d(&maps.w[0], w, K, N, B, (uint64_t)w_row_stride, (uint64_t)w_batch_stride, BK, BN, 128))
+        return false;
+    if (!make_tensor_map_bf16_3d(&maps.out[0], out, N, M, B, (uint64_t)out_row_stride, (uint64_t)out_batch_stride, 32, 32, 64))
+        return false;
+    for (int i = 1; i < 4; ++i) {
+        maps.w[i] = maps.w[0];
+        maps.out[i] = maps.out[0];
+    }
+    GemmParams p;
+    p.bias[0] = p.bias[1] = p.bias[2] = p.bias[3] = nullptr;
+    p.seg_n = N;
+    p.nseg = 1;
+    p.head_dim = 0;
+    p.head_layout_mask = 0;
+    p.transposed_mask = 0;
+    p.chanmajor_mask = 0;
+    p.w_batched = 1;
+    p.heads = 1;
+    p.K = K;
+    p.S = M;
+    p.B = B;
+    p.relu = 0;
+    p.sigmoid_mask = 0;
+    p.err = ew.device;
+    return launch(stream, maps, p, "tm_equation");
 }
 
 }  // namespace dev

@@ -78,8 +78,10 @@ extern "C" void kutacc_af2_global_attention(kutacc_af2_attention_inputs_t *q_bas
     DeviceArg d_out = resolve_out(o.data_ptr(), out_bytes);
     void *scratch = rt.take_workspace(scratch_bytes);
     if (kutacc_check_err_set) return;
-    KUTACC_CHECK((((uintptr_t)d_x.dev | (uintptr_t)d_out.dev | (uintptr_t)d_wg.dev | (uintptr_t)d_wo.dev) & 15u) == 0,
-                 "global_attention: q_data, out and weights must be 16-byte aligned");
+    // the kernels read activations and weights with 4- to 16-byte vector loads
+    KUTACC_CHECK((((uintptr_t)d_x.dev | (uintptr_t)d_out.dev | (uintptr_t)d_wg.dev | (uintptr_t)d_wo.dev |
+                   (uintptr_t)d_wq.dev | (uintptr_t)d_wk.dev | (uintptr_t)d_wv.dev) & 15u) == 0,
+                 "global_attention: q_data, out and the five weights must be 16-byte aligned");
     if (kutacc_check_err_set) return;
     // one pass over HBM where the shape allows it (a cluster of CTAs holds each column in shared memory),
     // otherwise three kernels per L2-sized group of columns with the split-softmax state in `scratch`

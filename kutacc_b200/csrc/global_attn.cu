@@ -664,8 +664,11 @@ extern "C" int kutacc_b200_global_attention_noalloc(const void *q_data, const vo
                  "kutacc_b200_global_attention_noalloc: invalid size (64 channels, batch <= 65535, out row stride a "
                  "multiple of 8 required)");
     if (kutacc_check_err_set) return -1;
-    KUTACC_CHECK((((uintptr_t)q_data | (uintptr_t)out | (uintptr_t)gating_w | (uintptr_t)output_w) & 15u) == 0,
-                 "kutacc_b200_global_attention_noalloc: q_data, out and weights must be 16-byte aligned");
+    // the kernels read activations and weights with 4- to 16-byte vector loads
+    KUTACC_CHECK((((uintptr_t)q_data | (uintptr_t)out | (uintptr_t)gating_w | (uintptr_t)output_w | (uintptr_t)query_w |
+                   (uintptr_t)key_w | (uintptr_t)value_w) & 15u) == 0 &&
+                     (((uintptr_t)gating_b | (uintptr_t)output_b) & 3u) == 0 && ((uintptr_t)q_mask & 1u) == 0,
+                 "kutacc_b200_global_attention_noalloc: q_data, out and the five weights must be 16-byte aligned");
     const size_t need = dev::global_attention_scratch_bytes((int)batch, (int)seq_len, (int)nheads, (int)head_size);
     KUTACC_CHECK(need <= KUTACC_B200_NOALLOC_SCRATCH_BYTES, "kutacc_b200_global_attention_noalloc: this shape needs ",
                  need, " bytes of scratch, the static scratch holds ", (size_t)KUTACC_B200_NOALLOC_SCRATCH_BYTES,

@@ -27,11 +27,42 @@ bool launch_linear_bias_bf16(cudaStream_t stream, const void *a, int64_t lda, co
 // K % 64 == 0, out row stride % 8 == 0). q is written unscaled. With v_transposed, v is written as
 // [B, H, D, S] with row pitch v_pitch (what the tcgen05 attention core consumes) instead of [B, H, S, D].
 // Return false when the shape is not covered.
+// With gate_sigmoid the gate segment stores bf16(sigmoid(bf16(x.Wg + bg))) instead of bf16(x.Wg + bg).
 bool tcgen05_proj_qkvg_bf16(cudaStream_t stream, const void *x, const void *wq, const void *wk, const void *wv,
                             const void *wg, const float *bg, void *q, void *k, void *v, void *gate, int B, int S,
-                            int H, int D, bool v_transposed, int64_t v_pitch);
+                            int H, int D, bool v_transposed, int64_t v_pitch, bool gate_sigmoid = false);
+// a_row_stride (elements, 0 = K): row stride of a, whose batch rows are S rows apart.
 bool tcgen05_linear_bias_bf16(cudaStream_t stream, const void *a, const void *w, const float *bias, void *out,
-                              int64_t out_row_stride, int B, int S, int N, int K, bool relu = false);
+                              int64_t out_row_stride, int B, int S, int N, int K, bool relu = false,
+                              int64_t a_row_stride = 0);
+// out_i[n, b, s] = x[b, s, :] . w_i[n, :] + bias_i[n], i = 0, 1: two projections stored channel-major
+// (N % 128 == 0, K % 64 == 0, strides multiples of 8 elements). False when the shape is not covered.
+bool tcgen05_proj2_chanmajor_bf16(cudaStream_t stream, const void *x, const void *w0, const float *bias0, const void *w1,
+                                  const float *bias1, void *out0, void *out1, int64_t out_c_stride, int64_t out_b_stride,
+                                  int B, int S, int N, int K);
+// out[b, m, n] = sum_k a[b, m, k] * w[b, n, k]: one right-hand matrix per batch (strides multiples of 8 elements).
+bool tcgen05_batched_nt_bf16(cudaStream_t stream, const void *a, int64_t a_row_stride, int64_t a_batch_stride,
+                             const void *w, int64_t w_row_stride, int64_t w_batch_stride, void *out,
+                             int64_t out_row_stride, int64_t out_batch_stride, int B, int M, int N, int K);
+
+// ---- triangle multiplication: element-wise steps and fallbacks (tm_kernels.cu) ------------------------
+// proj[c, b, i] = bf16((f32(proj) * f32(mask[b, i])) * sigmoid(f32(gate[c, b, i]))) in place; strides in elements.
+bool launch_tm_mask_gate(cudaStream_t stream, void *proj, const void *gate, const void *mask, int64_t c_i, int64_t n_res,
+                         int64_t n_gather, int64_t p_s0, int64_t p_s1, int64_t g_s0, int64_t g_s1, int64_t m_s0);
+// proj and gate of the projection step on CUDA cores (any shape): see tcgen05_proj2_chanmajor_bf16.
+bool launch_tm_proj_generic(cudaStream_t stream, const void *x, const void *w0, const float *b0, const void *w1,
+                            const float *b1, void *out0, void *out1, int64_t p_s0, int64_t p_s1, int64_t g_s0,
+                            int64_t g_s1, int64_t n_res, int64_t n_gather, int64_t c_o, int64_t c_i);
+// center[c, a, b] = sum_k left[c, a, k] * right[c, b, k] (incoming = 0) or sum_k right[c, k, a] * left[c, k, b]
+// on CUDA cores (any shape).
+bool launch_tm_equation_generic(cudaStream_t stream, const void *left, int64_t l_s0, int64_t l_s1, const void *right,
+                                int64_t r_s0, int64_t r_s1, void *center, int64_t c_s0, int64_t c_s1, int64_t c_i,
+                                int64_t n, bool incoming);
+// dst[c, a, k] = src[c, k, a] for every channel c (n x n matrices; dst dense with row pitch d_pitch)
+bool launch_tm_transpose(cudaStream_t stream, const void *src, int64_t s_s0, int64_t s_s1, void *dst, int64_t d_pitch,
+                         int64_t c_i, int64_t n);
+// out[r, :] = bf16(f32(out[r, :]) * sigmoid(f32(gate[r, :]))) for rows of c_o elements
+bool launch_tm_last(cudaStream_t stream, void *out, int64_t o_rs, const void *gate, int64_t g_rs, int64_t rows, int64_t c_o);
 
 // ---- fused attention core ------------------------------------------------------------------------
 // avg[b, s, h*D + d] = sigmoid(gate[b, s, h*D + d]) * softmax_k(bf16(q.k)*scale + bias[b,k] + nb[h,s,k]) . v
@@ -42,11 +73,13 @@ bool launch_attn_core_bf16(cudaStream_t stream, const void *q, const void *k, co
                            int64_t nb_stride_q, void *avg, int B, int S, int H, int D, float scale);
 
 // The same operator with both products on tcgen05 and the accumulators in tensor memory (head size 32).
-// vt is v transposed, [B, H, D, S] with row pitch vt_pitch, as tcgen05_proj_qkvg_bf16 writes it.
+// vt is v transposed, [B, H, D, S] with row pitch vt_pitch, as tcgen05_proj_qkvg_bf16 writes it. With
+// gate_is_sigmoid, `gate` already holds bf16(sigmoid(bf16(x.Wg + bg))) (the projection kernel's gate_sigmoid
+// option) and the kernel only multiplies.
 bool tcgen05_attn_core_bf16(cudaStream_t stream, const void *q, const void *k, const void *vt, int64_t vt_pitch,
                             const void *gate, const void *bias, int64_t bias_stride0, const void *nb,
                             int64_t nb_stride_h, int64_t nb_stride_q, void *avg, int B, int S, int H, int D,
-                            float scale);
+                            float scale, bool gate_is_sigmoid);
 
 // ---- generic (any shape, bf16 or fp32 storage, fp32 math) ------------------------------------------
 // c[m, n] = sum_k a[m, k] * w[n, k] (+ bias[n]) (+ beta * c[m, n]); a row stride lda, w row stride

@@ -1,7 +1,7 @@
 // Entry points of the reference that lie outside the gated-attention path. They are exported so
 // that a program linked against the reference library still resolves its symbols; calling one
 // reports an error through the usual convention and returns.
-// (include/kutacc.h:266,277,367,379,388,426-456 of the reference.)
+// (include/kutacc.h:266,277,367,379,388 of the reference.)
 #include "common.h"
 
 #define KUTACC_NOT_BUILT(name)                                                              \
@@ -15,7 +15,3 @@ KUTACC_NOT_BUILT(kutacc_af2_outer_product_mean_chunk)
 KUTACC_NOT_BUILT(kutacc_af2_invariant_point)
 KUTACC_NOT_BUILT(kutacc_af2_rigid_rot_vec_mul)
 KUTACC_NOT_BUILT(kutacc_af2_rigid_rot_matmul)
-KUTACC_NOT_BUILT(kutacc_af2_triangle_multiplication_calc_proj)
-KUTACC_NOT_BUILT(kutacc_af2_triangle_multiplication_equation)
-KUTACC_NOT_BUILT(kutacc_af2_triangle_multiplication_gate_and_out_linear)
-KUTACC_NOT_BUILT(kutacc_af2_triangle_multiplication_last)

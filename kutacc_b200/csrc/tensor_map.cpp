@@ -31,13 +31,14 @@ EncodeTiledFn encode_fn()
 }  // namespace
 
 bool make_tensor_map_bf16_3d(CUtensorMap *map, const void *base, uint64_t d0, uint64_t d1, uint64_t d2,
-                             uint64_t stride1, uint64_t stride2, uint32_t box0, uint32_t box1, int swizzle_bytes)
+                             uint64_t stride1, uint64_t stride2, uint32_t box0, uint32_t box1, int swizzle_bytes,
+                             uint32_t box2)
 {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return false;
     cuuint64_t dims[3] = {d0, d1, d2};
     cuuint64_t strides[2] = {stride1 * 2, stride2 * 2};  // bytes, dims 1 and 2
-    cuuint32_t box[3] = {box0, box1, 1};
+    cuuint32_t box[3] = {box0, box1, box2};
     cuuint32_t estr[3] = {1, 1, 1};
     CUtensorMapSwizzle sw = swizzle_bytes == 128  ? CU_TENSOR_MAP_SWIZZLE_128B
                             : swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B

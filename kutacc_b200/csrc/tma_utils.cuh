@@ -11,9 +11,10 @@ namespace dev {
 
 // ---- host: tensor maps ---------------------------------------------------------------------------
 // rank-3 bf16 tensor [d2][d1][d0] (d0 innermost, contiguous), strides in ELEMENTS for d1 and d2,
-// box [1][box1][box0]. swizzle_bytes in {0, 32, 64, 128} must equal box0 * 2 when non-zero.
+// box [box2][box1][box0]. swizzle_bytes in {0, 32, 64, 128} must equal box0 * 2 when non-zero.
 bool make_tensor_map_bf16_3d(CUtensorMap *map, const void *base, uint64_t d0, uint64_t d1, uint64_t d2,
-                             uint64_t stride1, uint64_t stride2, uint32_t box0, uint32_t box1, int swizzle_bytes);
+                             uint64_t stride1, uint64_t stride2, uint32_t box0, uint32_t box1, int swizzle_bytes,
+                             uint32_t box2 = 1);
 
 // Host-visible error word written by kernels whose bounded waits ran out (0 = none). The pointer is a
 // device-accessible alias of pinned host memory; the host reads *host after synchronising.
@@ -59,12 +60,29 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
         : "memory");
     return ok != 0;
 }
+// The same test with a suspend-time hint: the thread may sleep in hardware for up to `ns` nanoseconds (or until the
+// phase completes) instead of returning at once, so a waiting warp re-issues the instruction rarely and leaves the
+// issue slots and the memory-instruction queue to the warps that have work.
+__device__ __forceinline__ bool mbar_try_wait_suspend(uint32_t bar, uint32_t parity, uint32_t ns)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(ns)
+        : "memory");
+    return ok != 0;
+}
 // Bounded wait. `code` identifies the wait site in the error word; `limit` is in SM clocks.
 __device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, int *err, int code, long long limit)
 {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
-    while (!mbar_try_wait(bar, parity)) {
+    while (!mbar_try_wait_suspend(bar, parity, 0x989680u)) {
         if (clock64() - t0 > limit) {
             if (err) atomicCAS(err, 0, code);
             return false;

@@ -170,7 +170,8 @@ class HostShardedTriangleAttention:
         assert w.kind == "gating" and "wb" in w.arrays and w.B == w.S, "needs a full triangle workload"
         self.w, self.rank, self.world, self.device, self.api = w, rank, world, device, api
         N, S, C, H = w.B, w.S, w.C, w.H
-        r0, n = row_range(N, world, rank)
+        r0, r1 = row_range(N, world, rank)
+        n = r1 - r0
         assert n > 0 and N % world == 0, "rows must split evenly over the ranks"
         self.rows = (r0, n)
         A = w.arrays

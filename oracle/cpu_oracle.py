@@ -145,6 +145,62 @@ def transition_exact(x, w1, b1, w2, b2):
     return linear_exact(hid, w2, b2)
 
 
+def tm_calc_proj_bf16(x, mask, pw, pb, gw, gb):
+    """Triangle multiplication, projection step (src/attention/triangle_multiplication.cpp:25-70).
+    x [n_res, n_gather, c_o] u16, mask [n_res, n_gather] u16, pw/gw [c_i, c_o] u16, pb/gb [c_i] f32.
+    Returns (proj, gate), both [c_i, n_res, n_gather] u16: proj already multiplied by mask and sigmoid(gate)."""
+    x = np.ascontiguousarray(x, dtype=np.uint16)
+    n_res, n_gather, c_o = x.shape
+    c_i = pw.shape[0]
+    f16 = lambda a: np.ascontiguousarray(a, dtype=np.uint16)
+    f32 = lambda a: np.ascontiguousarray(a, dtype=np.float32)
+    mask, pw, gw, pb, gb = f16(mask), f16(pw), f16(gw), f32(pb), f32(gb)
+    proj = np.empty((c_i, n_res, n_gather), dtype=np.uint16)
+    gate = np.empty((c_i, n_res, n_gather), dtype=np.uint16)
+    lib().orc_tm_calc_proj_bf16(_p(x), _p(mask), _p(pw), _p(pb), _p(gw), _p(gb), C.c_int64(n_res), C.c_int64(n_gather),
+                                C.c_int64(c_o), C.c_int64(c_i), _p(proj), _p(gate))
+    return proj, gate
+
+
+def tm_calc_proj_exact(x, mask, pw, pb, gw, gb):
+    f32 = lambda a: np.ascontiguousarray(a, dtype=np.float32)
+    x, mask, pw, pb, gw, gb = map(f32, (x, mask, pw, pb, gw, gb))
+    n_res, n_gather, c_o = x.shape
+    c_i = pw.shape[0]
+    proj = np.empty((c_i, n_res, n_gather), dtype=np.float32)
+    lib().orc_tm_calc_proj_exact(_p(x), _p(mask), _p(pw), _p(pb), _p(gw), _p(gb), C.c_int64(n_res), C.c_int64(n_gather),
+                                 C.c_int64(c_o), C.c_int64(c_i), _p(proj))
+    return proj
+
+
+def tm_equation_bf16(left, right, incoming):
+    """center[ch] = left[ch] . right[ch]^T (outgoing) or right[ch]^T . left[ch] (incoming), per channel
+    (triangle_multiplication.cpp:75-104). left, right [c_i, n, n] u16 -> [c_i, n, n] u16."""
+    left = np.ascontiguousarray(left, dtype=np.uint16)
+    right = np.ascontiguousarray(right, dtype=np.uint16)
+    c_i, n, _ = left.shape
+    center = np.empty((c_i, n, n), dtype=np.uint16)
+    lib().orc_tm_equation_bf16(_p(left), _p(right), C.c_int64(c_i), C.c_int64(n), C.c_int(1 if incoming else 0), _p(center))
+    return center
+
+
+def tm_equation_exact(left, right, incoming):
+    left = np.ascontiguousarray(left, dtype=np.float32)
+    right = np.ascontiguousarray(right, dtype=np.float32)
+    c_i, n, _ = left.shape
+    center = np.empty((c_i, n, n), dtype=np.float32)
+    lib().orc_tm_equation_exact(_p(left), _p(right), C.c_int64(c_i), C.c_int64(n), C.c_int(1 if incoming else 0), _p(center))
+    return center
+
+
+def tm_last_bf16(out, gate):
+    """out = bf16(f32(out) * sigmoid(f32(gate))) element by element (triangle_multiplication.cpp:138-158)."""
+    res = np.ascontiguousarray(out, dtype=np.uint16).copy()
+    gate = np.ascontiguousarray(gate, dtype=np.uint16)
+    lib().orc_tm_last_bf16(_p(res), _p(gate), C.c_int64(res.size))
+    return res
+
+
 def transpose_bytes(shards, m, n):
     """shards[r]: uint8 [chunk_r(m), n, len] (rows split over the ranks) -> list of uint8 [m, chunk_r(n), len]."""
     world = len(shards)

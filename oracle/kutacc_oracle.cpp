@@ -623,4 +623,97 @@ void orc_layernorm_exact(const float *x, const float *gamma, const float *beta, 
     }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Triangle multiplication (src/attention/triangle_multiplication.cpp:25-150), in the four steps the
+// reference exports. Layouts: the input activations x are [n_res, n_gather, c_o]; the projections and
+// the per-channel products are channel-major, [c_i, n_res, n_gather]; gate and out of the last two steps
+// are [n_res, n_gather, c_o]. Biases are fp32.
+//
+//   calc_proj (:25-70)  p = bf16(x.pw^T + pb), g = bf16(x.gw^T + gb) (both stored), then in place
+//                       p = bf16((f32(p) * f32(mask)) * sigmoid(f32(g)))        (:56-65, this order)
+//   equation (:75-104)  outgoing: c[ch, a, b] = bf16(sum_k left[ch, a, k] * right[ch, b, k])
+//                       incoming: c[ch, a, b] = bf16(sum_k right[ch, k, a] * left[ch, k, b])
+//   gate_and_out_linear (:109-133)  two row-bias linears (orc_linear_bf16)
+//   last (:138-158)     out = bf16(f32(out) * sigmoid(f32(gate)))
+// ------------------------------------------------------------------------------------------------
+void orc_tm_calc_proj_bf16(const uint16_t *x, const uint16_t *mask, const uint16_t *pw, const float *pb,
+                           const uint16_t *gw, const float *gb, int64_t n_res, int64_t n_gather, int64_t c_o,
+                           int64_t c_i, uint16_t *proj, uint16_t *gate)
+{
+    fexpa_init();
+    const int64_t P = n_res * n_gather;
+#pragma omp parallel for schedule(static)
+    for (int64_t pos = 0; pos < P; ++pos) {
+        const uint16_t *xr = x + pos * c_o;
+        const float mk = bf2f(mask[pos]);
+        for (int64_t ci = 0; ci < c_i; ++ci) {
+            float ap = 0.f, ag = 0.f;
+            for (int64_t k = 0; k < c_o; ++k) {
+                const float xv = bf2f(xr[k]);
+                ap += xv * bf2f(pw[ci * c_o + k]);
+                ag += xv * bf2f(gw[ci * c_o + k]);
+            }
+            const uint16_t pbf = f2bf(ap + pb[ci]), gbf = f2bf(ag + gb[ci]);
+            gate[ci * P + pos] = gbf;
+            float v = bf2f(pbf) * mk;
+            v = v * fexpa_sigmoid(bf2f(gbf));
+            proj[ci * P + pos] = f2bf(v);
+        }
+    }
+}
+void orc_tm_calc_proj_exact(const float *x, const float *mask, const float *pw, const float *pb, const float *gw,
+                            const float *gb, int64_t n_res, int64_t n_gather, int64_t c_o, int64_t c_i, float *proj)
+{
+    const int64_t P = n_res * n_gather;
+#pragma omp parallel for schedule(static)
+    for (int64_t pos = 0; pos < P; ++pos)
+        for (int64_t ci = 0; ci < c_i; ++ci) {
+            double ap = pb[ci], ag = gb[ci];
+            for (int64_t k = 0; k < c_o; ++k) {
+                ap += (double)x[pos * c_o + k] * pw[ci * c_o + k];
+                ag += (double)x[pos * c_o + k] * gw[ci * c_o + k];
+            }
+            proj[ci * P + pos] = (float)(ap * mask[pos] / (1.0 + std::exp(-ag)));
+        }
+}
+void orc_tm_equation_bf16(const uint16_t *left, const uint16_t *right, int64_t c_i, int64_t n, int incoming,
+                          uint16_t *center)
+{
+#pragma omp parallel for schedule(static) collapse(2)
+    for (int64_t ch = 0; ch < c_i; ++ch)
+        for (int64_t a = 0; a < n; ++a) {
+            const uint16_t *L = left + ch * n * n, *R = right + ch * n * n;
+            for (int64_t b = 0; b < n; ++b) {
+                float acc = 0.f;
+                if (!incoming)
+                    for (int64_t k = 0; k < n; ++k) acc += bf2f(L[a * n + k]) * bf2f(R[b * n + k]);
+                else
+                    for (int64_t k = 0; k < n; ++k) acc += bf2f(R[k * n + a]) * bf2f(L[k * n + b]);
+                center[(ch * n + a) * n + b] = f2bf(acc);
+            }
+        }
+}
+void orc_tm_equation_exact(const float *left, const float *right, int64_t c_i, int64_t n, int incoming, float *center)
+{
+#pragma omp parallel for schedule(static) collapse(2)
+    for (int64_t ch = 0; ch < c_i; ++ch)
+        for (int64_t a = 0; a < n; ++a) {
+            const float *L = left + ch * n * n, *R = right + ch * n * n;
+            for (int64_t b = 0; b < n; ++b) {
+                double acc = 0;
+                if (!incoming)
+                    for (int64_t k = 0; k < n; ++k) acc += (double)L[a * n + k] * R[b * n + k];
+                else
+                    for (int64_t k = 0; k < n; ++k) acc += (double)R[k * n + a] * L[k * n + b];
+                center[(ch * n + a) * n + b] = (float)acc;
+            }
+        }
+}
+void orc_tm_last_bf16(uint16_t *out, const uint16_t *gate, int64_t n)
+{
+    fexpa_init();
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < n; ++i) out[i] = f2bf(bf2f(out[i]) * fexpa_sigmoid(bf2f(gate[i])));
+}
+
 }  // extern "C"

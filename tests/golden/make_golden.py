@@ -7,7 +7,8 @@ Two kinds of vectors live here:
   * transpose_grid.npz   - the byte grids of the reference's re-shard test
     (test/functest/comm/transpose_test.cpp:19-81), restated from their closed form: rank r holds a 5 x 6
     grid counting up from 32*r; afterwards rank d holds the three columns of block d of the stacked grid.
-  * gating_small.npz / global_small.npz / layernorm_small.npz / transition_small.npz - outputs of the CPU oracle (oracle/kutacc_oracle.cpp) on
+  * gating_small.npz / global_small.npz / layernorm_small.npz / transition_small.npz / triangle_multiplication_small.npz -
+    outputs of the CPU oracle (oracle/kutacc_oracle.cpp) on
     small seeded cases. The reference cannot be executed here (ARM SVE sources, closed GEMM), so
     these pin the oracle against accidental change; they are not outputs of the reference.
 
@@ -83,6 +84,23 @@ def transition_small():
              exact=O.transition_exact(W.as_f32(x), W.as_f32(w1), b1, W.as_f32(w2), b2))
 
 
+def triangle_multiplication_small():
+    from oracle import cpu_oracle as O
+    rng = np.random.default_rng(15)
+    n, c_o, c_i = 10, 16, 8
+    x = W.bf16_bits(rng.standard_normal((n, n, c_o), dtype=np.float32))
+    mask = W.bf16_bits((rng.random((n, n)) >= 0.2).astype(np.float32))
+    pw = W.bf16_bits(rng.standard_normal((c_i, c_o), dtype=np.float32) / 4)
+    gw = W.bf16_bits(rng.standard_normal((c_i, c_o), dtype=np.float32) / 4)
+    pb = rng.standard_normal(c_i).astype(np.float32)
+    gb = rng.standard_normal(c_i).astype(np.float32)
+    right = W.bf16_bits(rng.standard_normal((c_i, n, n), dtype=np.float32))
+    proj, gate = O.tm_calc_proj_bf16(x, mask, pw, pb, gw, gb)
+    np.savez(os.path.join(HERE, "triangle_multiplication_small.npz"), x=x, mask=mask, pw=pw, pb=pb, gw=gw, gb=gb, right=right,
+             proj=proj, gate=gate, outgoing=O.tm_equation_bf16(proj, right, False),
+             incoming=O.tm_equation_bf16(proj, right, True), last=O.tm_last_bf16(proj, gate))
+
+
 if __name__ == "__main__":
     all_gather_grid()
     transpose_grid()
@@ -90,4 +108,5 @@ if __name__ == "__main__":
     global_small()
     layernorm_small()
     transition_small()
+    triangle_multiplication_small()
     print("golden vectors written to", HERE)

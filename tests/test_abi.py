@@ -139,8 +139,16 @@ def test_error_flag_is_sticky_and_clearable(kutacc_lib):
 
 
 def test_not_built_entry_points_report(kutacc_lib):
-    kutacc_lib.kutacc_af2_triangle_multiplication_last()
+    kutacc_lib.kutacc_af2_invariant_point()
     assert api.error_set() and "not part of" in api.last_error()
+    api.clear_error()
+    # the reference's robustness tests for the triangle multiplication: one null handle each
+    # (test/functest/cal/triangle_multiplication_test.cpp)
+    kutacc_lib.kutacc_af2_triangle_multiplication_last(None, None, 2, 2, 2)
+    assert api.error_set() and "input args nullptr error" in api.last_error()
+    api.clear_error()
+    kutacc_lib.kutacc_af2_triangle_multiplication_equation(None, None, None, 4, False)
+    assert api.error_set() and "nullptr" in api.last_error()
     api.clear_error()
     # null arguments of a built operator are reported in the reference's words, nothing is dereferenced
     kutacc_lib.kutacc_af2_transition(None, None, None)

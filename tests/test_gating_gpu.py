@@ -81,6 +81,21 @@ def test_pipelined_host_path_matches_device_path(kutacc_lib):
     assert np.array_equal(_run(w, device=False), host)       # staging buffers are reused across calls
 
 
+def test_strided_host_out_keeps_the_bytes_between_rows(kutacc_lib):
+    """A HOST `out` whose row stride is wider than nchannels: the reference writes through strides()[1] and
+    touches only the C elements of each row, so the padding must come back unchanged (plain and chunked path)."""
+    for B, S in ((2, 64), (35, 256)):
+        w = W.random_gating_case(seed=19, B=B, S=S, H=4, D=32, with_nb=False)
+        dense = _run(w, device=False).copy()
+        host = runner.HostCase(w)
+        pad = torch.full((w.B, w.S, w.C + 16), 7.0, dtype=torch.bfloat16).pin_memory()
+        api.gating_attention(host.t_x, host.inputs, host.t_bias, host.t_nb, host.weights,
+                             api.tensor(pad, sizes=[w.B, w.S, w.C], strides=[w.S * (w.C + 16), w.C + 16, 1]))
+        got = pad.float().numpy()
+        assert np.array_equal(got[:, :, :w.C], dense)
+        assert (got[:, :, w.C:] == 7.0).all()
+
+
 def test_strided_out_and_bias(kutacc_lib):
     # out row stride (strides[1]) and bias row stride (strides[0]) are honoured
     w = W.random_gating_case(seed=9, B=2, S=64, H=2, D=32, with_nb=False)
@@ -105,6 +120,29 @@ def test_benchmark_shapes_subsampled_rows(kutacc_lib, name, rows):
     assert helpers.rel_err(got, helpers.oracle_faithful(w)) <= helpers.BF16_TOL
 
 
+def _pick_rows(w, rows):
+    """The batch rows `rows` of a gating workload as a workload of their own (weights and pair bias shared)."""
+    pick = W.Workload(name="pick", kind="gating", dtype=w.dtype, B=len(rows), S=w.S, H=w.H, D=w.D, seed=0, has_nb=w.has_nb)
+    pick.arrays = dict(w.arrays)
+    pick.arrays["x"] = w.arrays["x"][rows]
+    pick.arrays["bias"] = w.arrays["bias"][rows]
+    return pick
+
+
+@pytest.mark.parametrize("name,rows", [("triangle_end_1024", [0, 1, 510, 511, 1022, 1023]),
+                                       ("msa_col_512", [0, 1, 190, 191, 382, 383])])
+def test_full_size_rows_spread_over_the_batch(kutacc_lib, name, rows):
+    """The two largest gating shapes at FULL size on the GPU; the oracle checks rows at the start, in the middle
+    and at the end of the batch (both rows of a pair the kernel processes together), and a sub-batch must give
+    the same bits as the full call (rows are independent problems)."""
+    w = W.make(name)
+    full = _run(w)
+    assert np.isfinite(full).all()
+    assert helpers.rel_err(full[rows], helpers.oracle_faithful(_pick_rows(w, rows))) <= helpers.BF16_TOL
+    sub = W.make(name, rows=5)                           # odd: the last row has no partner in its pair
+    assert np.array_equal(_run(sub), full[:5])
+
+
 def test_msa_row_fp32_shape_subsampled(kutacc_lib):
     w = W.make("msa_row_fp32", rows=6)
     got = _run(w)
@@ -124,11 +162,7 @@ def test_full_size_properties_triangle_start(kutacc_lib):
     # (2) oracle on a few rows spread over the batch, including a fully masked one
     masked = np.where(w.arrays["mask"].sum(1) == 0)[0]
     rows = sorted(set([0, 191, 383] + masked[:1].tolist()))
-    pick = W.Workload(name="pick", kind="gating", dtype="bf16", B=len(rows), S=w.S, H=w.H, D=w.D, seed=0, has_nb=True)
-    pick.arrays = dict(w.arrays)
-    pick.arrays["x"] = w.arrays["x"][rows]
-    pick.arrays["bias"] = w.arrays["bias"][rows]
-    assert helpers.rel_err(full[rows], helpers.oracle_faithful(pick)) <= helpers.BF16_TOL
+    assert helpers.rel_err(full[rows], helpers.oracle_faithful(_pick_rows(w, rows))) <= helpers.BF16_TOL
     # (3) shifting the output bias shifts the output by the same amount (up to bf16 rounding)
     case.bo += 0.5
     shifted = runner.out_to_f32(case.run())
@@ -145,7 +179,8 @@ def test_repeat_calls_are_deterministic(kutacc_lib):
 
 def test_sharded_triangle_flow_on_one_rank_matches_the_plain_call(kutacc_lib):
     # pair-bias projection + attention slab by slab (kutacc_b200/sharding.py) against one call with the
-    # workload's own pair bias; the two biases may differ in the last bf16 bit (fp32 summation order)
+    # workload's own pair bias; the two biases may differ in the last bf16 bit (fp32 summation order of the host's
+    # BLAS against the kernel's), which can move an output by one bf16 step (2^-8 relative)
     from kutacc_b200 import sharding
     w = W.make("triangle_start_384", rows=128, seq=128)
     want = runner.out_to_f32(runner.DeviceCase(w).run())
@@ -153,7 +188,7 @@ def test_sharded_triangle_flow_on_one_rank_matches_the_plain_call(kutacc_lib):
     got = runner.out_to_f32(op.step())
     torch.cuda.synchronize()
     api.raise_if_error()
-    assert helpers.rel_err(got, want) <= 2e-3
+    assert helpers.rel_err(got, want) <= 5e-3
     assert helpers.rel_err(got, helpers.oracle_faithful(w)) <= helpers.BF16_TOL
 
 

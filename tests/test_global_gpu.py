@@ -42,6 +42,20 @@ def test_extra_msa_shape_subsampled_columns(kutacc_lib):
     assert helpers.rel_err(got, helpers.oracle_faithful(w)) <= helpers.BF16_TOL
 
 
+def test_extra_msa_shape_full_size_columns_spread_over_the_batch(kutacc_lib):
+    """The extra-MSA shape at FULL size on the GPU; the oracle checks columns at the start, in the middle and at
+    the end of the 384."""
+    w = W.make("extra_msa_global")
+    full = _run(w)
+    assert np.isfinite(full).all()
+    cols = [0, 1, 191, 192, 382, 383]
+    pick = W.Workload(name="pick", kind="global", dtype="bf16", B=len(cols), S=w.S, H=w.H, D=w.D, seed=0)
+    pick.arrays = dict(w.arrays)
+    pick.arrays["x"] = w.arrays["x"][cols]
+    pick.arrays["mask"] = w.arrays["mask"][cols]
+    assert helpers.rel_err(full[cols], helpers.oracle_faithful(pick)) <= helpers.BF16_TOL
+
+
 def test_host_pointers_match_device_pointers(kutacc_lib):
     w = W.random_global_case(seed=22, B=2, S=200)
     assert np.array_equal(_run(w, True), _run(w, False))

@@ -236,3 +236,35 @@ def test_new_operator_oracles_against_committed_vectors():
     assert np.array_equal(O.transition_bf16(tr["x"], tr["w1"], tr["b1"], tr["w2"], tr["b2"]), tr["faithful"])
     assert np.allclose(O.transition_exact(as_f32(tr["x"]), as_f32(tr["w1"]), tr["b1"], as_f32(tr["w2"]), tr["b2"]), tr["exact"],
                        rtol=0, atol=1e-5)
+
+
+def test_triangle_multiplication_oracle():
+    """The restatement of src/attention/triangle_multiplication.cpp:25-158 against an independent float64 formula
+    and against its committed vectors (tests/golden/make_golden.py)."""
+    from kutacc_b200.workloads import as_f32, bf16_bits
+    tm = np.load(os.path.join(GOLD, "triangle_multiplication_small.npz"))
+    proj, gate = O.tm_calc_proj_bf16(tm["x"], tm["mask"], tm["pw"], tm["pb"], tm["gw"], tm["gb"])
+    assert np.array_equal(proj, tm["proj"]) and np.array_equal(gate, tm["gate"])
+    assert np.array_equal(O.tm_equation_bf16(proj, tm["right"], False), tm["outgoing"])
+    assert np.array_equal(O.tm_equation_bf16(proj, tm["right"], True), tm["incoming"])
+    assert np.array_equal(O.tm_last_bf16(proj, gate), tm["last"])
+    # float64 textbook formula
+    f = lambda a: as_f32(a).astype(np.float64)
+    x, mask, pw, gw = f(tm["x"]), f(tm["mask"]), f(tm["pw"]), f(tm["gw"])
+    n, c_o = x.shape[0], x.shape[2]
+    c_i = pw.shape[0]
+    lin = x.reshape(-1, c_o) @ pw.T + tm["pb"]
+    g = x.reshape(-1, c_o) @ gw.T + tm["gb"]
+    want = (lin * mask.reshape(-1, 1) / (1 + np.exp(-g))).T.reshape(c_i, n, n)
+    exact = O.tm_calc_proj_exact(as_f32(tm["x"]), as_f32(tm["mask"]), as_f32(tm["pw"]), tm["pb"], as_f32(tm["gw"]), tm["gb"])
+    assert np.abs(exact - want).max() <= 1e-5
+    assert np.abs(as_f32(proj) - want).max() <= 1e-2 * np.abs(want).max()
+    L, R = f(proj), f(tm["right"])
+    for incoming, eq in ((False, "cak,cbk->cab"), (True, "cka,ckb->cab")):
+        a, b = (L, R) if not incoming else (R, L)
+        ref = np.einsum(eq, a, b)
+        got = O.tm_equation_exact(as_f32(proj), as_f32(tm["right"]), incoming)
+        assert np.abs(got - ref).max() <= 1e-4
+        assert np.abs(as_f32(O.tm_equation_bf16(proj, tm["right"], incoming)) - ref).max() <= 2.0 ** -8 * np.abs(ref).max()
+    sig = 1 / (1 + np.exp(-f(gate)))
+    assert np.abs(as_f32(O.tm_last_bf16(proj, gate)) - f(proj) * sig).max() <= 1e-2 * np.abs(f(proj)).max()

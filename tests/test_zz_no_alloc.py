@@ -17,6 +17,7 @@ import torch
 
 from kutacc_b200 import api, runner
 from kutacc_b200 import workloads as W
+from tests import helpers
 
 pytestmark = pytest.mark.gpu
 
@@ -50,6 +51,41 @@ def test_noalloc_entry_matches_regular_operator_twice_in_a_row(kutacc_lib):
         if (w.H, w.D) != (8, 8):
             assert np.array_equal(got, want)
         assert api.lib().kutacc_b200_workspace_bytes() == held      # the library's pool did not grow
+
+
+def test_noalloc_entry_matches_the_oracle_on_split_columns_and_on_a_stream(kutacc_lib):
+    """The entry point's own kernels against the CPU oracle (the regular operator runs a different kernel for
+    8 heads x 8): a column long enough to be cut into several row splits, a length that is not a multiple of
+    16, one column with every row masked, and the call made on a stream of the caller's."""
+    w = W.random_global_case(seed=34, B=3, S=1000 + 13, H=8, D=8, zero_mask_rows=1)
+    case = runner.DeviceCase(w)
+    ref = helpers.oracle_faithful(w)
+    stream = torch.cuda.Stream()
+    for _ in range(2):
+        out = torch.full((w.B, w.S, w.C), float("nan"), dtype=torch.bfloat16, device="cuda:0")
+        stream.wait_stream(torch.cuda.current_stream())
+        assert _noalloc(case, out, stream.cuda_stream) == 0
+        stream.synchronize()
+        api.raise_if_error()
+        got = out.float().cpu().numpy()
+        assert np.isfinite(got).all()
+        assert helpers.rel_err(got, ref) <= helpers.BF16_TOL
+
+
+def test_noalloc_entry_refuses_unaligned_weights(kutacc_lib):
+    # the kernels read the weights with vector loads: a view that starts on an odd element is refused, not launched
+    w = W.random_global_case(seed=35, B=2, S=64)
+    case = runner.DeviceCase(w)
+    out = torch.zeros((w.B, w.S, w.C), dtype=torch.bfloat16, device="cuda:0")
+    shifted = torch.zeros(w.D * w.C + 8, dtype=torch.bfloat16, device="cuda:0")
+    before = api.launch_count()
+    rc = api.lib().kutacc_b200_global_attention_noalloc(
+        case.x.data_ptr(), case.mask.data_ptr(), case.wq.data_ptr(), shifted.data_ptr() + 2, case.wv.data_ptr(),
+        case.wg.data_ptr(), case.bg.data_ptr(), case.wo.data_ptr(), case.bo.data_ptr(), out.data_ptr(), w.C,
+        w.B, w.S, w.H, w.D, C.c_void_p(0))
+    assert rc == -1 and "16-byte aligned" in api.last_error()
+    assert api.launch_count() == before
+    api.clear_error()
 
 
 def test_noalloc_entry_refuses_shapes_beyond_the_static_scratch(kutacc_lib):
