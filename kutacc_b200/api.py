@@ -119,15 +119,16 @@ def lib() -> C.CDLL:
     L.kutacc_af2_linear_weight_prepack.restype = None
     L.kutacc_af2_gemm_pack_get_size.argtypes = [C.c_char, C.c_char, C.c_char, C.c_int, C.c_int, C.c_int]
     L.kutacc_af2_gemm_pack_get_size.restype = C.c_size_t
-    L.kutacc_af2_triangle_multiplication_calc_proj.argtypes = [C.POINTER(TmActInputs), vp, C.POINTER(TmProjWeights), C.c_bool]
-    L.kutacc_af2_triangle_multiplication_calc_proj.restype = None
-    L.kutacc_af2_triangle_multiplication_equation.argtypes = [vp, vp, vp, i64, C.c_bool]
-    L.kutacc_af2_triangle_multiplication_equation.restype = None
-    L.kutacc_af2_triangle_multiplication_gate_and_out_linear.argtypes = [vp, vp, C.POINTER(TmActInputs), vp,
-                                                                         C.POINTER(TmLinearWeights), C.c_bool]
-    L.kutacc_af2_triangle_multiplication_gate_and_out_linear.restype = None
-    L.kutacc_af2_triangle_multiplication_last.argtypes = [vp, vp, i64, i64, i64]
-    L.kutacc_af2_triangle_multiplication_last.restype = None
+    if hasattr(L, "kutacc_af2_triangle_multiplication_calc_proj"):
+        L.kutacc_af2_triangle_multiplication_calc_proj.argtypes = [C.POINTER(TmActInputs), vp, C.POINTER(TmProjWeights), C.c_bool]
+        L.kutacc_af2_triangle_multiplication_calc_proj.restype = None
+        L.kutacc_af2_triangle_multiplication_equation.argtypes = [vp, vp, vp, i64, C.c_bool]
+        L.kutacc_af2_triangle_multiplication_equation.restype = None
+        L.kutacc_af2_triangle_multiplication_gate_and_out_linear.argtypes = [vp, vp, C.POINTER(TmActInputs), vp,
+                                                                             C.POINTER(TmLinearWeights), C.c_bool]
+        L.kutacc_af2_triangle_multiplication_gate_and_out_linear.restype = None
+        L.kutacc_af2_triangle_multiplication_last.argtypes = [vp, vp, i64, i64, i64]
+        L.kutacc_af2_triangle_multiplication_last.restype = None
     L.kutacc_b200_tensor_create.argtypes = [vp, i64, C.POINTER(i64), C.POINTER(i64), C.c_int]
     L.kutacc_b200_tensor_create.restype = vp
     L.kutacc_b200_tensor_destroy.argtypes = [vp]

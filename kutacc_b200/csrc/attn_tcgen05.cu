@@ -348,11 +348,14 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             uint32_t sr[NR][16];
             tmem_ld_32x16(t_lane + S_COL + qtr * 16, sr[0]);
             tmem_ld_32x16(t_lane + S_COL + BN + qtr * 16, sr[1]);
+            // the test of kv_full (pair bias and mask bias of this step have landed; a barrier test costs about a
+            // hundred cycles even when it succeeds at once) runs while the tensor-memory loads are in flight
+            const bool landed = mbar_wait_warp(kv_full(s), (uint32_t)((g / NST) & 1), p.err, 27);
             tmem_ld_wait();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(s_free);
-            if (!mbar_wait_warp(kv_full(s), (uint32_t)((g / NST) & 1), p.err, 27)) return false;
+            if (!landed) return false;
 
             float tmax[NR] = {-INFINITY, -INFINITY};
             // x = bf16(logit)*scale + bias (+ pair bias) for 8 keys of both rows; keeps x in sr and tracks the maxima

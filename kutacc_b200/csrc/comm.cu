@@ -99,17 +99,21 @@ ncclResult_t settle(ncclResult_t r)
     if (r != ncclInProgress || g_comm == nullptr) return r;
     const double limit = env_seconds("KUTACC_COMM_TIMEOUT_S", 120.0);
     const auto t0 = std::chrono::steady_clock::now();
-    for (;;) {
+    for (long polls = 0;; ++polls) {
         ncclResult_t state = ncclSuccess;
         const ncclResult_t q = g_nccl.CommGetAsyncError(g_comm, &state);
         if (q != ncclSuccess) return q;
         if (state != ncclInProgress) return state;
-        if (std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count() > limit) {
-            g_nccl.CommAbort(g_comm);
-            g_comm = nullptr;
-            return ncclSystemError;
+        // an enqueue settles within microseconds: poll without yielding first, sleep only when it takes long
+        if ((polls & 63) == 63) {
+            const double waited = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+            if (waited > limit) {
+                g_nccl.CommAbort(g_comm);
+                g_comm = nullptr;
+                return ncclSystemError;
+            }
+            if (waited > 2e-3) std::this_thread::sleep_for(std::chrono::microseconds(50));
         }
-        std::this_thread::sleep_for(std::chrono::microseconds(50));
     }
 }
 
@@ -370,6 +374,14 @@ void kutacc_af2_all_gather(kutacc_tensor_h data_h, kutacc_tensor_h out_h)
     } else if (dense_dim0 && full % world_size == 0) {
         // every rank's rows are one contiguous slab of out: gather in place
         KUTACC_NCCL(g_nccl.AllGather(d_in.dev, d_out.dev, slot, ncclUint8, g_comm, stream));
+    } else if (dim1 && ds_a == len && os_a == len && full % world_size == 0 && other <= 64) {
+        // sharded on dim 1 with dense strips (the pair bias [H, rows, keys]): for each of the few leading indices
+        // every rank's rows are one contiguous slab of that strip of out: one group of in-place gathers, no copies
+        KUTACC_NCCL(g_nccl.GroupStart());
+        for (int64_t o = 0; o < other; ++o)
+            KUTACC_NCCL(g_nccl.AllGather((const uint8_t *)d_in.dev + o * ds_o, (uint8_t *)d_out.dev + o * os_o,
+                                         (size_t)block * len, ncclUint8, g_comm, stream));
+        KUTACC_NCCL(g_nccl.GroupEnd());
     } else {
         if (!rt.reserve_workspace((size_t)(world_size + 1) * (slot + 256))) return;
         uint8_t *send = (uint8_t *)rt.take_workspace(slot);

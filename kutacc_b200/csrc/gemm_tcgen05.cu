@@ -94,13 +94,19 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr)
 // instruction descriptor: D fp32, A and B bf16, both K-major, N = 128, M = 128
 constexpr uint32_t kInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 
-// 1 / (1 + exp(-g)) of the bf16-rounded g, in fp32
+// 1 / (1 + exp(-g)) of the bf16-rounded g as 0.5 * tanh(g / 2) + 0.5: one MUFU operation (relative error about
+// 2^-11, below the bf16 step of the stored result) instead of an exponential and a division
 __device__ __forceinline__ float sigmoid_of_bf16(float y)
 {
     const float g = round_to_bf16_f32(y);
-    return 1.0f / (1.0f + ex2_approx(-g * 1.4426950408889634f));
+    return fmaf(0.5f, tanh_approx(0.5f * g), 0.5f);
 }
 
+// Compile-time feature sets, so that each use of the kernel carries only the epilogue code it needs
+// (the sigmoid and the transposed staging cost registers that the plain linear layer would spill).
+constexpr int F_SIGMOID = 1, F_TRANSPOSED = 2, F_RELU = 4, F_WBATCH = 8;
+
+template <int FEAT>
 __global__ void __launch_bounds__(THREADS, 2)
 gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p)
 {
@@ -161,7 +167,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p)
                     const uint32_t st = smem + (uint32_t)s * STAGE_BYTES;
                     mbar_arrive_expect_tx(full_bar(s), STAGE_BYTES);
                     tma_load_3d(st, &maps.a, full_bar(s), kc * BK, s0, b);
-                    tma_load_3d(st + SLAB_BYTES, wmap, full_bar(s), kc * BK, n0, p.w_batched ? b : 0);
+                    tma_load_3d(st + SLAB_BYTES, wmap, full_bar(s), kc * BK, n0, (FEAT & F_WBATCH) ? b : 0);
                 }
             }
         }
@@ -218,9 +224,10 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p)
             tc_fence_after();
             const float *bias = p.bias[seg];
             const bool head_layout = (p.head_layout_mask >> seg) & 1;
-            const bool chanmajor = (p.chanmajor_mask >> seg) & 1;
-            const bool transposed = ((p.transposed_mask >> seg) & 1) || chanmajor;
-            const bool sigmoid = (p.sigmoid_mask >> seg) & 1;
+            const bool chanmajor = (FEAT & F_TRANSPOSED) && ((p.chanmajor_mask >> seg) & 1);
+            const bool transposed = (FEAT & F_TRANSPOSED) && (((p.transposed_mask >> seg) & 1) || chanmajor);
+            const bool sigmoid = (FEAT & F_SIGMOID) && ((p.sigmoid_mask >> seg) & 1);
+            const bool relu = (FEAT & F_RELU) && p.relu;
             const CUtensorMap *omap = &maps.out[seg];
             const int row0 = s0 + quad * 32;                  // first row of this warp inside the batch row
             uint32_t r[2][32];
@@ -238,7 +245,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p)
                         const float4 bv = __ldg(reinterpret_cast<const float4 *>(bias + n) + j4);
                         float y0 = __uint_as_float(r[c][4 * j4]) + bv.x, y1 = __uint_as_float(r[c][4 * j4 + 1]) + bv.y;
                         float y2 = __uint_as_float(r[c][4 * j4 + 2]) + bv.z, y3 = __uint_as_float(r[c][4 * j4 + 3]) + bv.w;
-                        if (p.relu) {
+                        if (relu) {
                             y0 = fmaxf(y0, 0.f);
                             y1 = fmaxf(y1, 0.f);
                             y2 = fmaxf(y2, 0.f);
@@ -257,7 +264,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p)
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         float y0 = __uint_as_float(r[c][2 * j]), y1 = __uint_as_float(r[c][2 * j + 1]);
-                        if (p.relu) {
+                        if (relu) {
                             y0 = fmaxf(y0, 0.f);
                             y1 = fmaxf(y1, 0.f);
                         }
@@ -344,18 +351,19 @@ int sm_count()
     return n;
 }
 
+template <int FEAT>
 bool launch(cudaStream_t stream, const GemmMaps &maps, const GemmParams &p, const char *name)
 {
     static bool configured = false;
     if (!configured) {
-        KUTACC_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        KUTACC_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<FEAT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
         configured = true;
     }
     const int s_tiles = (p.S + BM - 1) / BM;
     const int64_t tiles = (int64_t)p.B * s_tiles * ((p.seg_n + BN - 1) / BN) * p.nseg;
     const unsigned grid = (unsigned)std::min<int64_t>(tiles, 2 * std::max(1, sm_count() - runtime().sm_margin));
     KernelTimer timer__(name, stream);
-    gemm_tcgen05_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(maps, p);
+    gemm_tcgen05_kernel<FEAT><<<grid, THREADS, SMEM_BYTES, stream>>>(maps, p);
     count_launch();
     return true;
 }
@@ -406,7 +414,10 @@ bool tcgen05_proj_qkvg_bf16(cudaStream_t stream, const void *x, const void *wq, 
     p.relu = 0;
     p.sigmoid_mask = gate_sigmoid ? 0x8 : 0;
     p.err = ew.device;
-    return launch(stream, maps, p, "proj_qkvg");
+    if (v_transposed)
+        return gate_sigmoid ? launch<F_TRANSPOSED | F_SIGMOID>(stream, maps, p, "proj_qkvg")
+                            : launch<F_TRANSPOSED>(stream, maps, p, "proj_qkvg");
+    return gate_sigmoid ? launch<F_SIGMOID>(stream, maps, p, "proj_qkvg") : launch<0>(stream, maps, p, "proj_qkvg");
 }
 
 bool tcgen05_linear_bias_bf16(cudaStream_t stream, const void *a, const void *w, const float *bias, void *out,
@@ -446,7 +457,7 @@ bool tcgen05_linear_bias_bf16(cudaStream_t stream, const void *a, const void *w,
     p.relu = relu ? 1 : 0;
     p.sigmoid_mask = 0;
     p.err = ew.device;
-    return launch(stream, maps, p, relu ? "linear_bias_relu" : "linear_bias");
+    return relu ? launch<F_RELU>(stream, maps, p, "linear_bias_relu") : launch<0>(stream, maps, p, "linear_bias");
 }
 
 // Two projections of x [B, S, K] with row biases, both stored channel-major: out_i[n, b, s] = x[b, s, :] . w_i[n, :]
@@ -494,7 +505,7 @@ bool tcgen05_proj2_chanmajor_bf16(cudaStream_t stream, const void *x, const void
     p.relu = 0;
     p.sigmoid_mask = 0;
     p.err = ew.device;
-    return launch(stream, maps, p, "tm_proj");
+    return launch<F_TRANSPOSED>(stream, maps, p, "tm_proj");
 }
 
 // Batched product with one right-hand matrix per batch: out[b, m, n] = sum_k a[b, m, k] * w[b, n, k]
@@ -536,7 +547,7 @@ bool tcgen05_batched_nt_bf16(cudaStream_t stream, const void *a, int64_t a_row_s
     p.relu = 0;
     p.sigmoid_mask = 0;
     p.err = ew.device;
-    return launch(stream, maps, p, "tm_equation");
+    return launch<F_WBATCH>(stream, maps, p, "tm_equation");
 }
 
 }  // namespace dev
