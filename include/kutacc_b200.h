@@ -330,6 +330,21 @@ KUTACC_B200_API int kutacc_b200_selftest_wait_timeout(int64_t limit_microseconds
  * kutacc_af2_linear on z viewed [rows*n_k, c_z] followed by the caller's permute. dtype bf16/fp32. */
 KUTACC_B200_API void kutacc_b200_pair_bias(kutacc_tensor_h z, kutacc_tensor_h wb, kutacc_tensor_h nb);
 
+/* LayerNorm fused in front of the two projections of the attention path (no counterpart in the reference, whose
+ * callers run kutacc_af2_layernorm row by row first, include/kutacc.h:334, and pass the normalised tensor on).
+ * Both take the LayerNorm's fp32 gamma and beta (one value per channel, host or device) and eps, and compute what the
+ * unfused sequence computes, up to bf16 rounding: the normalisation is folded into the projection weights and
+ * applied in the projection's epilogue from per-row statistics, so the normalised activations are never stored.
+ *   kutacc_b200_gating_attention_ln : kutacc_af2_gating_attention(LayerNorm(input), ...), bf16
+ *   kutacc_b200_pair_bias_ln        : kutacc_b200_pair_bias(LayerNorm(z), wb, nb), bf16 */
+KUTACC_B200_API void kutacc_b200_gating_attention_ln(kutacc_tensor_h input, kutacc_af2_attention_inputs_t *q_based_ptr,
+                                                     kutacc_tensor_h bias, kutacc_tensor_h nonbatched_bias,
+                                                     kutacc_af2_attention_weights_t *weight_ptr, const float *ln_gamma,
+                                                     const float *ln_beta, float eps, kutacc_tensor_h out,
+                                                     int64_t block_size);
+KUTACC_B200_API void kutacc_b200_pair_bias_ln(kutacc_tensor_h z, const float *ln_gamma, const float *ln_beta, float eps,
+                                              kutacc_tensor_h wb, kutacc_tensor_h nb);
+
 /* The same LayerNorm over every row of a [rows, size] bf16 matrix in one launch (the loop over rows that the
  * reference leaves to its caller). Strides in elements, row_stride and out_row_stride >= size; out may alias
  * data. Host or device pointers. */

@@ -35,6 +35,7 @@ EXPORTS = [
     "kutacc_b200_workspace_bytes", "kutacc_b200_release_workspace", "kutacc_b200_launch_count",
     "kutacc_b200_set_profile", "kutacc_b200_profile_read", "kutacc_b200_comm_unique_id", "kutacc_b200_comm_init_with_id", "kutacc_b200_pair_bias",
     "kutacc_b200_global_attention_noalloc", "kutacc_b200_layernorm_rows", "kutacc_b200_selftest_wait_timeout",
+    "kutacc_b200_gating_attention_ln", "kutacc_b200_pair_bias_ln",
 ]
 EXPORTED_DATA = ["world_size", "rank"]
 
@@ -129,6 +130,12 @@ def lib() -> C.CDLL:
         L.kutacc_af2_triangle_multiplication_gate_and_out_linear.restype = None
         L.kutacc_af2_triangle_multiplication_last.argtypes = [vp, vp, i64, i64, i64]
         L.kutacc_af2_triangle_multiplication_last.restype = None
+    if hasattr(L, "kutacc_b200_gating_attention_ln"):
+        L.kutacc_b200_gating_attention_ln.argtypes = [vp, C.POINTER(AttentionInputs), vp, vp, C.POINTER(AttentionWeights), vp, vp,
+                                                      C.c_float, vp, i64]
+        L.kutacc_b200_gating_attention_ln.restype = None
+        L.kutacc_b200_pair_bias_ln.argtypes = [vp, vp, vp, C.c_float, vp, vp]
+        L.kutacc_b200_pair_bias_ln.restype = None
     L.kutacc_b200_tensor_create.argtypes = [vp, i64, C.POINTER(i64), C.POINTER(i64), C.c_int]
     L.kutacc_b200_tensor_create.restype = vp
     L.kutacc_b200_tensor_destroy.argtypes = [vp]
@@ -335,6 +342,21 @@ def global_attention(q_based: AttentionInputs, q_data, q_mask, weights: Attentio
                      check: bool = True) -> None:
     lib().kutacc_af2_global_attention(C.byref(q_based) if q_based is not None else None, _h(q_data), _h(q_mask),
                                       C.byref(weights) if weights is not None else None, _h(out))
+    if check:
+        raise_if_error()
+
+
+def gating_attention_ln(input, q_based: AttentionInputs, bias, nonbatched_bias, weights: AttentionWeights, gamma_ptr: int,
+                        beta_ptr: int, eps: float, out, block_size: int = 128, check: bool = True) -> None:
+    """kutacc_af2_gating_attention on LayerNorm(input); gamma/beta are raw fp32 pointers (host or device)."""
+    lib().kutacc_b200_gating_attention_ln(_h(input), C.byref(q_based), _h(bias), _h(nonbatched_bias), C.byref(weights),
+                                          C.c_void_p(gamma_ptr), C.c_void_p(beta_ptr), C.c_float(eps), _h(out), int(block_size))
+    if check:
+        raise_if_error()
+
+
+def pair_bias_ln(z, gamma_ptr: int, beta_ptr: int, eps: float, wb, nb, check: bool = True) -> None:
+    lib().kutacc_b200_pair_bias_ln(_h(z), C.c_void_p(gamma_ptr), C.c_void_p(beta_ptr), C.c_float(eps), _h(wb), _h(nb))
     if check:
         raise_if_error()
 

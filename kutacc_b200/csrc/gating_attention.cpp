@@ -13,13 +13,20 @@ namespace kutacc {
 
 namespace {
 bool aligned16(const void *p) { return ((uintptr_t)p & 15u) == 0; }
+
+// LayerNorm applied to `input` before the projections (kutacc_b200_gating_attention_ln): fp32 gamma and beta of
+// nchannels elements, host or device.
+struct LayerNormArgs {
+    const float *gamma, *beta;
+    float eps;
+};
 }  // namespace
 
 static void gating_attention_impl(Tensor &input, int64_t batch, int64_t seq_len, Tensor &bias, Tensor &nonbatched_bias,
                                   const Tensor &query_w, const Tensor &key_w, const Tensor &value_w,
                                   const Tensor &gating_w, const Tensor &gating_b, const Tensor &output_w,
                                   const Tensor &output_b, Tensor &out, int64_t block_size, int64_t head_size,
-                                  int64_t nheads, int64_t nchannels)
+                                  int64_t nheads, int64_t nchannels, const LayerNormArgs *ln = nullptr)
 {
     // same scalar validation, in the same place, as gating_attention.cpp:39-45 and :69
     KUTACC_CHECK(batch > 0 && seq_len > 0 && block_size > 0 && head_size > 0 && nheads > 0 && nchannels > 0 &&
@@ -35,6 +42,7 @@ static void gating_attention_impl(Tensor &input, int64_t batch, int64_t seq_len,
 
     const DType dt = input.dtype();
     KUTACC_CHECK(dt == kBF16 || dt == kFP32, "gating_attention dtype invalid: [", (int)dt, "]");
+    KUTACC_CHECK(ln == nullptr || dt == kBF16, "gating_attention with LayerNorm: bf16 only");
     KUTACC_CHECK(input.data_ptr() && bias.data_ptr() && out.data_ptr() && query_w.data_ptr() && key_w.data_ptr() &&
                      value_w.data_ptr() && gating_w.data_ptr() && gating_b.data_ptr() && output_w.data_ptr() &&
                      output_b.data_ptr(),
@@ -71,11 +79,15 @@ static void gating_attention_impl(Tensor &input, int64_t batch, int64_t seq_len,
     if (has_nb) stage += staged_bytes_needed(nonbatched_bias.data_ptr(), nb_bytes);
     for (const Tensor *w : {&query_w, &key_w, &value_w, &gating_w, &output_w})
         stage += staged_bytes_needed(w->data_ptr(), w_bytes);
+    if (ln) stage += 2 * staged_bytes_needed(ln->gamma, b_bytes);
     if (!rt.reserve_stage(stage)) return;
     const int64_t s_pad8 = (S + 7) / 8 * 8;
     const size_t nb_pad_bytes = has_nb ? (size_t)H * S * s_pad8 * 2 : 0;
     const size_t v_bytes = std::max(x_bytes, (size_t)B * C * s_pad8 * es);   // v may be stored key-major with padded rows
-    if (!rt.reserve_workspace(4 * (x_bytes + 256) + v_bytes + 256 + nb_pad_bytes + 256)) return;
+    // with LayerNorm: row statistics, four folded weights with their s and t, and (for shapes the folded projection does
+    // not cover) a normalised copy of the activations
+    const size_t ln_bytes = ln ? (size_t)M * 8 + 4 * (w_bytes + 256) + 8 * (b_bytes + 256) + x_bytes + 1024 : 0;
+    if (!rt.reserve_workspace(4 * (x_bytes + 256) + v_bytes + 256 + nb_pad_bytes + 256 + ln_bytes)) return;
 
     // When the result lives in host memory, the batch rows (independent problems) are processed in chunks so
     // that the upload of chunk i+1 (when the activations are in host memory too), the kernels of chunk i and
@@ -106,6 +118,19 @@ static void gating_attention_impl(Tensor &input, int64_t batch, int64_t seq_len,
          *wv_ = (char *)rt.take_workspace(v_bytes), *wg_ = (char *)rt.take_workspace(x_bytes),
          *wavg = (char *)rt.take_workspace(x_bytes);
     void *nb_pad = nb_pad_bytes ? rt.take_workspace(nb_pad_bytes) : nullptr;
+    DeviceArg d_lg = ln ? resolve_in(ln->gamma, b_bytes) : DeviceArg{}, d_lb = ln ? resolve_in(ln->beta, b_bytes) : DeviceArg{};
+    char *ln_stats = ln ? (char *)rt.take_workspace((size_t)M * 8) : nullptr;
+    void *ln_w[4] = {nullptr, nullptr, nullptr, nullptr};
+    float *ln_s[4] = {nullptr, nullptr, nullptr, nullptr}, *ln_t[4] = {nullptr, nullptr, nullptr, nullptr};
+    char *x_norm = nullptr;
+    if (ln) {
+        for (int i = 0; i < 4; ++i) {
+            ln_w[i] = rt.take_workspace(w_bytes);
+            ln_s[i] = (float *)rt.take_workspace(b_bytes);
+            ln_t[i] = (float *)rt.take_workspace(b_bytes);
+        }
+        x_norm = (char *)rt.take_workspace(x_bytes);
+    }
     if (kutacc_check_err_set) return;
 
     const float scale = (float)(1 / std::sqrt((double)head_size));  // gating_attention.cpp:68
@@ -131,10 +156,29 @@ static void gating_attention_impl(Tensor &input, int64_t batch, int64_t seq_len,
         nb_sh = S * s_pad8;
     }
 
+    // LayerNorm in front: folded into the tcgen05 projection where that kernel runs (head size 32), otherwise the
+    // rows are normalised into the workspace chunk by chunk and the usual sequence runs on the copy
+    const bool ln_folded = ln && fast && D == 32 && C % 128 == 0;
+    if (ln_folded) {
+        const void *w_in[4] = {d_wq.dev, d_wk.dev, d_wv.dev, d_wg.dev};
+        const float *b_in[4] = {nullptr, nullptr, nullptr, (const float *)d_bg.dev};
+        const bool folded = dev::launch_ln_fold(stream, 4, w_in, b_in, (const float *)d_lg.dev, (const float *)d_lb.dev, ln_w,
+                                                ln_s, ln_t, (int)C, (int)C);
+        KUTACC_CHECK(folded, "gating_attention with LayerNorm: weight folding failed");
+        if (kutacc_check_err_set) return;
+    }
+
     // kernel sequence for batch rows [b0, b0 + nb): every buffer is batch-major, so a chunk is an offset
     auto run_rows = [&](int64_t b0, int64_t nbr) -> bool {
         const size_t row_bytes = (size_t)S * C * es;                       // one batch row of a [B, S, C]-sized buffer
         const char *x_c = (const char *)d_x.dev + b0 * row_bytes;
+        char *st_c = ln ? ln_stats + (size_t)b0 * S * 8 : nullptr;
+        if (ln && !ln_folded) {
+            if (!dev::launch_layernorm_rows(stream, x_c, (const float *)d_lg.dev, (const float *)d_lb.dev, x_norm + b0 * row_bytes,
+                                            nbr * S, C, C, C, ln->eps))
+                return false;
+            x_c = x_norm + b0 * row_bytes;
+        }
         char *q_c = wq_ + b0 * row_bytes, *k_c = wk_ + b0 * row_bytes, *g_c = wg_ + b0 * row_bytes,
              *a_c = wavg + b0 * row_bytes;
         const char *bias_c = (const char *)d_bias.dev + (size_t)b0 * bias_s0 * es;
@@ -148,7 +192,14 @@ static void gating_attention_impl(Tensor &input, int64_t batch, int64_t seq_len,
             char *v_c = wv_ + b0 * row_bytes;                                  // [B, H, S, D]
             bool v_key_major = false;
             ok = false;
-            if (D == 32) {
+            if (ln_folded) {
+                ok = dev::launch_ln_stats(stream, x_c, nbr * S, C, C, ln->eps, st_c) &&
+                     dev::tcgen05_proj_qkvg_bf16(stream, x_c, ln_w[0], ln_w[1], ln_w[2], ln_w[3], nullptr, q_c, k_c, v_km, g_c,
+                                                 (int)nbr, (int)S, (int)H, (int)D, true, s_pad8, /*gate_sigmoid=*/true, st_c,
+                                                 ln_s, ln_t);
+                if (!ok) return false;
+                v_key_major = true;
+            } else if (D == 32) {
                 ok = dev::tcgen05_proj_qkvg_bf16(stream, x_c, d_wq.dev, d_wk.dev, d_wv.dev, d_wg.dev,
                                                  (const float *)d_bg.dev, q_c, k_c, v_km, g_c, (int)nbr, (int)S, (int)H,
                                                  (int)D, true, s_pad8, /*gate_sigmoid=*/true);
@@ -242,30 +293,50 @@ static void gating_attention_impl(Tensor &input, int64_t batch, int64_t seq_len,
 
 }  // namespace kutacc
 
+// The argument checks of the two entry points, expanded inside each of them so that a failed check names the
+// entry point the caller used (the reference prints __func__: src/utils/check.h:38-45).
+#define KUTACC_GATING_ENTRY(ln_ptr) \
+ /* handle / struct nulls first (gating_attention.cpp:165-170) ... */ \
+    KUTACC_CHECK(input != nullptr && q_based_ptr != nullptr && bias != nullptr && nonbatched_bias != nullptr && \
+                     weight_ptr != nullptr && out != nullptr, \
+                 "kutacc_af2_gating_attention: input args nullptr error"); \
+    if (kutacc_check_err_set) return; \
+ /* ... then the scalars, before any handle is dereferenced: the reference's robustness tests */ \
+ /* pass pointers to stack floats as handles together with one bad integer. */ \
+    const int64_t batch = q_based_ptr->batch, seq_len = q_based_ptr->seq_len; \
+    const int64_t head_size = weight_ptr->head_size, nheads = weight_ptr->nheads, nchannels = weight_ptr->nchannels; \
+    KUTACC_CHECK(batch > 0 && seq_len > 0 && block_size > 0 && head_size > 0 && nheads > 0 && nchannels > 0, \
+                 "input param <= 0 or overflow"); \
+    KUTACC_CHECK(weight_ptr->query_w && weight_ptr->key_w && weight_ptr->value_w && weight_ptr->gating_w && \
+                     weight_ptr->gating_b && weight_ptr->output_w && weight_ptr->output_b, \
+                 "kutacc_af2_gating_attention: weight handle nullptr error"); \
+    if (kutacc_check_err_set) return; \
+    gating_attention_impl(*as_tensor(input), batch, seq_len, *as_tensor(bias), *as_tensor(nonbatched_bias), \
+                          *as_tensor(weight_ptr->query_w), *as_tensor(weight_ptr->key_w), \
+                          *as_tensor(weight_ptr->value_w), *as_tensor(weight_ptr->gating_w), \
+                          *as_tensor(weight_ptr->gating_b), *as_tensor(weight_ptr->output_w), \
+                          *as_tensor(weight_ptr->output_b), *as_tensor(out), block_size, head_size, nheads, nchannels, ln_ptr);
+
 extern "C" void kutacc_af2_gating_attention(kutacc_tensor_h input, kutacc_af2_attention_inputs_t *q_based_ptr,
                                             kutacc_tensor_h bias, kutacc_tensor_h nonbatched_bias,
                                             kutacc_af2_attention_weights_t *weight_ptr, kutacc_tensor_h out,
                                             int64_t block_size)
 {
     using namespace kutacc;
-    // handle / struct nulls first (gating_attention.cpp:165-170) ...
-    KUTACC_CHECK(input != nullptr && q_based_ptr != nullptr && bias != nullptr && nonbatched_bias != nullptr &&
-                     weight_ptr != nullptr && out != nullptr,
-                 "kutacc_af2_gating_attention: input args nullptr error");
+    KUTACC_GATING_ENTRY(nullptr)
+}
+
+// kutacc_af2_gating_attention applied to LayerNorm(input): same arguments plus the LayerNorm's fp32 gamma and beta
+// (nchannels elements each, host or device) and eps. For head size 32 the normalisation is folded into the
+// projection kernel: the normalised activations are never written to memory.
+extern "C" void kutacc_b200_gating_attention_ln(kutacc_tensor_h input, kutacc_af2_attention_inputs_t *q_based_ptr,
+                                                kutacc_tensor_h bias, kutacc_tensor_h nonbatched_bias,
+                                                kutacc_af2_attention_weights_t *weight_ptr, const float *ln_gamma,
+                                                const float *ln_beta, float eps, kutacc_tensor_h out, int64_t block_size)
+{
+    using namespace kutacc;
+    KUTACC_CHECK(ln_gamma != nullptr && ln_beta != nullptr && eps >= 0.f, "kutacc_b200_gating_attention_ln: LayerNorm arguments invalid");
     if (kutacc_check_err_set) return;
-    // ... then the scalars, before any handle is dereferenced: the reference's robustness tests
-    // pass pointers to stack floats as handles together with one bad integer.
-    const int64_t batch = q_based_ptr->batch, seq_len = q_based_ptr->seq_len;
-    const int64_t head_size = weight_ptr->head_size, nheads = weight_ptr->nheads, nchannels = weight_ptr->nchannels;
-    KUTACC_CHECK(batch > 0 && seq_len > 0 && block_size > 0 && head_size > 0 && nheads > 0 && nchannels > 0,
-                 "input param <= 0 or overflow");
-    KUTACC_CHECK(weight_ptr->query_w && weight_ptr->key_w && weight_ptr->value_w && weight_ptr->gating_w &&
-                     weight_ptr->gating_b && weight_ptr->output_w && weight_ptr->output_b,
-                 "kutacc_af2_gating_attention: weight handle nullptr error");
-    if (kutacc_check_err_set) return;
-    gating_attention_impl(*as_tensor(input), batch, seq_len, *as_tensor(bias), *as_tensor(nonbatched_bias),
-                          *as_tensor(weight_ptr->query_w), *as_tensor(weight_ptr->key_w),
-                          *as_tensor(weight_ptr->value_w), *as_tensor(weight_ptr->gating_w),
-                          *as_tensor(weight_ptr->gating_b), *as_tensor(weight_ptr->output_w),
-                          *as_tensor(weight_ptr->output_b), *as_tensor(out), block_size, head_size, nheads, nchannels);
+    const LayerNormArgs ln{ln_gamma, ln_beta, eps};
+    KUTACC_GATING_ENTRY(&ln)
 }

@@ -73,6 +73,8 @@ struct GemmParams {
     int K;
     int S, B;
     int relu;               // non-zero: max(0, .) after the bias, before the bf16 rounding
+    const float2 *ln_stats; // F_LN: (mean, rstd) of every row of X, [B * S]
+    const float *ln_s[4];   // F_LN: rounding residue of the folded weight rows, per segment
     int sigmoid_mask;       // bit i set: segment i stores bf16(sigmoid(bf16(y))) (the gate of the attention, whose
                             // reference rounds the gate to bf16 before the sigmoid: gating_attention.cpp:62-66,134-147)
     int *err;
@@ -104,7 +106,7 @@ __device__ __forceinline__ float sigmoid_of_bf16(float y)
 
 // Compile-time feature sets, so that each use of the kernel carries only the epilogue code it needs
 // (the sigmoid and the transposed staging cost registers that the plain linear layer would spill).
-constexpr int F_SIGMOID = 1, F_TRANSPOSED = 2, F_RELU = 4, F_WBATCH = 8;
+constexpr int F_SIGMOID = 1, F_TRANSPOSED = 2, F_RELU = 4, F_WBATCH = 8, F_LN = 16;
 
 template <int FEAT>
 __global__ void __launch_bounds__(THREADS, 2)
@@ -230,6 +232,14 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p)
             const bool relu = (FEAT & F_RELU) && p.relu;
             const CUtensorMap *omap = &maps.out[seg];
             const int row0 = s0 + quad * 32;                  // first row of this warp inside the batch row
+            // LayerNorm-folded projection: y = rstd * (acc - mean * s[n]) + t[n] with this thread's row statistics
+            float ln_a = 1.f, ln_b = 0.f;
+            if (FEAT & F_LN) {
+                const int rr = row0 + lane < p.S ? row0 + lane : p.S - 1;
+                const float2 st = __ldg(p.ln_stats + (int64_t)b * p.S + rr);
+                ln_a = st.y;
+                ln_b = -st.y * st.x;
+            }
             uint32_t r[2][32];
             const uint32_t tcol = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(a * BN + half * 64);
             tmem_ld_32x32(tcol, r[0]);
@@ -243,8 +253,19 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p)
 #pragma unroll
                     for (int j4 = 0; j4 < 8; ++j4) {
                         const float4 bv = __ldg(reinterpret_cast<const float4 *>(bias + n) + j4);
-                        float y0 = __uint_as_float(r[c][4 * j4]) + bv.x, y1 = __uint_as_float(r[c][4 * j4 + 1]) + bv.y;
-                        float y2 = __uint_as_float(r[c][4 * j4 + 2]) + bv.z, y3 = __uint_as_float(r[c][4 * j4 + 3]) + bv.w;
+                        float y0, y1, y2, y3;
+                        if (FEAT & F_LN) {
+                            const float4 sv = __ldg(reinterpret_cast<const float4 *>(p.ln_s[seg] + n) + j4);
+                            y0 = fmaf(ln_a, __uint_as_float(r[c][4 * j4]), fmaf(ln_b, sv.x, bv.x));
+                            y1 = fmaf(ln_a, __uint_as_float(r[c][4 * j4 + 1]), fmaf(ln_b, sv.y, bv.y));
+                            y2 = fmaf(ln_a, __uint_as_float(r[c][4 * j4 + 2]), fmaf(ln_b, sv.z, bv.z));
+                            y3 = fmaf(ln_a, __uint_as_float(r[c][4 * j4 + 3]), fmaf(ln_b, sv.w, bv.w));
+                        } else {
+                            y0 = __uint_as_float(r[c][4 * j4]) + bv.x;
+                            y1 = __uint_as_float(r[c][4 * j4 + 1]) + bv.y;
+                            y2 = __uint_as_float(r[c][4 * j4 + 2]) + bv.z;
+                            y3 = __uint_as_float(r[c][4 * j4 + 3]) + bv.w;
+                        }
                         if (relu) {
                             y0 = fmaxf(y0, 0.f);
                             y1 = fmaxf(y1, 0.f);
@@ -372,7 +393,8 @@ bool launch(cudaStream_t stream, const GemmMaps &maps, const GemmParams &p, cons
 
 bool tcgen05_proj_qkvg_bf16(cudaStream_t stream, const void *x, const void *wq, const void *wk, const void *wv,
                             const void *wg, const float *bg, void *q, void *k, void *v, void *gate, int B, int S,
-                            int H, int D, bool v_transposed, int64_t v_pitch, bool gate_sigmoid)
+                            int H, int D, bool v_transposed, int64_t v_pitch, bool gate_sigmoid, const void *ln_stats,
+                            const float *const *ln_s, const float *const *ln_t)
 {
     const int C = H * D;
     if (C % 128 != 0 || (D != 32 && D != 64) || C > 256 * 64 || ((uintptr_t)bg & 15u)) return false;
@@ -400,6 +422,12 @@ bool tcgen05_proj_qkvg_bf16(cudaStream_t stream, const void *x, const void *wq, 
     GemmParams p;
     p.bias[0] = p.bias[1] = p.bias[2] = nullptr;
     p.bias[3] = bg;
+    p.ln_stats = (const float2 *)ln_stats;
+    for (int i = 0; i < 4; ++i) {
+        p.ln_s[i] = ln_stats ? ln_s[i] : nullptr;
+        if (ln_stats) p.bias[i] = ln_t[i];
+        if (ln_stats && ((((uintptr_t)ln_s[i] | (uintptr_t)ln_t[i]) & 15u) != 0)) return false;
+    }
     p.seg_n = C;
     p.nseg = 4;
     p.head_dim = D;
@@ -414,6 +442,8 @@ bool tcgen05_proj_qkvg_bf16(cudaStream_t stream, const void *x, const void *wq, 
     p.relu = 0;
     p.sigmoid_mask = gate_sigmoid ? 0x8 : 0;
     p.err = ew.device;
+    if (ln_stats)
+        return v_transposed && gate_sigmoid ? launch<F_TRANSPOSED | F_SIGMOID | F_LN>(stream, maps, p, "proj_qkvg_ln") : false;
     if (v_transposed)
         return gate_sigmoid ? launch<F_TRANSPOSED | F_SIGMOID>(stream, maps, p, "proj_qkvg")
                             : launch<F_TRANSPOSED>(stream, maps, p, "proj_qkvg");
@@ -455,6 +485,8 @@ bool tcgen05_linear_bias_bf16(cudaStream_t stream, const void *a, const void *w,
     p.S = S;
     p.B = B;
     p.relu = relu ? 1 : 0;
+    p.ln_stats = nullptr;
+    p.ln_s[0] = p.ln_s[1] = p.ln_s[2] = p.ln_s[3] = nullptr;
     p.sigmoid_mask = 0;
     p.err = ew.device;
     return relu ? launch<F_RELU>(stream, maps, p, "linear_bias_relu") : launch<0>(stream, maps, p, "linear_bias");
@@ -503,6 +535,8 @@ bool tcgen05_proj2_chanmajor_bf16(cudaStream_t stream, const void *x, const void
     p.S = S;
     p.B = B;
     p.relu = 0;
+    p.ln_stats = nullptr;
+    p.ln_s[0] = p.ln_s[1] = p.ln_s[2] = p.ln_s[3] = nullptr;
     p.sigmoid_mask = 0;
     p.err = ew.device;
     return launch<F_TRANSPOSED>(stream, maps, p, "tm_proj");
@@ -545,6 +579,8 @@ bool tcgen05_batched_nt_bf16(cudaStream_t stream, const void *a, int64_t a_row_s
     p.S = M;
     p.B = B;
     p.relu = 0;
+    p.ln_stats = nullptr;
+    p.ln_s[0] = p.ln_s[1] = p.ln_s[2] = p.ln_s[3] = nullptr;
     p.sigmoid_mask = 0;
     p.err = ew.device;
     return launch<F_WBATCH>(stream, maps, p, "tm_equation");

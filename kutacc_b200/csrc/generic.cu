@@ -390,11 +390,13 @@ __global__ void __launch_bounds__(256) pair_bias_vec_kernel(const __nv_bfloat16 
 // bf16 pair bias on tensor cores: a CTA streams 128-position tiles of z through a cp.async ring (16-byte
 // chunks, swizzled by row), each warp multiplies its 16 positions by Wb^T (heads padded to 8) with
 // mma.sync m16n8k16 and writes nb[h, pos]. Bandwidth bound: z is read once, 128-bit loads.
-template <int CZ>
+// With LN the weights are LayerNorm-folded (ln_fold.cu) and a position's result is rstd * (acc - mean * s[h]) + t[h].
+template <int CZ, bool LN>
 __global__ void __launch_bounds__(256) pair_bias_mma_kernel(const __nv_bfloat16 *__restrict__ z,
                                                             const __nv_bfloat16 *__restrict__ wb,
                                                             __nv_bfloat16 *__restrict__ nb, int64_t nb_head_stride,
-                                                            int64_t total, int H)
+                                                            int64_t total, int H, const float2 *__restrict__ stats,
+                                                            const float *__restrict__ ln_s, const float *__restrict__ ln_t)
 {
     constexpr int ROWB = CZ * 2, CHUNKS = ROWB / 16, TP = 128, STAGES = 3, STAGE_BYTES = TP * ROWB;
     extern __shared__ __align__(128) unsigned char pb_smem[];
@@ -437,6 +439,15 @@ __global__ void __launch_bounds__(256) pair_bias_mma_kernel(const __nv_bfloat16 
         }
         const int64_t p0 = tile * TP + warp * 16 + g, p1 = p0 + 8;
         const int h0 = 2 * t, h1 = 2 * t + 1;
+        if (LN) {
+            const float s0 = h0 < H ? ln_s[h0] : 0.f, s1 = h1 < H ? ln_s[h1] : 0.f;
+            const float t0 = h0 < H ? ln_t[h0] : 0.f, t1 = h1 < H ? ln_t[h1] : 0.f;
+            const float2 st0 = stats[p0 < total ? p0 : 0], st1 = stats[p1 < total ? p1 : 0];
+            acc[0] = fmaf(st0.y, acc[0] - st0.x * s0, t0);
+            acc[1] = fmaf(st0.y, acc[1] - st0.x * s1, t1);
+            acc[2] = fmaf(st1.y, acc[2] - st1.x * s0, t0);
+            acc[3] = fmaf(st1.y, acc[3] - st1.x * s1, t1);
+        }
         if (p0 < total) {
             if (h0 < H) nb[h0 * nb_head_stride + p0] = __float2bfloat16_rn(acc[0]);
             if (h1 < H) nb[h1 * nb_head_stride + p0] = __float2bfloat16_rn(acc[1]);
@@ -449,14 +460,15 @@ __global__ void __launch_bounds__(256) pair_bias_mma_kernel(const __nv_bfloat16 
     cp_async_wait<0>();
 }
 
-template <int CZ>
+template <int CZ, bool LN = false>
 bool launch_pair_bias_mma(cudaStream_t stream, const void *z, const void *wb, void *nb, int64_t nb_head_stride,
-                          int64_t total, int H)
+                          int64_t total, int H, const void *stats = nullptr, const float *ln_s = nullptr,
+                          const float *ln_t = nullptr)
 {
     constexpr int SMEM = 3 * 128 * CZ * 2;
     static bool configured = false;
     if (!configured) {
-        if (cudaFuncSetAttribute(pair_bias_mma_kernel<CZ>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) {
+        if (cudaFuncSetAttribute(pair_bias_mma_kernel<CZ, LN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) {
             cudaGetLastError();
             return false;
         }
@@ -464,8 +476,9 @@ bool launch_pair_bias_mma(cudaStream_t stream, const void *z, const void *wb, vo
     }
     const int64_t ntiles = (total + 127) / 128;
     const unsigned grid = (unsigned)std::min<int64_t>(ntiles, 148 * 2);
-    pair_bias_mma_kernel<CZ><<<grid, 256, SMEM, stream>>>((const __nv_bfloat16 *)z, (const __nv_bfloat16 *)wb,
-                                                          (__nv_bfloat16 *)nb, nb_head_stride, total, H);
+    pair_bias_mma_kernel<CZ, LN><<<grid, 256, SMEM, stream>>>((const __nv_bfloat16 *)z, (const __nv_bfloat16 *)wb,
+                                                              (__nv_bfloat16 *)nb, nb_head_stride, total, H,
+                                                              (const float2 *)stats, ln_s, ln_t);
     return true;
 }
 
@@ -554,6 +567,17 @@ bool launch_attn_generic(cudaStream_t stream, ElemType t, const void *q, const v
                                             avg, B, S, H, D, scale);
     return launch_attn_generic_t<__nv_bfloat16>(stream, q, k, v, gate, bias, bias_stride0, nb, nb_stride_h,
                                                 nb_stride_q, avg, B, S, H, D, scale);
+}
+
+bool launch_pair_bias_ln(cudaStream_t stream, const void *z, const void *wb_folded, const void *stats, const float *ln_s,
+                         const float *ln_t, void *nb, int64_t nb_head_stride, int64_t R, int64_t Nk, int Cz, int H)
+{
+    if (H > 8 || (Cz != 128 && Cz != 64) || ((uintptr_t)z % 16) != 0 || ((uintptr_t)wb_folded % 4) != 0) return false;
+    KernelTimer timer__("pair_bias_ln", stream);
+    const bool ok = Cz == 128 ? launch_pair_bias_mma<128, true>(stream, z, wb_folded, nb, nb_head_stride, R * Nk, H, stats, ln_s, ln_t)
+                              : launch_pair_bias_mma<64, true>(stream, z, wb_folded, nb, nb_head_stride, R * Nk, H, stats, ln_s, ln_t);
+    if (ok) count_launch();
+    return ok;
 }
 
 bool launch_pair_bias(cudaStream_t stream, ElemType t, const void *z, const void *wb, void *nb,

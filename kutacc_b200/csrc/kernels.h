@@ -28,9 +28,13 @@ bool launch_linear_bias_bf16(cudaStream_t stream, const void *a, int64_t lda, co
 // [B, H, D, S] with row pitch v_pitch (what the tcgen05 attention core consumes) instead of [B, H, S, D].
 // Return false when the shape is not covered.
 // With gate_sigmoid the gate segment stores bf16(sigmoid(bf16(x.Wg + bg))) instead of bf16(x.Wg + bg).
+// With ln_stats (float2 mean/rstd per row of x) the four weights are LayerNorm-folded ones (launch_ln_fold) and the
+// epilogue applies y = rstd * (acc - mean * ln_s[seg][n]) + ln_t[seg][n] (ln_t carries the gate bias; bg is ignored).
 bool tcgen05_proj_qkvg_bf16(cudaStream_t stream, const void *x, const void *wq, const void *wk, const void *wv,
                             const void *wg, const float *bg, void *q, void *k, void *v, void *gate, int B, int S,
-                            int H, int D, bool v_transposed, int64_t v_pitch, bool gate_sigmoid = false);
+                            int H, int D, bool v_transposed, int64_t v_pitch, bool gate_sigmoid = false,
+                            const void *ln_stats = nullptr, const float *const *ln_s = nullptr,
+                            const float *const *ln_t = nullptr);
 // a_row_stride (elements, 0 = K): row stride of a, whose batch rows are S rows apart.
 bool tcgen05_linear_bias_bf16(cudaStream_t stream, const void *a, const void *w, const float *bias, void *out,
                               int64_t out_row_stride, int B, int S, int N, int K, bool relu = false,
@@ -98,6 +102,10 @@ bool launch_attn_generic(cudaStream_t stream, ElemType t, const void *q, const v
 // (head_stride = R*Nk, pos_stride = 1) writes [H, R, Nk]; (1, H) writes [R*Nk, H]. H <= 16.
 bool launch_pair_bias(cudaStream_t stream, ElemType t, const void *z, const void *wb, void *nb,
                       int64_t nb_head_stride, int64_t pos_stride, int64_t R, int64_t Nk, int Cz, int H);
+// The same projection of LayerNorm(z) with folded weights (launch_ln_fold) and per-position statistics: only the
+// tensor-core kernel (bf16, c_z 64 or 128, up to 8 heads, [H, R, Nk] output); false otherwise.
+bool launch_pair_bias_ln(cudaStream_t stream, const void *z, const void *wb_folded, const void *stats, const float *ln_s,
+                         const float *ln_t, void *nb, int64_t nb_head_stride, int64_t R, int64_t Nk, int Cz, int H);
 
 // ---- global attention (bf16, C = 64) ---------------------------------------------------------------
 // scratch: qk [B, H, 64] fp32-sized slots and wa [B, 64]; see global_attention.cu
@@ -105,6 +113,13 @@ bool launch_pair_bias(cudaStream_t stream, ElemType t, const void *z, const void
 bool launch_attn_f32(cudaStream_t stream, const void *q, const void *k, const void *v, const void *gate, const void *bias,
                      int64_t bias_stride0, const void *nb, int64_t nb_stride_h, int64_t nb_stride_q, void *avg, int B,
                      int S, int H, int D, float scale);
+
+// LayerNorm folded into the projection that follows (ln_fold.cu): per-row (mean, rstd) pairs as float2, and
+// for up to four [N, K] weight matrices the folded, centred bf16 weights with the epilogue terms s and t
+// (y = rstd * (acc - mean * s[n]) + t[n]).
+bool launch_ln_stats(cudaStream_t stream, const void *x, int64_t rows, int64_t size, int64_t x_stride, float eps, void *stats);
+bool launch_ln_fold(cudaStream_t stream, int nmat, const void *const *w, const float *const *bias, const float *gamma,
+                    const float *beta, void *const *w2, float *const *s, float *const *t, int N, int K);
 
 // LayerNorm of every row of a [rows, size] bf16 matrix (strides in elements); fp32 gamma and beta.
 bool launch_layernorm_rows(cudaStream_t stream, const void *x, const float *gamma, const float *beta, void *out,

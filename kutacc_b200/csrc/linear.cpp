@@ -143,3 +143,59 @@ extern "C" void kutacc_b200_pair_bias(kutacc_tensor_h z_h, kutacc_tensor_h wb_h,
     finish_out(d_n);
     end_of_call();
 }
+
+// Pair bias of LayerNorm(z): nb[h, r, k] = LayerNorm(z[r, k, :]) . wb[h, :]. The normalisation is folded into the
+// projection (one read of z for the row statistics, one for the product; the normalised tensor is never written).
+// Shapes the folded tensor-core kernel does not cover normalise into the workspace first.
+extern "C" void kutacc_b200_pair_bias_ln(kutacc_tensor_h z_h, const float *ln_gamma, const float *ln_beta, float eps,
+                                         kutacc_tensor_h wb_h, kutacc_tensor_h nb_h)
+{
+    using namespace kutacc;
+    KUTACC_CHECK(z_h != nullptr && wb_h != nullptr && nb_h != nullptr && ln_gamma != nullptr && ln_beta != nullptr,
+                 "kutacc_b200_pair_bias_ln: nullptr error");
+    if (kutacc_check_err_set) return;
+    Tensor &z = *as_tensor(z_h), &wb = *as_tensor(wb_h), &nb = *as_tensor(nb_h);
+    KUTACC_CHECK(z.dim() == 3 && wb.dim() == 2 && nb.dim() == 3 && z.data_ptr() && wb.data_ptr() && nb.data_ptr(),
+                 "kutacc_b200_pair_bias_ln: z [rows, keys, c_z], wb [nheads, c_z], nb [nheads, rows, keys] expected");
+    if (kutacc_check_err_set) return;
+    const int64_t R = z.sizes()[0], Nk = z.sizes()[1], Cz = z.sizes()[2], H = wb.sizes()[0];
+    KUTACC_CHECK(z.dtype() == kBF16 && wb.sizes()[1] == Cz && nb.sizes()[0] == H && nb.sizes()[1] == R && nb.sizes()[2] == Nk &&
+                     z.strides()[2] == 1 && z.strides()[1] == Cz && z.strides()[0] == Nk * Cz && nb.strides()[2] == 1 &&
+                     nb.strides()[1] == Nk && wb.strides()[1] == 1 && wb.strides()[0] == Cz && R > 0 && Nk > 0 && Cz > 0 &&
+                     H > 0 && H <= 16 && Cz <= 4096 && eps >= 0.f,
+                 "kutacc_b200_pair_bias_ln: shape/stride invalid (bf16 only)");
+    if (kutacc_check_err_set) return;
+    const int64_t hs = nb.strides()[0], P = R * Nk;
+    const size_t z_bytes = (size_t)P * Cz * 2, w_bytes = (size_t)H * Cz * 2, nb_bytes = (size_t)((H - 1) * hs + P) * 2,
+                 g_bytes = (size_t)Cz * 4;
+    Runtime &rt = runtime();
+    cudaStream_t stream = (cudaStream_t)rt.stream;
+    if (!rt.reserve_stage(staged_bytes_needed(z.data_ptr(), z_bytes) + staged_bytes_needed(wb.data_ptr(), w_bytes) +
+                          staged_bytes_needed(nb.data_ptr(), nb_bytes) + 2 * staged_bytes_needed(ln_gamma, g_bytes)))
+        return;
+    // workspace: statistics, folded weights with s and t, and room for the normalised copy of the fallback
+    if (!rt.reserve_workspace((size_t)P * 8 + w_bytes + 2 * (size_t)H * 4 + z_bytes + 4 * 256)) return;
+    DeviceArg d_z = resolve_in(z.data_ptr(), z_bytes), d_w = resolve_in(wb.data_ptr(), w_bytes),
+              d_g = resolve_in(ln_gamma, g_bytes), d_b = resolve_in(ln_beta, g_bytes), d_n = resolve_out(nb.data_ptr(), nb_bytes);
+    void *stats = rt.take_workspace((size_t)P * 8), *w2 = rt.take_workspace(w_bytes);
+    float *s = (float *)rt.take_workspace((size_t)H * 4), *t = (float *)rt.take_workspace((size_t)H * 4);
+    if (kutacc_check_err_set) return;
+    const void *w_in[1] = {d_w.dev};
+    const float *no_bias[1] = {nullptr};
+    void *w_out[1] = {w2};
+    float *s_out[1] = {s}, *t_out[1] = {t};
+    bool ok = H <= 8 && (Cz == 128 || Cz == 64) && ((uintptr_t)d_z.dev % 16) == 0 &&
+              dev::launch_ln_stats(stream, d_z.dev, P, Cz, Cz, eps, stats) &&
+              dev::launch_ln_fold(stream, 1, w_in, no_bias, (const float *)d_g.dev, (const float *)d_b.dev, w_out, s_out, t_out,
+                                  (int)H, (int)Cz) &&
+              dev::launch_pair_bias_ln(stream, d_z.dev, w2, stats, s, t, d_n.dev, hs, R, Nk, (int)Cz, (int)H);
+    if (!ok && !kutacc_check_err_set) {
+        void *zn = rt.take_workspace(z_bytes);
+        ok = zn != nullptr &&
+             dev::launch_layernorm_rows(stream, d_z.dev, (const float *)d_g.dev, (const float *)d_b.dev, zn, P, Cz, Cz, Cz, eps) &&
+             dev::launch_pair_bias(stream, dev::kElemBF16, zn, d_w.dev, d_n.dev, hs, 1, R, Nk, (int)Cz, (int)H);
+    }
+    KUTACC_CHECK(ok, "kutacc_b200_pair_bias_ln: no device kernel for nheads=", H, " c_z=", Cz);
+    finish_out(d_n);
+    end_of_call();
+}
