@@ -408,6 +408,84 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                              : "memory");
             };
 
+            // The same two steps for 8 keys of BOTH rows, written stage by stage over the 8 independent key pairs (all
+            // loads, all roundings, all scale-and-bias, ... all exponentials, all packs) instead of pair by pair: the
+            // instruction stream of a warp then has eight independent chains in flight at every point, which is what
+            // hides the arithmetic and MUFU latencies at four softmax warps per scheduler.
+            auto xp_chunk = [&](const int c) {
+                uint32_t nbw[4] = {0, 0, 0, 0};
+                if (HAS_NB)
+                    asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];\n"
+                                 : "=r"(nbw[0]), "=r"(nbw[1]), "=r"(nbw[2]), "=r"(nbw[3])
+                                 : "r"(nb_addr[c] + soff));
+                float4 mbq[NR][2];
+#pragma unroll
+                for (int r = 0; r < NR; ++r) {
+                    const uint32_t ma = mb_addr + soff + r * (BN * 4) + c * 32;
+                    mbq[r][0] = lds128_f32(ma);
+                    mbq[r][1] = lds128_f32(ma + 16);
+                }
+                float lr[NR][8];
+#pragma unroll
+                for (int r = 0; r < NR; ++r)
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) lr[r][i] = round_to_bf16_f32(__uint_as_float(sr[r][c * 8 + i]));
+                uint64_t x2[NR][4];
+#pragma unroll
+                for (int r = 0; r < NR; ++r) {
+                    const float mbv[8] = {mbq[r][0].x, mbq[r][0].y, mbq[r][0].z, mbq[r][0].w,
+                                          mbq[r][1].x, mbq[r][1].y, mbq[r][1].z, mbq[r][1].w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        x2[r][j] = fma_f32x2(pack_f32x2(lr[r][2 * j], lr[r][2 * j + 1]), scale2, pack_f32x2(mbv[2 * j], mbv[2 * j + 1]));
+                }
+                if (HAS_NB) {
+                    uint64_t nb2[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) nb2[j] = pack_f32x2(bf16lo_to_f32(nbw[j]), bf16hi_to_f32(nbw[j]));
+#pragma unroll
+                    for (int r = 0; r < NR; ++r)
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) x2[r][j] = add_f32x2(x2[r][j], nb2[j]);
+                }
+                uint64_t t2[NR][4];
+#pragma unroll
+                for (int r = 0; r < NR; ++r) {
+                    const uint64_t mneg2 = pack_f32x2(-m2[r], -m2[r]);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) t2[r][j] = fma_f32x2(x2[r][j], log2e2, mneg2);
+                }
+#pragma unroll
+                for (int r = 0; r < NR; ++r)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        float x0, x1;
+                        unpack_f32x2(x2[r][j], x0, x1);
+                        sr[r][c * 8 + 2 * j] = __float_as_uint(x0);          // kept for the rare redo against a new max
+                        sr[r][c * 8 + 2 * j + 1] = __float_as_uint(x1);
+                        tmax[r] = fmax3(tmax[r], x0, x1);
+                    }
+                float e[NR][8];
+#pragma unroll
+                for (int r = 0; r < NR; ++r)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        float a, b;
+                        unpack_f32x2(t2[r][j], a, b);
+                        e[r][2 * j] = ex2_approx(a);
+                        e[r][2 * j + 1] = ex2_approx(b);
+                    }
+#pragma unroll
+                for (int r = 0; r < NR; ++r) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) w[j] = pack_bf16x2(e[r][2 * j], e[r][2 * j + 1]);
+                    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};\n" ::"r"(nb_addr[c] + soff + (r ? (uint32_t)(OFF_P1 - OFF_NB) : 0u)),
+                                 "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3])
+                                 : "memory");
+                }
+            };
+
             if (kt == 0) {
                 // first step of an item: the maxima must be known before any probability is formed
 #pragma unroll
@@ -424,11 +502,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 // so that the exp (XU pipe) of one chunk overlaps the arithmetic of the next; a running max
                 // may be stale by up to 2^8, which cancels in the final division
 #pragma unroll
-                for (int c = 0; c < 2; ++c) {
-                    x_chunk(c);
-#pragma unroll
-                    for (int r = 0; r < NR; ++r) p_chunk(c, r, -m2[r]);
-                }
+                for (int c = 0; c < 2; ++c) xp_chunk(c);
                 bool grow[NR];
                 float t2[NR];
 #pragma unroll
