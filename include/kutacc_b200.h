@@ -304,7 +304,8 @@ KUTACC_B200_API void kutacc_b200_comm_init_with_id(int64_t world_size_, int64_t 
  * cudaMalloc/cudaFree, a process under a fixed memory quota). It has no counterpart in the reference.
  * Same arithmetic as kutacc_af2_global_attention; every pointer is a device pointer owned by the caller
  * (q_data [batch, seq_len, 64] bf16 contiguous, q_mask [batch, seq_len] bf16, weights as for the operator
- * above, biases fp32, out [batch, seq_len, 64] bf16 with row stride out_row_stride elements); work is
+ * above, biases fp32, out [batch, seq_len, 64] bf16 with row stride out_row_stride elements; q_data, out and the
+ * five weights 16-byte aligned, or the call is refused); work is
  * enqueued on cuda_stream and the call returns without synchronising. Its scratch is a 4 MiB array
  * inside the library image, resident on every GPU that loads the library until the process exits;
  * shapes that need more (batch * row-splits beyond about 7000) are refused with an error. The first

@@ -257,6 +257,12 @@ static void init_common(int64_t nranks, int64_t me, int64_t bufsz, const ncclUni
     }
     ncclConfig_t config = NCCL_CONFIG_INITIALIZER;
     config.blocking = 0;
+    // KUTACC_NCCL_MAX_CTAS bounds the CTAs a collective of this communicator launches. The persistent kernels fill
+    // every SM with one CTA each; a collective that runs beside them takes whole SMs away, and the CTAs that find no
+    // SM start late and finish late. With the collective bounded to n CTAs and kutacc_b200_set_sm_margin(n) the
+    // kernels size their grids to the SMs that are left.
+    const int max_ctas = (int)env_seconds("KUTACC_NCCL_MAX_CTAS", 0.0);
+    if (max_ctas > 0) config.maxCTAs = max_ctas;
     const ncclResult_t r = g_nccl.CommInitRankConfig(&g_comm, (int)nranks, id, (int)me, &config);
     if (r != ncclSuccess && r != ncclInProgress) {
         KUTACC_CHECK(false, "NCCL error: ", g_nccl.GetErrorString(r), " (ncclCommInitRankConfig)");
