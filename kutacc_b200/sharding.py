@@ -105,6 +105,14 @@ class ShardedTriangleAttention:
                                         [S * C * esz, C * esz, 1], api.DTYPE_BF16, keep=self.out_full),
             }
             self.parts.append(part)
+        # The bias of all slabs in ONE gather: [H, N, S] with N = nslab * srows is also [H * nslab, srows, S] with a
+        # uniform stride between the (head, slab) strips, and inside every strip rank r owns block r.
+        srows, blk = self.slabs[0][1], self.slabs[0][2]
+        strides = [srows * S * esz, S * esz, 1]
+        self.g_nb_src_all = api.Tensor(self.nb_full.data_ptr() + rank * blk * S * esz, [H * nslab, blk, S * esz], strides,
+                                       api.DTYPE_BF16, keep=self.nb_full)
+        self.g_nb_dst_all = api.Tensor(self.nb_full.data_ptr(), [H * nslab, srows, S * esz], strides, api.DTYPE_BF16,
+                                       keep=self.nb_full)
         self.compute = torch.cuda.current_stream(device)
         self.comm = torch.cuda.Stream(device=device)
         self.events = [torch.cuda.Event() for _ in self.parts]
@@ -130,8 +138,7 @@ class ShardedTriangleAttention:
                 api.pair_bias(p["t_z"], self.t_wb, p["t_nb_rows"])
             self.marks[1].record(self.compute)
             if self.world > 1:
-                for p in self.parts:
-                    api.all_gather(p["g_nb_src"], p["g_nb_dst"])
+                api.all_gather(self.g_nb_src_all, self.g_nb_dst_all)        # every slab's strips in one grouped call
             self.marks[2].record(self.compute)
             for p, ev in zip(self.parts, self.events):
                 api.set_stream(self.compute.cuda_stream)
