@@ -50,8 +50,11 @@ UNIT = "TFLOP/s"
 # DRAM bytes (read + write) of one launch of the dominant kernel from an ncu capture, per workload;
 # None until a capture exists for the current kernel. See profiles/.
 NCU_TRAFFIC = {
-    # attn_tc_kernel, ncu --set full, dram__bytes_read.sum + dram__bytes_write.sum (profiles/attn_core_triangle_start_384.md)
+    # attn_tc_kernel, ncu --set full, dram__bytes_read.sum + dram__bytes_write.sum of one launch
     "triangle_start_384": 152.5e6 + 22.0e6,
+    # captured on 64 of the 1024 rows and scaled by the rows (the 8.4 MB pair bias does not scale):
+    # profiles/attn_core_triangle_end_1024.md
+    "triangle_end_1024": (75.7e6 - 8.4e6) * 16 + 8.4e6 + 5.3e6 * 16,
 }
 
 
