@@ -87,6 +87,7 @@ struct AttnParams {
     int n_qt;                         // query tiles per (b, h)
     int n_items;                      // B * H * n_qt
     int gate_is_sigmoid;              // gate already holds bf16(sigmoid(bf16(x.Wg + bg)))
+    int *counter;                     // next work item of this launch (zero at launch)
     float scale;
 };
 
@@ -119,18 +120,30 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     auto q_empty = [&](int i) { return bar + 8u * (uint32_t)(3 * NST + 2 + (i & 1)); };
     const uint32_t s_full = bar + 8u * (3 * NST + 4), s_free = s_full + 8, pv_done = s_full + 16, o_final = s_full + 24,
                    o_free = s_full + 32, x_full = s_full + 40, tmem_slot = s_full + 48;
+    auto it_full = [&](int i) { return s_full + 56u + 8u * (uint32_t)(i & 3); };      // item id of item i has been written
+    const uint32_t item_ring = s_full + 88;                                          // four ints
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int S = p.S;
     const int nkt = (S + BN - 1) / BN;
-    // items of this CTA: blockIdx.x, blockIdx.x + gridDim.x, ...
-    const int my_items = ((int)blockIdx.x < p.n_items) ? (p.n_items - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
-    auto decode = [&](int i, int &q0, int &h, int &b) {
-        const int w = (int)blockIdx.x + i * (int)gridDim.x;
+    // Work items are handed out through an atomic counter in global memory: the producer warp takes the next
+    // item number, publishes it to the other roles through a ring of four shared-memory words (one mbarrier each),
+    // and publishes -1 when the list is exhausted. A CTA that starts late (its SM was busy with another kernel, a
+    // collective running beside this one for instance) simply takes fewer items instead of finishing late.
+    // Ring depth: the producer writes slot i & 3 after its wait for Q buffer i & 1 to be free, i.e. after the MMA
+    // role has finished item i - 2, by which time every role has long read the number of item i - 4.
+    auto decode = [&](int w, int &q0, int &h, int &b) {
         const int qt = w % p.n_qt, hb = w / p.n_qt;
         q0 = qt * BM;
         h = hb % p.H;
         b = hb / p.H;
+    };
+    // item number of this CTA's i-th item, or -1 (bounded wait; -2 on a timeout)
+    auto item_of = [&](int i, int code) -> int {
+        if (!mbar_wait_warp(it_full(i), (uint32_t)((i >> 2) & 1), p.err, code)) return -2;
+        int w;
+        asm volatile("ld.shared.b32 %0, [%1];\n" : "=r"(w) : "r"(item_ring + 4u * (uint32_t)(i & 3)));
+        return w;
     };
 
     if (threadIdx.x == 0) {
@@ -149,6 +162,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         mbar_init(o_final, 1);
         mbar_init(o_free, SOFTMAX_WARPS);
         mbar_init(x_full, SOFTMAX_WARPS);
+        for (int i = 0; i < 4; ++i) mbar_init(it_full(i), 1);
         fence_barrier_init();
     }
     // static rows 32..47 of every V^T stage: row 32 = 1.0 (row-sum column of O), rows 33..47 = 0
@@ -179,11 +193,21 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         }
         int g = 0;                                      // tiles issued so far (all items)
         bool ok = true;
-        for (int i = 0; i < my_items && ok; ++i) {
-            int q0, h, b;
-            decode(i, q0, h, b);
-            const int bh = b * p.H + h;
+        for (int i = 0; ok; ++i) {
+            int w = 0;
+            if (lane == 0) w = atomicAdd(p.counter, 1);
+            w = __shfl_sync(0xffffffffu, w, 0);
+            const bool have = w < p.n_items;
             if (i >= 2 && !mbar_wait_warp(q_empty(i), (uint32_t)(((i >> 1) - 1) & 1), p.err, 20)) break;
+            if (lane == 0) {
+                asm volatile("st.shared.b32 [%0], %1;\n" ::"r"(item_ring + 4u * (uint32_t)(i & 3)), "r"(have ? w : -1) : "memory");
+                mbar_arrive(it_full(i));                               // releases the store above
+            }
+            __syncwarp();
+            if (!have) break;
+            int q0, h, b;
+            decode(w, q0, h, b);
+            const int bh = b * p.H + h;
             if (lane == 0) {
                 mbar_arrive_expect_tx(q_full(i), Q_BYTES);
                 tma_load_3d(q_buf(i), &tm_q, q_full(i), 0, q0, bh);
@@ -216,7 +240,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         // ================= MMA issuer =================
         constexpr uint32_t idesc_s = make_instr_desc_bf16(BM, BN);
         constexpr uint32_t idesc_o = make_instr_desc_bf16(BM, VT_ROWS);
-        const int total = my_items * nkt;               // tiles of this CTA, all items
         // S = Q_i . K_g^T for global tile g of item i
         auto issue_qk = [&](int g, int i, bool first_of_item) -> bool {
             const int s = g % NST;
@@ -235,14 +258,21 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             __syncwarp();
             return true;
         };
-        bool ok = total > 0 ? issue_qk(0, 0, true) : true;
+        bool more = item_of(0, 32) >= 0;                 // this role needs only to know whether an item exists
+        bool ok = more ? issue_qk(0, 0, true) : true;
         int g = 0;
-        for (int i = 0; i < my_items && ok; ++i) {
+        for (int i = 0; more && ok; ++i) {
             for (int kt = 0; kt < nkt && ok; ++kt, ++g) {
                 const int s = g % NST;
                 // look one tile ahead in the stream (possibly the first tile of the next item): its Q.K^T
                 // overlaps the softmax of tile g
-                if (g + 1 < total) ok = issue_qk(g + 1, kt + 1 < nkt ? i : i + 1, kt + 1 == nkt);
+                if (kt + 1 < nkt) {
+                    ok = issue_qk(g + 1, i, false);
+                } else {
+                    const int nxt = item_of(i + 1, 33);
+                    more = nxt >= 0;
+                    ok = nxt != -2 && (!more || issue_qk(g + 1, i + 1, true));
+                }
                 if (!ok) break;
                 if (!mbar_wait_warp(p_full(s), (uint32_t)((g / NST) & 1), p.err, 25)) {
                     ok = false;
@@ -400,9 +430,11 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         };
 
         int g = 0;
-        for (int i = 0; i < my_items && ok; ++i) {
+        for (int i = 0; ok; ++i) {
+            const int w = item_of(i, 34);
+            if (w < 0) break;
             int q0, h, b;
-            decode(i, q0, h, b);
+            decode(w, q0, h, b);
             for (int kt = 0; kt < nkt && ok; ++kt, ++g) ok = do_tile(g, kt);
             if (!ok) break;
 
@@ -488,8 +520,22 @@ bool launch_one(cudaStream_t stream, const CUtensorMap &tq, const CUtensorMap &t
         configured = true;
     }
     const unsigned grid = (unsigned)std::min<int64_t>(p.n_items, 2 * std::max(1, sm_count_attn() - runtime().sm_margin));
+    // one work counter per launch, out of a small ring so that launches in flight on different streams do not share one
+    constexpr int kCounters = 64;
+    static int *counters[64] = {};                       // per device
+    static unsigned next_counter = 0;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) return false;
+    if (counters[dev] == nullptr) {
+        KUTACC_CUDA(cudaMalloc(&counters[dev], kCounters * sizeof(int)));
+        if (counters[dev] == nullptr) return false;
+    }
+    AttnParams q = p;
+    q.counter = counters[dev] + (next_counter++ % kCounters);
+    KUTACC_CUDA(cudaMemsetAsync(q.counter, 0, sizeof(int), stream));
     KernelTimer timer__("attn_core", stream);
-    attn_tc_kernel<HAS_NB><<<grid, THREADS, SMEM_BYTES, stream>>>(tq, tk, tvt, tnb, p);
+    attn_tc_kernel<HAS_NB><<<grid, THREADS, SMEM_BYTES, stream>>>(tq, tk, tvt, tnb, q);
     count_launch();
     return true;
 }
@@ -521,6 +567,7 @@ bool tcgen05_attn_core_bf16(cudaStream_t stream, const void *q, const void *k, c
     p.n_items = (int)n_items;
     p.scale = scale;
     p.gate_is_sigmoid = gate_is_sigmoid ? 1 : 0;
+    p.counter = nullptr;
     const uint64_t Su = (uint64_t)S, BH = (uint64_t)B * H;
     CUtensorMap tq, tk, tvt, tnb;
     if (!make_tensor_map_bf16_3d(&tq, q, D, Su, BH, D, Su * D, D, BM, 64)) return false;
