@@ -1,12 +1,14 @@
 // Fused gated-attention core on the fifth-generation tensor cores (head size 32).
 //
-// A work item is (batch row b, head h, 128 queries). The kernel is persistent: two CTAs per SM each walk
-// a strided list of items, and every pipeline below keeps running across item boundaries, so the loads
-// and the first Q.K^T of the next item overlap the epilogue of the current one. Both matrix products run
+// A work item is (batch row b, head h, 128 queries). The kernel is persistent: two CTAs per SM each take
+// items from an atomic counter until the list is exhausted (a CTA whose SM was busy at launch takes fewer
+// items instead of finishing late), and every pipeline below keeps running across item boundaries, so the
+// loads and the first Q.K^T of the next item overlap the epilogue of the current one. Both matrix products run
 // on tcgen05.mma with accumulators in tensor memory, issued by one elected lane; the softmax runs on the
 // logits read back with tcgen05.ld. The S x S logits never leave the SM.
 //
-//   warp 0     producer: TMA tile loads (hardware swizzle) of Q (double-buffered across items) and, per
+//   warp 0     producer: takes the next item number and publishes it to the other roles; TMA tile loads
+//              (hardware swizzle) of Q (double-buffered across items) and, per
 //              64-key tile, K [64 x 32], V^T [32 x 64] and the 128 x 64 pair-bias tile into a 3-stage ring;
 //              its lanes also convert the tile's 64 mask-bias values to fp32
 //   warp 1     MMA issuer: S = Q.K^T (M 128, N 64, K 32) into TMEM columns 0..63; then two products
