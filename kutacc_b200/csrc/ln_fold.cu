@@ -26,9 +26,72 @@ namespace dev {
 
 namespace {
 
-// one warp per row; 16-byte loads when the row allows it
+// Sums of one 16-byte vector (8 bf16) of shifted data
+__device__ __forceinline__ void stats_acc(const uint4 &raw, float delta, float &sum, float &sum2)
+{
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const float a = bf16lo_to_f32(w[e]) - delta, b = bf16hi_to_f32(w[e]) - delta;
+        sum += a;
+        sum2 = fmaf(a, a, sum2);
+        sum += b;
+        sum2 = fmaf(b, b, sum2);
+    }
+}
+
+// Rows of 16-byte vectors: a group of G lanes (the smallest power of two that covers a row, 4 to 32) per row, so a
+// warp works on 32 / G rows at once, and every group keeps two rows in flight. The shift (the reference sums the
+// data minus the row's first element) comes out of the first vector by a shuffle instead of a load of its own.
+template <int G>
+__global__ void __launch_bounds__(256) ln_stats_vec_kernel(const __nv_bfloat16 *__restrict__ x, int64_t rows, int size,
+                                                           int64_t x_stride, float eps, float2 *__restrict__ stats)
+{
+    constexpr int R = 32 / G;                                    // rows per warp and pass
+    const int lane = threadIdx.x & 31, l = lane % G, gi = lane / G;
+    const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int64_t step = (int64_t)gridDim.x * (blockDim.x >> 5) * R;
+    const int nvec = size / 8;
+    const float n = (float)size;
+    // a warp's lanes stay together (the shuffles below are warp-wide): the loop runs while ANY group has a row
+    for (int64_t base = warp * R; base < rows; base += 2 * step) {
+        const int64_t row0 = base + gi, row1 = base + step + gi;
+        const bool have0 = row0 < rows, have1 = row1 < rows;
+        const uint4 *p0 = reinterpret_cast<const uint4 *>(x + (have0 ? row0 : 0) * x_stride);
+        const uint4 *p1 = reinterpret_cast<const uint4 *>(x + (have1 ? row1 : 0) * x_stride);
+        const uint4 zero = make_uint4(0, 0, 0, 0);
+        uint4 a0 = l < nvec ? __ldg(p0 + l) : zero, a1 = l < nvec ? __ldg(p1 + l) : zero;
+        const float d0 = bf16lo_to_f32(__shfl_sync(0xffffffffu, a0.x, gi * G));
+        const float d1 = bf16lo_to_f32(__shfl_sync(0xffffffffu, a1.x, gi * G));
+        float s0 = 0.f, q0 = 0.f, s1 = 0.f, q1 = 0.f;
+        for (int v = l; v < nvec; v += G) {
+            uint4 b0 = zero, b1 = zero;
+            if (v + G < nvec) {
+                b0 = __ldg(p0 + v + G);
+                b1 = __ldg(p1 + v + G);
+            }
+            stats_acc(a0, d0, s0, q0);
+            stats_acc(a1, d1, s1, q1);
+            a0 = b0;
+            a1 = b1;
+        }
+#pragma unroll
+        for (int o = G / 2; o > 0; o >>= 1) {
+            s0 += __shfl_xor_sync(0xffffffffu, s0, o);
+            q0 += __shfl_xor_sync(0xffffffffu, q0, o);
+            s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+            q1 += __shfl_xor_sync(0xffffffffu, q1, o);
+        }
+        if (l == 0) {
+            if (have0) stats[row0] = make_float2(s0 / n + d0, 1.0f / sqrtf(fmaxf((q0 - s0 * s0 / n) / n, 0.f) + eps));
+            if (have1) stats[row1] = make_float2(s1 / n + d1, 1.0f / sqrtf(fmaxf((q1 - s1 * s1 / n) / n, 0.f) + eps));
+        }
+    }
+}
+
+// any row length and alignment: one warp per row, element loads
 __global__ void __launch_bounds__(256) ln_stats_kernel(const __nv_bfloat16 *__restrict__ x, int64_t rows, int size,
-                                                       int64_t x_stride, float eps, float2 *__restrict__ stats, int vec)
+                                                       int64_t x_stride, float eps, float2 *__restrict__ stats)
 {
     const int lane = threadIdx.x & 31;
     const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -38,25 +101,10 @@ __global__ void __launch_bounds__(256) ln_stats_kernel(const __nv_bfloat16 *__re
         const __nv_bfloat16 *xr = x + row * x_stride;
         const float delta = __bfloat162float(xr[0]);            // shifted data, as the reference sums it
         float sum = 0.f, sum2 = 0.f;
-        if (vec) {
-            for (int v = lane; v < size / 8; v += 32) {
-                const uint4 raw = __ldg(reinterpret_cast<const uint4 *>(xr) + v);
-                const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float a = bf16lo_to_f32(w[e]) - delta, b = bf16hi_to_f32(w[e]) - delta;
-                    sum += a;
-                    sum2 = fmaf(a, a, sum2);
-                    sum += b;
-                    sum2 = fmaf(b, b, sum2);
-                }
-            }
-        } else {
-            for (int i = lane; i < size; i += 32) {
-                const float a = __bfloat162float(xr[i]) - delta;
-                sum += a;
-                sum2 = fmaf(a, a, sum2);
-            }
+        for (int i = lane; i < size; i += 32) {
+            const float a = __bfloat162float(xr[i]) - delta;
+            sum += a;
+            sum2 = fmaf(a, a, sum2);
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
@@ -119,10 +167,27 @@ __global__ void __launch_bounds__(256) ln_fold_kernel(const FoldArgs a, const fl
 bool launch_ln_stats(cudaStream_t stream, const void *x, int64_t rows, int64_t size, int64_t x_stride, float eps, void *stats)
 {
     if (rows <= 0 || size <= 0 || size > INT32_MAX) return false;
-    const int vec = (size % 8 == 0) && (x_stride % 8 == 0) && (((uintptr_t)x & 15u) == 0);
-    const unsigned grid = (unsigned)std::min<int64_t>((rows + 7) / 8, 148 * 16);
+    const bool vec = (size % 8 == 0) && (x_stride % 8 == 0) && (((uintptr_t)x & 15u) == 0);
+    const __nv_bfloat16 *xp = (const __nv_bfloat16 *)x;
+    float2 *sp = (float2 *)stats;
     KernelTimer timer__("ln_stats", stream);
-    ln_stats_kernel<<<grid, 256, 0, stream>>>((const __nv_bfloat16 *)x, rows, (int)size, x_stride, eps, (float2 *)stats, vec);
+    if (vec) {
+        const int64_t nvec = size / 8;
+        const int g = nvec <= 4 ? 4 : nvec <= 8 ? 8 : nvec <= 16 ? 16 : 32;
+        const int64_t rows_per_block = 8 * (32 / g) * 2;                    // 8 warps, two rows in flight per group
+        const unsigned grid = (unsigned)std::min<int64_t>((rows + rows_per_block - 1) / rows_per_block, 148 * 8);
+        if (g == 4)
+            ln_stats_vec_kernel<4><<<grid, 256, 0, stream>>>(xp, rows, (int)size, x_stride, eps, sp);
+        else if (g == 8)
+            ln_stats_vec_kernel<8><<<grid, 256, 0, stream>>>(xp, rows, (int)size, x_stride, eps, sp);
+        else if (g == 16)
+            ln_stats_vec_kernel<16><<<grid, 256, 0, stream>>>(xp, rows, (int)size, x_stride, eps, sp);
+        else
+            ln_stats_vec_kernel<32><<<grid, 256, 0, stream>>>(xp, rows, (int)size, x_stride, eps, sp);
+    } else {
+        const unsigned grid = (unsigned)std::min<int64_t>((rows + 7) / 8, 148 * 16);
+        ln_stats_kernel<<<grid, 256, 0, stream>>>(xp, rows, (int)size, x_stride, eps, sp);
+    }
     count_launch();
     return true;
 }

@@ -167,6 +167,13 @@ class HostShardedTriangleAttention:
     the gated attention with a HOST ``out``: the library then runs the batch rows in chunks and overlaps the
     download of chunk i with the kernels of chunk i + 1. Every rank ends with its own rows in host memory (the
     ranks of one node share that memory, so nothing is gathered). Rank r owns the contiguous block r.
+
+    The attention of a step needs the pair bias of EVERY row, so inside one step the upload cannot overlap the
+    kernels or the download. With ``prefetch=True`` (the default) the device side of the input is double-buffered
+    and a step starts the upload of the NEXT step's rows on a stream of its own just before it blocks in the
+    attention call: the upload of step i + 1 then travels beside the kernels and the download of step i (the link
+    is full duplex). ``step(prefetch=False)`` runs one step on its own (its latency). ``drain()`` makes the compute
+    stream wait for an upload still in flight.
     """
 
     def __init__(self, w, rank: int, world: int, device):
@@ -188,8 +195,9 @@ class HostShardedTriangleAttention:
         self.hx = _to_torch(A["x"][r0:r0 + n], w.dtype, "cpu", pin=True)
         self.hbias = _to_torch(A["bias"][r0:r0 + n], w.dtype, "cpu", pin=True)
         self.hout = torch.zeros((n, S, C), dtype=tdt).pin_memory()
-        self.x = torch.empty((n, S, C), dtype=tdt, device=device)
-        self.bias = torch.empty((n, S), dtype=tdt, device=device)
+        self.xs = [torch.empty((n, S, C), dtype=tdt, device=device) for _ in range(2)]
+        self.biases = [torch.empty((n, S), dtype=tdt, device=device) for _ in range(2)]
+        self.x = self.xs[0]
         f = lambda a: _to_torch(a, w.dtype, device)
         f32 = lambda a: _to_torch(a, "fp32", device)
         self.wq, self.wk, self.wv, self.wg, self.wo = (f(A[k]) for k in ("wq", "wk", "wv", "wg", "wo"))
@@ -200,9 +208,9 @@ class HostShardedTriangleAttention:
         self.inputs = api.make_inputs(n, S)
         self.t_wb = api.tensor(self.wb)
         self.t_nb = api.tensor(self.nb_full)
-        self.t_x = api.tensor(self.x, sizes=[n * S, C], strides=[C, 1])
-        self.t_z = api.tensor(self.x)
-        self.t_bias = api.tensor(self.bias)
+        self.t_x = [api.tensor(x, sizes=[n * S, C], strides=[C, 1]) for x in self.xs]
+        self.t_z = [api.tensor(x) for x in self.xs]
+        self.t_bias = [api.tensor(b) for b in self.biases]
         self.t_out = api.tensor(self.hout)
         nb_rows = self.nb_full[:, r0:r0 + n, :]
         self.t_nb_rows = api.Tensor(nb_rows.data_ptr(), [H, n, S], [S * S, S, 1], dt, keep=self.nb_full)
@@ -211,6 +219,11 @@ class HostShardedTriangleAttention:
         self.g_nb_dst = api.Tensor(self.nb_full.data_ptr(), [H, N, S * esz], [S * S * esz, S * esz, 1], api.DTYPE_BF16,
                                    keep=self.nb_full)
         self.compute = torch.cuda.current_stream(device)
+        self.upload = torch.cuda.Stream(device)
+        self.uploaded = [torch.cuda.Event() for _ in range(2)]
+        self.index = 0                 # number of the next step
+        self.in_flight = -1            # step whose rows have been sent to the device (or are on their way)
+        self.torch = torch
 
     def h2d_bytes(self) -> int:
         return int(self.hx.numel() * self.hx.element_size() + self.hbias.numel() * self.hbias.element_size())
@@ -218,18 +231,39 @@ class HostShardedTriangleAttention:
     def d2h_bytes(self) -> int:
         return int(self.hout.numel() * self.hout.element_size())
 
-    def step(self, block_size: int = 128):
+    def _send(self, i: int):
+        """Queue the upload of step i's rows on the upload stream. Device buffer i % 2 was last read by step i - 2,
+        whose attention call has returned (it returns when its last output row is in host memory)."""
+        j = i & 1
+        with self.torch.cuda.stream(self.upload):
+            self.xs[j].copy_(self.hx, non_blocking=True)
+            self.biases[j].copy_(self.hbias, non_blocking=True)
+            self.uploaded[j].record(self.upload)
+        self.in_flight = i
+
+    def drain(self):
+        if self.in_flight >= 0:
+            self.compute.wait_event(self.uploaded[self.in_flight & 1])
+
+    def step(self, block_size: int = 128, prefetch: bool = True):
         api = self.api
+        i, j = self.index, self.index & 1
         api.set_async(True)
         try:
             api.set_stream(self.compute.cuda_stream)
-            self.x.copy_(self.hx, non_blocking=True)
-            self.bias.copy_(self.hbias, non_blocking=True)
-            api.pair_bias(self.t_z, self.t_wb, self.t_nb_rows)
+            if self.in_flight != i:
+                self.upload.wait_stream(self.compute)
+                self._send(i)
+            self.compute.wait_event(self.uploaded[j])
+            api.pair_bias(self.t_z[j], self.t_wb, self.t_nb_rows)
             if self.world > 1:
                 api.all_gather(self.g_nb_src, self.g_nb_dst)
+            if prefetch:
+                self._send(i + 1)
             # returns when the last chunk of `out` has landed in host memory
-            api.gating_attention(self.t_x, self.inputs, self.t_bias, self.t_nb, self.weights, self.t_out, block_size)
+            api.gating_attention(self.t_x[j], self.inputs, self.t_bias[j], self.t_nb, self.weights, self.t_out, block_size)
+            api.synchronize()      # small problems are not chunked: their single download is only queued so far
         finally:
             api.set_async(False)
+        self.index = i + 1
         return self.hout

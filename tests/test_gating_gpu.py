@@ -192,6 +192,22 @@ def test_sharded_triangle_flow_on_one_rank_matches_the_plain_call(kutacc_lib):
     assert helpers.rel_err(got, helpers.oracle_faithful(w)) <= helpers.BF16_TOL
 
 
+def test_host_rows_flow_with_and_without_prefetch_matches_the_device_flow(kutacc_lib):
+    # rows of z in pinned host memory, output rows to pinned host memory (sharding.HostShardedTriangleAttention):
+    # every step, stand-alone or with the next step's upload already in flight, gives the device flow's bits
+    from kutacc_b200 import sharding
+    w = W.make("triangle_start_384", rows=128, seq=128)
+    want = runner.out_to_f32(sharding.ShardedTriangleAttention(w, 0, 1, 1, "cuda:0").step()).copy()
+    host = sharding.HostShardedTriangleAttention(w, 0, 1, "cuda:0")
+    for prefetch in (False, True, True, False, True):
+        got = host.step(prefetch=prefetch).float().numpy()
+        assert np.array_equal(got, want)
+        host.hout.zero_()
+    host.drain()
+    torch.cuda.synchronize()
+    api.raise_if_error()
+
+
 def test_sm_margin_changes_the_grid_not_the_result(kutacc_lib):
     # the persistent kernels walk their work items with a stride of the grid size: leaving SMs free for a
     # collective must not change a single bit
