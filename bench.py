@@ -292,7 +292,7 @@ def run_reference_arm(args):
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line))
+    emit(json.dumps(line))
     return 0
 
 
@@ -527,7 +527,7 @@ def run_strong_scaling(args, torch, dist, api, W, runner, dev, world, rank, loca
             glob = global_attention_extra(torch, api, W, runner, dev, peaks)
     if rank == 0:
         cfg = config_for(args.workload, world, "strong")
-        print(json.dumps({
+        emit(json.dumps({
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": w.dtype, "data": "synthetic (seeded numpy, AlphaFold2 model shapes)",
@@ -543,6 +543,28 @@ def run_strong_scaling(args, torch, dist, api, W, runner, dev, world, rank, loca
             "result_mean_abs": checksum, "clocks": clocks.summary(), "hbm_copy_gbs_now": copy_now,
         }))
     return 0
+
+
+_RESULT_FD = None
+
+
+def keep_stdout_for_the_result():
+    """Libraries loaded below write to the process's standard output on their own (NCCL prints its version line
+    there when NCCL_DEBUG asks for it). The contract is ONE JSON line on stdout, so file descriptor 1 is pointed at
+    stderr for the rest of the run and the result line goes to a saved copy of the original stdout."""
+    global _RESULT_FD
+    if _RESULT_FD is None:
+        sys.stdout.flush()
+        _RESULT_FD = os.dup(1)
+        os.dup2(2, 1)
+
+
+def emit(line: str):
+    sys.stdout.flush()
+    if _RESULT_FD is None:
+        print(line, flush=True)
+    else:
+        os.write(_RESULT_FD, (line + "\n").encode())
 
 
 def main():
@@ -571,6 +593,7 @@ def main():
                     help="strong scaling: skip the all-gather of the output rows in the headline figure too")
     ap.add_argument("--slabs", type=int, default=2, help="strong scaling: slabs the output gather is pipelined in")
     args = ap.parse_args()
+    keep_stdout_for_the_result()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     args.steps = max(args.steps, 1)
 
@@ -732,7 +755,7 @@ def main():
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches),
             "clocks": clocks.summary(), "hbm_copy_gbs_now": hbm_copy_gbs(torch, dev),
         }
-        print(json.dumps(line))
+        emit(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
     return 0

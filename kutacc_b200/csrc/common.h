@@ -78,10 +78,24 @@ struct Runtime {
     char *stage_base = nullptr;
     size_t stage_cap = 0, stage_off = 0;
 
+    // An enqueue-only call (async) whose result goes to HOST memory in chunks returns while its downloads are still
+    // running on the copy-out stream. `out_done` (cudaEvent_t) follows the last of them. out_unsynced: the host has
+    // not waited for it yet (kutacc_b200_synchronize does); out_hazard: later work on the runtime stream has not been
+    // ordered after it yet, so the staging block the downloads read must not be rewritten. pend_*: which staged
+    // output and which chunking the downloads belong to, for a following call of the same shape that orders itself
+    // chunk by chunk instead.
+    void *out_done = nullptr;
+    bool out_unsynced = false, out_hazard = false;
+    const void *pend_dev = nullptr;
+    size_t pend_bytes = 0;
+    int pend_nchunks = 0;
+    int64_t pend_rows = 0;
+
     // reserve() must be called once per operator call with the total need, before any take()
     bool reserve_workspace(size_t bytes);
     void *take_workspace(size_t bytes);   // 256-byte aligned slices of the reserved block
-    bool reserve_stage(size_t bytes);
+    // caller_orders_downloads: the caller itself orders its writes after downloads still in flight (see out_hazard)
+    bool reserve_stage(size_t bytes, bool caller_orders_downloads = false);
     void *take_stage(size_t bytes);
     void release();
 };
@@ -123,7 +137,7 @@ void sync_and_check();                                                 // stream
 struct CopyPipeline {
     void *in = nullptr, *out = nullptr;       // cudaStream_t
     void *start = nullptr;                    // cudaEvent_t
-    std::vector<void *> uploaded, computed;   // cudaEvent_t per chunk
+    std::vector<void *> uploaded, computed, downloaded;   // cudaEvent_t per chunk
 };
 CopyPipeline &copy_pipeline(int nchunks);
 

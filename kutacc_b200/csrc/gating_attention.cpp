@@ -73,6 +73,14 @@ static void gating_attention_impl(Tensor &input, int64_t batch, int64_t seq_len,
     Runtime &rt = runtime();
     cudaStream_t stream = (cudaStream_t)rt.stream;
 
+    // When the result lives in host memory, the batch rows (independent problems) are processed in chunks so
+    // that the upload of chunk i+1 (when the activations are in host memory too), the kernels of chunk i and
+    // the download of chunk i-1 overlap on three streams. Otherwise the call is a single chunk on the runtime
+    // stream.
+    const bool x_host = staged_bytes_needed(input.data_ptr(), x_bytes) != 0;
+    const bool out_host = staged_bytes_needed(out.data_ptr(), out_bytes) != 0;
+    const bool pipelined = out_host && B >= 8 && x_bytes >= ((size_t)4 << 20);
+
     size_t stage = staged_bytes_needed(input.data_ptr(), x_bytes) + staged_bytes_needed(bias.data_ptr(), bias_bytes) +
                    staged_bytes_needed(out.data_ptr(), out_bytes) + staged_bytes_needed(gating_b.data_ptr(), b_bytes) +
                    staged_bytes_needed(output_b.data_ptr(), b_bytes);
@@ -80,7 +88,8 @@ static void gating_attention_impl(Tensor &input, int64_t batch, int64_t seq_len,
     for (const Tensor *w : {&query_w, &key_w, &value_w, &gating_w, &output_w})
         stage += staged_bytes_needed(w->data_ptr(), w_bytes);
     if (ln) stage += 2 * staged_bytes_needed(ln->gamma, b_bytes);
-    if (!rt.reserve_stage(stage)) return;
+    const bool downloads_in_flight = rt.out_hazard;          // of an earlier enqueue-only call with a HOST result
+    if (!rt.reserve_stage(stage, pipelined)) return;
     const int64_t s_pad8 = (S + 7) / 8 * 8;
     const size_t nb_pad_bytes = has_nb ? (size_t)H * S * s_pad8 * 2 : 0;
     const size_t v_bytes = std::max(x_bytes, (size_t)B * C * s_pad8 * es);   // v may be stored key-major with padded rows
@@ -89,13 +98,20 @@ static void gating_attention_impl(Tensor &input, int64_t batch, int64_t seq_len,
     const size_t ln_bytes = ln ? (size_t)M * 8 + 4 * (w_bytes + 256) + 8 * (b_bytes + 256) + x_bytes + 1024 : 0;
     if (!rt.reserve_workspace(4 * (x_bytes + 256) + v_bytes + 256 + nb_pad_bytes + 256 + ln_bytes)) return;
 
-    // When the result lives in host memory, the batch rows (independent problems) are processed in chunks so
-    // that the upload of chunk i+1 (when the activations are in host memory too), the kernels of chunk i and
-    // the download of chunk i-1 overlap on three streams. Otherwise the call is a single chunk on the runtime
-    // stream.
-    const bool x_host = staged_bytes_needed(input.data_ptr(), x_bytes) != 0;
-    const bool out_host = staged_bytes_needed(out.data_ptr(), out_bytes) != 0;
-    const bool pipelined = out_host && B >= 8 && x_bytes >= ((size_t)4 << 20);
+    // The staged output is placed first: its address tells whether downloads of an earlier enqueue-only call, still
+    // in flight, read the very block this call will fill. A call of the same shape (same block, same chunks) lets its
+    // chunk i wait for the earlier download of chunk i only, so its first chunks run beside the tail of those
+    // downloads; any other call waits for all of them before it writes anything into the staging area.
+    DeviceArg d_out = resolve_out(out.data_ptr(), out_bytes);
+    // about 8 MiB of activations per chunk on average, between 2 and 12 chunks of at least 4 rows
+    int nchunks = (int)std::max<int64_t>(2, std::min<int64_t>(12, (int64_t)((x_bytes + ((size_t)4 << 20)) >> 23)));
+    nchunks = (int)std::max<int64_t>(1, std::min<int64_t>(nchunks, B / 4));
+    const bool same_chunks = pipelined && downloads_in_flight && rt.pend_dev == d_out.dev && rt.pend_bytes == out_bytes &&
+                             rt.pend_nchunks == nchunks && rt.pend_rows == B;
+    if (pipelined && downloads_in_flight && !same_chunks) {
+        KUTACC_CUDA(cudaStreamWaitEvent(stream, (cudaEvent_t)rt.out_done, 0));
+        rt.out_hazard = false;
+    }
 
     if (pipelined) {
         // the copy streams may start as soon as the previous work on the runtime stream is done: mark that
@@ -113,7 +129,6 @@ static void gating_attention_impl(Tensor &input, int64_t batch, int64_t seq_len,
               d_wv = resolve_in(value_w.data_ptr(), w_bytes), d_wg = resolve_in(gating_w.data_ptr(), w_bytes),
               d_wo = resolve_in(output_w.data_ptr(), w_bytes);
     DeviceArg d_bg = resolve_in(gating_b.data_ptr(), b_bytes), d_bo = resolve_in(output_b.data_ptr(), b_bytes);
-    DeviceArg d_out = resolve_out(out.data_ptr(), out_bytes);
     char *wq_ = (char *)rt.take_workspace(x_bytes), *wk_ = (char *)rt.take_workspace(x_bytes),
          *wv_ = (char *)rt.take_workspace(v_bytes), *wg_ = (char *)rt.take_workspace(x_bytes),
          *wavg = (char *)rt.take_workspace(x_bytes);
@@ -248,9 +263,6 @@ static void gating_attention_impl(Tensor &input, int64_t batch, int64_t seq_len,
         if (d_out.staged)
             copy_rows_d2h((char *)d_out.host, (const char *)d_out.dev, (size_t)M, (size_t)C * es, (size_t)out_rs * es, stream);
     } else {
-        // about 8 MiB of activations per chunk on average, between 2 and 12 chunks of at least 4 rows
-        int nchunks = (int)std::max<int64_t>(2, std::min<int64_t>(12, (int64_t)((x_bytes + ((size_t)4 << 20)) >> 23)));
-        nchunks = (int)std::max<int64_t>(1, std::min<int64_t>(nchunks, B / 4));
         // Chunk i gets a share of the rows proportional to nchunks + 2 - i: the chunks shrink towards the end,
         // because the kernels and the download of the last chunk are the part of the call nothing overlaps.
         int64_t chunk_begin[17];
@@ -270,6 +282,7 @@ static void gating_attention_impl(Tensor &input, int64_t batch, int64_t seq_len,
         for (int i = 0; i < nchunks && ok; ++i) {
             const int64_t b0 = chunk_begin[i], nbr = chunk_begin[i + 1] - b0;
             if (nbr <= 0) continue;
+            if (same_chunks) KUTACC_CUDA(cudaStreamWaitEvent(stream, (cudaEvent_t)cp.downloaded[i], 0));
             if (x_host) {
                 KUTACC_CUDA(cudaMemcpyAsync((char *)d_x.dev + b0 * row_bytes, (const char *)input.data_ptr() + b0 * row_bytes,
                                             (size_t)nbr * row_bytes, cudaMemcpyHostToDevice, s_in));
@@ -284,8 +297,29 @@ static void gating_attention_impl(Tensor &input, int64_t batch, int64_t seq_len,
             const size_t o_off = (size_t)b0 * S * out_rs * es;
             copy_rows_d2h((char *)out.data_ptr() + o_off, (const char *)d_out.dev + o_off, (size_t)nbr * S, (size_t)C * es,
                           (size_t)out_rs * es, s_out);
+            KUTACC_CUDA(cudaEventRecord((cudaEvent_t)cp.downloaded[i], s_out));
         }
-        KUTACC_CUDA(cudaStreamSynchronize(s_out));
+        if (rt.async) {
+            // enqueue-only: the call returns with its downloads in flight; kutacc_b200_synchronize waits for them
+            if (rt.out_done == nullptr) {
+                cudaEvent_t e = nullptr;
+                KUTACC_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+                rt.out_done = e;
+            }
+            if (rt.out_done) {
+                KUTACC_CUDA(cudaEventRecord((cudaEvent_t)rt.out_done, s_out));
+                rt.out_unsynced = rt.out_hazard = true;
+                rt.pend_dev = d_out.dev;
+                rt.pend_bytes = out_bytes;
+                rt.pend_nchunks = nchunks;
+                rt.pend_rows = B;
+            } else {
+                KUTACC_CUDA(cudaStreamSynchronize(s_out));
+            }
+        } else {
+            KUTACC_CUDA(cudaStreamSynchronize(s_out));
+            rt.out_unsynced = rt.out_hazard = false;
+        }
     }
     KUTACC_CHECK(ok, "gating_attention: no device kernel for this shape (B=", B, " S=", S, " H=", H, " D=", D, ")");
     end_of_call();

@@ -41,8 +41,9 @@ __device__ __forceinline__ void stats_acc(const uint4 &raw, float delta, float &
 }
 
 // Rows of 16-byte vectors: a group of G lanes (the smallest power of two that covers a row, 4 to 32) per row, so a
-// warp works on 32 / G rows at once, and every group keeps two rows in flight. The shift (the reference sums the
+// warp works on 32 / G rows at once, and every group keeps NR rows in flight. The shift (the reference sums the
 // data minus the row's first element) comes out of the first vector by a shuffle instead of a load of its own.
+constexpr int NR = 4;
 template <int G>
 __global__ void __launch_bounds__(256) ln_stats_vec_kernel(const __nv_bfloat16 *__restrict__ x, int64_t rows, int size,
                                                            int64_t x_stride, float eps, float2 *__restrict__ stats)
@@ -53,38 +54,47 @@ __global__ void __launch_bounds__(256) ln_stats_vec_kernel(const __nv_bfloat16 *
     const int64_t step = (int64_t)gridDim.x * (blockDim.x >> 5) * R;
     const int nvec = size / 8;
     const float n = (float)size;
+    const uint4 zero = make_uint4(0, 0, 0, 0);
     // a warp's lanes stay together (the shuffles below are warp-wide): the loop runs while ANY group has a row
-    for (int64_t base = warp * R; base < rows; base += 2 * step) {
-        const int64_t row0 = base + gi, row1 = base + step + gi;
-        const bool have0 = row0 < rows, have1 = row1 < rows;
-        const uint4 *p0 = reinterpret_cast<const uint4 *>(x + (have0 ? row0 : 0) * x_stride);
-        const uint4 *p1 = reinterpret_cast<const uint4 *>(x + (have1 ? row1 : 0) * x_stride);
-        const uint4 zero = make_uint4(0, 0, 0, 0);
-        uint4 a0 = l < nvec ? __ldg(p0 + l) : zero, a1 = l < nvec ? __ldg(p1 + l) : zero;
-        const float d0 = bf16lo_to_f32(__shfl_sync(0xffffffffu, a0.x, gi * G));
-        const float d1 = bf16lo_to_f32(__shfl_sync(0xffffffffu, a1.x, gi * G));
-        float s0 = 0.f, q0 = 0.f, s1 = 0.f, q1 = 0.f;
+    for (int64_t base = warp * R; base < rows; base += NR * step) {
+        int64_t row[NR];
+        const uint4 *p[NR];
+        uint4 a[NR];
+        float d[NR], s[NR], q[NR];
+#pragma unroll
+        for (int r = 0; r < NR; ++r) {
+            row[r] = base + r * step + gi;
+            p[r] = reinterpret_cast<const uint4 *>(x + (row[r] < rows ? row[r] : 0) * x_stride);
+            a[r] = l < nvec ? __ldg(p[r] + l) : zero;
+        }
+#pragma unroll
+        for (int r = 0; r < NR; ++r) {
+            d[r] = bf16lo_to_f32(__shfl_sync(0xffffffffu, a[r].x, gi * G));
+            s[r] = q[r] = 0.f;
+        }
         for (int v = l; v < nvec; v += G) {
-            uint4 b0 = zero, b1 = zero;
-            if (v + G < nvec) {
-                b0 = __ldg(p0 + v + G);
-                b1 = __ldg(p1 + v + G);
+            uint4 b[NR];
+#pragma unroll
+            for (int r = 0; r < NR; ++r) b[r] = v + G < nvec ? __ldg(p[r] + v + G) : zero;
+#pragma unroll
+            for (int r = 0; r < NR; ++r) {
+                stats_acc(a[r], d[r], s[r], q[r]);
+                a[r] = b[r];
             }
-            stats_acc(a0, d0, s0, q0);
-            stats_acc(a1, d1, s1, q1);
-            a0 = b0;
-            a1 = b1;
         }
 #pragma unroll
         for (int o = G / 2; o > 0; o >>= 1) {
-            s0 += __shfl_xor_sync(0xffffffffu, s0, o);
-            q0 += __shfl_xor_sync(0xffffffffu, q0, o);
-            s1 += __shfl_xor_sync(0xffffffffu, s1, o);
-            q1 += __shfl_xor_sync(0xffffffffu, q1, o);
+#pragma unroll
+            for (int r = 0; r < NR; ++r) {
+                s[r] += __shfl_xor_sync(0xffffffffu, s[r], o);
+                q[r] += __shfl_xor_sync(0xffffffffu, q[r], o);
+            }
         }
         if (l == 0) {
-            if (have0) stats[row0] = make_float2(s0 / n + d0, 1.0f / sqrtf(fmaxf((q0 - s0 * s0 / n) / n, 0.f) + eps));
-            if (have1) stats[row1] = make_float2(s1 / n + d1, 1.0f / sqrtf(fmaxf((q1 - s1 * s1 / n) / n, 0.f) + eps));
+#pragma unroll
+            for (int r = 0; r < NR; ++r)
+                if (row[r] < rows)
+                    stats[row[r]] = make_float2(s[r] / n + d[r], 1.0f / sqrtf(fmaxf((q[r] - s[r] * s[r] / n) / n, 0.f) + eps));
         }
     }
 }
@@ -174,7 +184,7 @@ bool launch_ln_stats(cudaStream_t stream, const void *x, int64_t rows, int64_t s
     if (vec) {
         const int64_t nvec = size / 8;
         const int g = nvec <= 4 ? 4 : nvec <= 8 ? 8 : nvec <= 16 ? 16 : 32;
-        const int64_t rows_per_block = 8 * (32 / g) * 2;                    // 8 warps, two rows in flight per group
+        const int64_t rows_per_block = 8 * (32 / g) * NR;                   // 8 warps, NR rows in flight per group
         const unsigned grid = (unsigned)std::min<int64_t>((rows + rows_per_block - 1) / rows_per_block, 148 * 8);
         if (g == 4)
             ln_stats_vec_kernel<4><<<grid, 256, 0, stream>>>(xp, rows, (int)size, x_stride, eps, sp);

@@ -48,8 +48,13 @@ static size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 static bool grow(char *&base, size_t &cap, size_t need)
 {
     if (need <= cap) return true;
-    // Blocks are handed to kernels enqueued on the stream; let them drain before the old block goes.
+    // Blocks are handed to kernels enqueued on the stream (and to downloads on the copy-out stream); let them
+    // drain before the old block goes.
     KUTACC_CUDA(cudaStreamSynchronize((cudaStream_t)runtime().stream));
+    if (runtime().out_unsynced && runtime().out_done) {
+        KUTACC_CUDA(cudaEventSynchronize((cudaEvent_t)runtime().out_done));
+        runtime().out_unsynced = runtime().out_hazard = false;
+    }
     if (base) KUTACC_CUDA(cudaFree(base));
     base = nullptr;
     cap = 0;
@@ -75,10 +80,16 @@ void *Runtime::take_workspace(size_t bytes)
     KUTACC_CHECK(ws_off <= ws_cap, "workspace slice beyond reservation: ", ws_off, " > ", ws_cap);
     return ws_off <= ws_cap ? ws_base + off : nullptr;
 }
-bool Runtime::reserve_stage(size_t bytes)
+bool Runtime::reserve_stage(size_t bytes, bool caller_orders_downloads)
 {
     stage_off = 0;
-    return bytes == 0 ? true : grow(stage_base, stage_cap, bytes);
+    if (bytes == 0) return true;
+    if (out_hazard && !caller_orders_downloads) {
+        // downloads of an earlier enqueue-only call still read the staging block this call is about to fill
+        KUTACC_CUDA(cudaStreamWaitEvent((cudaStream_t)stream, (cudaEvent_t)out_done, 0));
+        out_hazard = false;
+    }
+    return grow(stage_base, stage_cap, bytes);
 }
 void *Runtime::take_stage(size_t bytes)
 {
@@ -175,11 +186,13 @@ CopyPipeline &copy_pipeline(int nchunks)
         cp.start = e;
     }
     while ((int)cp.uploaded.size() < nchunks) {
-        cudaEvent_t e1 = nullptr, e2 = nullptr;
+        cudaEvent_t e1 = nullptr, e2 = nullptr, e3 = nullptr;
         KUTACC_CUDA(cudaEventCreateWithFlags(&e1, cudaEventDisableTiming));
         KUTACC_CUDA(cudaEventCreateWithFlags(&e2, cudaEventDisableTiming));
+        KUTACC_CUDA(cudaEventCreateWithFlags(&e3, cudaEventDisableTiming));
         cp.uploaded.push_back(e1);
         cp.computed.push_back(e2);
+        cp.downloaded.push_back(e3);
     }
     return cp;
 }
@@ -196,6 +209,11 @@ void end_of_call()
 void sync_and_check()
 {
     KUTACC_CUDA(cudaStreamSynchronize((cudaStream_t)runtime().stream));
+    if (runtime().out_unsynced && runtime().out_done) {
+        // chunked downloads of an enqueue-only call: the host result is complete only now
+        KUTACC_CUDA(cudaEventSynchronize((cudaEvent_t)runtime().out_done));
+        runtime().out_unsynced = runtime().out_hazard = false;
+    }
     dev::KernelErrorWord &ew = dev::kernel_error_word();
     if (ew.host && *ew.host != 0) {
         const int code = *ew.host;

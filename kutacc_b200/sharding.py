@@ -170,10 +170,11 @@ class HostShardedTriangleAttention:
 
     The attention of a step needs the pair bias of EVERY row, so inside one step the upload cannot overlap the
     kernels or the download. With ``prefetch=True`` (the default) the device side of the input is double-buffered
-    and a step starts the upload of the NEXT step's rows on a stream of its own just before it blocks in the
+    and a step starts the upload of the NEXT step's rows on a stream of its own just before it queues the
     attention call: the upload of step i + 1 then travels beside the kernels and the download of step i (the link
-    is full duplex). ``step(prefetch=False)`` runs one step on its own (its latency). ``drain()`` makes the compute
-    stream wait for an upload still in flight.
+    is full duplex), and the calls only queue work, so the first chunks of step i + 1 are computed beside the last
+    downloads of step i. ``step(prefetch=False)`` runs one step on its own (its latency). ``drain()`` waits for
+    everything queued.
     """
 
     def __init__(self, w, rank: int, world: int, device):
@@ -221,6 +222,7 @@ class HostShardedTriangleAttention:
         self.compute = torch.cuda.current_stream(device)
         self.upload = torch.cuda.Stream(device)
         self.uploaded = [torch.cuda.Event() for _ in range(2)]
+        self.computed = [None, None]   # recorded after the kernels of the last step that read device buffer 0 / 1
         self.index = 0                 # number of the next step
         self.in_flight = -1            # step whose rows have been sent to the device (or are on their way)
         self.torch = torch
@@ -232,9 +234,11 @@ class HostShardedTriangleAttention:
         return int(self.hout.numel() * self.hout.element_size())
 
     def _send(self, i: int):
-        """Queue the upload of step i's rows on the upload stream. Device buffer i % 2 was last read by step i - 2,
-        whose attention call has returned (it returns when its last output row is in host memory)."""
+        """Queue the upload of step i's rows on the upload stream, after the kernels of step i - 2 (the last reader
+        of device buffer i % 2)."""
         j = i & 1
+        if self.computed[j] is not None:
+            self.upload.wait_event(self.computed[j])
         with self.torch.cuda.stream(self.upload):
             self.xs[j].copy_(self.hx, non_blocking=True)
             self.biases[j].copy_(self.hbias, non_blocking=True)
@@ -242,10 +246,16 @@ class HostShardedTriangleAttention:
         self.in_flight = i
 
     def drain(self):
+        """Wait (on the host) until every queued step has delivered its rows and no upload is in flight."""
         if self.in_flight >= 0:
             self.compute.wait_event(self.uploaded[self.in_flight & 1])
+        self.api.set_stream(self.compute.cuda_stream)
+        self.api.synchronize()
 
     def step(self, block_size: int = 128, prefetch: bool = True):
+        """One step. With ``prefetch`` the call only queues work: the next step's rows start their way to the device
+        and the output rows of this step are complete in ``hout`` after a later ``drain()`` (or after the next
+        stand-alone step). Without it the step runs on its own and ``hout`` is complete on return."""
         api = self.api
         i, j = self.index, self.index & 1
         api.set_async(True)
@@ -260,9 +270,14 @@ class HostShardedTriangleAttention:
                 api.all_gather(self.g_nb_src, self.g_nb_dst)
             if prefetch:
                 self._send(i + 1)
-            # returns when the last chunk of `out` has landed in host memory
+            # enqueue-only: the library downloads the output rows chunk by chunk on its copy stream while the later
+            # chunks (and, with prefetch, the first chunks of the next step) are computed
             api.gating_attention(self.t_x[j], self.inputs, self.t_bias[j], self.t_nb, self.weights, self.t_out, block_size)
-            api.synchronize()      # small problems are not chunked: their single download is only queued so far
+            if self.computed[j] is None:
+                self.computed[j] = self.torch.cuda.Event()
+            self.computed[j].record(self.compute)
+            if not prefetch:
+                api.synchronize()
         finally:
             api.set_async(False)
         self.index = i + 1

@@ -200,12 +200,42 @@ def test_host_rows_flow_with_and_without_prefetch_matches_the_device_flow(kutacc
     want = runner.out_to_f32(sharding.ShardedTriangleAttention(w, 0, 1, 1, "cuda:0").step()).copy()
     host = sharding.HostShardedTriangleAttention(w, 0, 1, "cuda:0")
     for prefetch in (False, True, True, False, True):
-        got = host.step(prefetch=prefetch).float().numpy()
-        assert np.array_equal(got, want)
+        out = host.step(prefetch=prefetch)
+        if prefetch:
+            host.drain()                      # a prefetching step only queues its work
+        assert np.array_equal(out.float().numpy(), want)
         host.hout.zero_()
+    # three steps queued back to back before anything is waited for
+    for _ in range(3):
+        host.step()
     host.drain()
+    assert np.array_equal(host.hout.float().numpy(), want)
     torch.cuda.synchronize()
     api.raise_if_error()
+
+
+def test_enqueue_only_call_with_host_out_is_complete_after_synchronize(kutacc_lib):
+    """An enqueue-only call whose `out` is in HOST memory returns with its chunked downloads in flight;
+    kutacc_b200_synchronize waits for them, and a following call of another shape orders itself after them."""
+    w = W.random_gating_case(seed=8, B=35, S=256, H=8, D=32, with_nb=True, full_mask_rows=2)
+    want = _run(w, device=True)
+    host = runner.HostCase(w)
+    other = W.random_gating_case(seed=9, B=18, S=512, H=8, D=32, with_nb=False)       # chunked too, other chunks
+    tiny = W.random_gating_case(seed=10, B=2, S=64, H=2, D=32, with_nb=True)           # one chunk, staged whole
+    want_other, want_tiny = _run(other, device=True), _run(tiny, device=True)
+    host_other, host_tiny = runner.HostCase(other), runner.HostCase(tiny)
+    api.set_async(True)
+    try:
+        for _ in range(2):                    # the second call finds the downloads of the first in flight
+            api.gating_attention(host.t_x, host.inputs, host.t_bias, host.t_nb, host.weights, host.t_out)
+        for c in (host_other, host, host_tiny):
+            api.gating_attention(c.t_x, c.inputs, c.t_bias, c.t_nb, c.weights, c.t_out)
+        api.synchronize()
+    finally:
+        api.set_async(False)
+    assert np.array_equal(runner.out_to_f32(host.out), want)
+    assert np.array_equal(runner.out_to_f32(host_other.out), want_other)
+    assert np.array_equal(runner.out_to_f32(host_tiny.out), want_tiny)
 
 
 def test_sm_margin_changes_the_grid_not_the_result(kutacc_lib):
