@@ -89,7 +89,8 @@ struct AttnParams {
     int n_qt;                         // query tiles per (b, h)
     int n_items;                      // B * H * n_qt
     int gate_is_sigmoid;              // gate already holds bf16(sigmoid(bf16(x.Wg + bg)))
-    int *counter;                     // next work item of this launch (zero at launch)
+    int *counter;                     // [0] next work item of this launch, [1] CTAs that have finished (both zero at
+                                      // launch; the last CTA to finish zeroes them again)
     float scale;
 };
 
@@ -498,6 +499,17 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         tc_fence_after();
         tmem_dealloc(tmem_base, TMEM_COLS);
     }
+    // The last CTA to get here puts the work counter back to zero for the launch that uses it next (every CTA has
+    // taken its last item number by now: the producer's atomics precede the barrier above).
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(p.counter + 1, 1) == (int)gridDim.x - 1) {
+            __threadfence();
+            p.counter[0] = 0;
+            p.counter[1] = 0;
+            __threadfence();
+        }
+    }
 }
 
 int sm_count_attn()
@@ -522,7 +534,8 @@ bool launch_one(cudaStream_t stream, const CUtensorMap &tq, const CUtensorMap &t
         configured = true;
     }
     const unsigned grid = (unsigned)std::min<int64_t>(p.n_items, 2 * std::max(1, sm_count_attn() - runtime().sm_margin));
-    // one work counter per launch, out of a small ring so that launches in flight on different streams do not share one
+    // one pair of counters per launch, out of a small ring so that launches in flight on different streams do not
+    // share one; zeroed when allocated and by every launch's last CTA
     constexpr int kCounters = 64;
     static int *counters[64] = {};                       // per device
     static unsigned next_counter = 0;
@@ -530,12 +543,14 @@ bool launch_one(cudaStream_t stream, const CUtensorMap &tq, const CUtensorMap &t
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64) return false;
     if (counters[dev] == nullptr) {
-        KUTACC_CUDA(cudaMalloc(&counters[dev], kCounters * sizeof(int)));
-        if (counters[dev] == nullptr) return false;
+        int *c = nullptr;
+        KUTACC_CUDA(cudaMalloc(&c, 2 * kCounters * sizeof(int)));
+        if (c == nullptr) return false;
+        KUTACC_CUDA(cudaMemset(c, 0, 2 * kCounters * sizeof(int)));
+        counters[dev] = c;
     }
     AttnParams q = p;
-    q.counter = counters[dev] + (next_counter++ % kCounters);
-    KUTACC_CUDA(cudaMemsetAsync(q.counter, 0, sizeof(int), stream));
+    q.counter = counters[dev] + 2 * (next_counter++ % kCounters);
     KernelTimer timer__("attn_core", stream);
     attn_tc_kernel<HAS_NB><<<grid, THREADS, SMEM_BYTES, stream>>>(tq, tk, tvt, tnb, q);
     count_launch();

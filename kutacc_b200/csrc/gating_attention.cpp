@@ -113,15 +113,6 @@ static void gating_attention_impl(Tensor &input, int64_t batch, int64_t seq_len,
         rt.out_hazard = false;
     }
 
-    if (pipelined) {
-        // the copy streams may start as soon as the previous work on the runtime stream is done: mark that
-        // point before the small uploads below are queued, so that the first chunk travels beside them
-        CopyPipeline &cp0 = copy_pipeline(1);
-        if (kutacc_check_err_set) return;
-        KUTACC_CUDA(cudaEventRecord((cudaEvent_t)cp0.start, stream));
-        KUTACC_CUDA(cudaStreamWaitEvent((cudaStream_t)cp0.in, (cudaEvent_t)cp0.start, 0));
-        KUTACC_CUDA(cudaStreamWaitEvent((cudaStream_t)cp0.out, (cudaEvent_t)cp0.start, 0));
-    }
     DeviceArg d_x = pipelined ? resolve_out(input.data_ptr(), x_bytes) : resolve_in(input.data_ptr(), x_bytes);
     DeviceArg d_bias = resolve_in(bias.data_ptr(), bias_bytes);
     DeviceArg d_nb = has_nb ? resolve_in(nonbatched_bias.data_ptr(), nb_bytes) : DeviceArg{};
@@ -129,6 +120,16 @@ static void gating_attention_impl(Tensor &input, int64_t batch, int64_t seq_len,
               d_wv = resolve_in(value_w.data_ptr(), w_bytes), d_wg = resolve_in(gating_w.data_ptr(), w_bytes),
               d_wo = resolve_in(output_w.data_ptr(), w_bytes);
     DeviceArg d_bg = resolve_in(gating_b.data_ptr(), b_bytes), d_bo = resolve_in(output_b.data_ptr(), b_bytes);
+    if (pipelined) {
+        // The copy streams start once the previous work on the runtime stream AND the small uploads queued above are
+        // done. (Letting the first chunk travel beside the small uploads was tried: the copy engine then served
+        // some of the small uploads only after every chunk, and the first kernel waited for all of them.)
+        CopyPipeline &cp0 = copy_pipeline(1);
+        if (kutacc_check_err_set) return;
+        KUTACC_CUDA(cudaEventRecord((cudaEvent_t)cp0.start, stream));
+        KUTACC_CUDA(cudaStreamWaitEvent((cudaStream_t)cp0.in, (cudaEvent_t)cp0.start, 0));
+        KUTACC_CUDA(cudaStreamWaitEvent((cudaStream_t)cp0.out, (cudaEvent_t)cp0.start, 0));
+    }
     char *wq_ = (char *)rt.take_workspace(x_bytes), *wk_ = (char *)rt.take_workspace(x_bytes),
          *wv_ = (char *)rt.take_workspace(v_bytes), *wg_ = (char *)rt.take_workspace(x_bytes),
          *wavg = (char *)rt.take_workspace(x_bytes);
@@ -279,16 +280,20 @@ static void gating_attention_impl(Tensor &input, int64_t batch, int64_t seq_len,
         if (kutacc_check_err_set) return;
         cudaStream_t s_in = (cudaStream_t)cp.in, s_out = (cudaStream_t)cp.out;
         const size_t row_bytes = (size_t)S * C * es;
+        // every upload is queued before the first kernel: the copy-in stream then never waits for the host, which
+        // needs a while per chunk to encode tensor maps and launch
+        for (int i = 0; i < nchunks && x_host; ++i) {
+            const int64_t b0 = chunk_begin[i], nbr = chunk_begin[i + 1] - b0;
+            if (nbr <= 0) continue;
+            KUTACC_CUDA(cudaMemcpyAsync((char *)d_x.dev + b0 * row_bytes, (const char *)input.data_ptr() + b0 * row_bytes,
+                                        (size_t)nbr * row_bytes, cudaMemcpyHostToDevice, s_in));
+            KUTACC_CUDA(cudaEventRecord((cudaEvent_t)cp.uploaded[i], s_in));
+        }
         for (int i = 0; i < nchunks && ok; ++i) {
             const int64_t b0 = chunk_begin[i], nbr = chunk_begin[i + 1] - b0;
             if (nbr <= 0) continue;
             if (same_chunks) KUTACC_CUDA(cudaStreamWaitEvent(stream, (cudaEvent_t)cp.downloaded[i], 0));
-            if (x_host) {
-                KUTACC_CUDA(cudaMemcpyAsync((char *)d_x.dev + b0 * row_bytes, (const char *)input.data_ptr() + b0 * row_bytes,
-                                            (size_t)nbr * row_bytes, cudaMemcpyHostToDevice, s_in));
-                KUTACC_CUDA(cudaEventRecord((cudaEvent_t)cp.uploaded[i], s_in));
-                KUTACC_CUDA(cudaStreamWaitEvent(stream, (cudaEvent_t)cp.uploaded[i], 0));
-            }
+            if (x_host) KUTACC_CUDA(cudaStreamWaitEvent(stream, (cudaEvent_t)cp.uploaded[i], 0));
             ok = run_rows(b0, nbr);
             KUTACC_CUDA(cudaEventRecord((cudaEvent_t)cp.computed[i], stream));
             KUTACC_CUDA(cudaStreamWaitEvent(s_out, (cudaEvent_t)cp.computed[i], 0));

@@ -61,14 +61,6 @@ extern "C" void kutacc_af2_global_attention(kutacc_af2_attention_inputs_t *q_bas
     // chunks with upload, kernels and download overlapped on three streams (as in the gated attention).
     const bool pipelined = staged_bytes_needed(x.data_ptr(), x_bytes) != 0 && staged_bytes_needed(o.data_ptr(), out_bytes) != 0 &&
                            B >= 8 && x_bytes >= ((size_t)4 << 20) && out_rs == C;
-    if (pipelined) {
-        // the copy streams may start once the previous work on the runtime stream is done, beside the small uploads
-        CopyPipeline &cp0 = copy_pipeline(1);
-        if (kutacc_check_err_set) return;
-        KUTACC_CUDA(cudaEventRecord((cudaEvent_t)cp0.start, stream));
-        KUTACC_CUDA(cudaStreamWaitEvent((cudaStream_t)cp0.in, (cudaEvent_t)cp0.start, 0));
-        KUTACC_CUDA(cudaStreamWaitEvent((cudaStream_t)cp0.out, (cudaEvent_t)cp0.start, 0));
-    }
     DeviceArg d_x = pipelined ? resolve_out(x.data_ptr(), x_bytes) : resolve_in(x.data_ptr(), x_bytes);
     DeviceArg d_m = resolve_in(mask.data_ptr(), m_bytes);
     DeviceArg d_wq = resolve_in(wq.data_ptr(), wcc), d_wk = resolve_in(wk.data_ptr(), wdc),
@@ -76,6 +68,14 @@ extern "C" void kutacc_af2_global_attention(kutacc_af2_attention_inputs_t *q_bas
               d_wo = resolve_in(wo.data_ptr(), wcc), d_bg = resolve_in(bg.data_ptr(), bb),
               d_bo = resolve_in(bo.data_ptr(), bb);
     DeviceArg d_out = resolve_out(o.data_ptr(), out_bytes);
+    if (pipelined) {
+        // the copy streams start once the previous work on the runtime stream and the small uploads above are done
+        CopyPipeline &cp0 = copy_pipeline(1);
+        if (kutacc_check_err_set) return;
+        KUTACC_CUDA(cudaEventRecord((cudaEvent_t)cp0.start, stream));
+        KUTACC_CUDA(cudaStreamWaitEvent((cudaStream_t)cp0.in, (cudaEvent_t)cp0.start, 0));
+        KUTACC_CUDA(cudaStreamWaitEvent((cudaStream_t)cp0.out, (cudaEvent_t)cp0.start, 0));
+    }
     void *scratch = rt.take_workspace(scratch_bytes);
     if (kutacc_check_err_set) return;
     // the kernels read activations and weights with 4- to 16-byte vector loads
@@ -118,12 +118,16 @@ extern "C" void kutacc_af2_global_attention(kutacc_af2_attention_inputs_t *q_bas
         if (kutacc_check_err_set) return;
         cudaStream_t s_in = (cudaStream_t)cp.in, s_out = (cudaStream_t)cp.out;
         const size_t col_bytes = (size_t)S * C * 2;
-        for (int i = 0; i < nchunks && ok; ++i) {
+        for (int i = 0; i < nchunks; ++i) {                 // every upload is queued before the first kernel
             const int64_t b0 = chunk_begin[i], nb = chunk_begin[i + 1] - b0;
             if (nb <= 0) continue;
             KUTACC_CUDA(cudaMemcpyAsync((char *)d_x.dev + b0 * col_bytes, (const char *)x.data_ptr() + b0 * col_bytes,
                                         (size_t)nb * col_bytes, cudaMemcpyHostToDevice, s_in));
             KUTACC_CUDA(cudaEventRecord((cudaEvent_t)cp.uploaded[i], s_in));
+        }
+        for (int i = 0; i < nchunks && ok; ++i) {
+            const int64_t b0 = chunk_begin[i], nb = chunk_begin[i + 1] - b0;
+            if (nb <= 0) continue;
             KUTACC_CUDA(cudaStreamWaitEvent(stream, (cudaEvent_t)cp.uploaded[i], 0));
             ok = run_cols(b0, nb);
             KUTACC_CUDA(cudaEventRecord((cudaEvent_t)cp.computed[i], stream));
