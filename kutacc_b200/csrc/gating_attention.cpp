@@ -96,7 +96,11 @@ static void gating_attention_impl(Tensor &input, int64_t batch, int64_t seq_len,
     // with LayerNorm: row statistics, four folded weights with their s and t, and (for shapes the folded projection does
     // not cover) a normalised copy of the activations
     const size_t ln_bytes = ln ? (size_t)M * 8 + 4 * (w_bytes + 256) + 8 * (b_bytes + 256) + x_bytes + 1024 : 0;
-    if (!rt.reserve_workspace(4 * (x_bytes + 256) + v_bytes + 256 + nb_pad_bytes + 256 + ln_bytes)) return;
+    // fp32 on the tensor-memory GEMM: operands split into tf32 head and tail (activations: one [M, 2C] buffer that the
+    // projection and, later, the output projection use in turn; five weights [C, 2C])
+    const bool f32_tc = dt == kFP32 && C % 128 == 0 && out_rs % 4 == 0;
+    const size_t f32_bytes = f32_tc ? 2 * x_bytes + 256 + 5 * (2 * w_bytes + 256) : 0;
+    if (!rt.reserve_workspace(4 * (x_bytes + 256) + v_bytes + 256 + nb_pad_bytes + 256 + ln_bytes + f32_bytes)) return;
 
     // The staged output is placed first: its address tells whether downloads of an earlier enqueue-only call, still
     // in flight, read the very block this call will fill. A call of the same shape (same block, same chunks) lets its
@@ -147,6 +151,9 @@ static void gating_attention_impl(Tensor &input, int64_t batch, int64_t seq_len,
         }
         x_norm = (char *)rt.take_workspace(x_bytes);
     }
+    char *a_split = f32_tc ? (char *)rt.take_workspace(2 * x_bytes) : nullptr;
+    void *w_split[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
+    for (int i = 0; i < 5 && f32_tc; ++i) w_split[i] = rt.take_workspace(2 * w_bytes);
     if (kutacc_check_err_set) return;
 
     const float scale = (float)(1 / std::sqrt((double)head_size));  // gating_attention.cpp:68
@@ -182,6 +189,13 @@ static void gating_attention_impl(Tensor &input, int64_t batch, int64_t seq_len,
                                                 ln_s, ln_t, (int)C, (int)C);
         KUTACC_CHECK(folded, "gating_attention with LayerNorm: weight folding failed");
         if (kutacc_check_err_set) return;
+    }
+
+    bool f32_tc_ok = f32_tc && aligned16(d_x.dev) && aligned16(d_out.dev);
+    if (f32_tc_ok) {
+        const void *w_in[5] = {d_wq.dev, d_wk.dev, d_wv.dev, d_wg.dev, d_wo.dev};
+        for (int i = 0; i < 5 && f32_tc_ok; ++i)
+            f32_tc_ok = dev::launch_split_tf32(stream, w_in[i], C, w_split[i], C, (int)C);
     }
 
     // kernel sequence for batch rows [b0, b0 + nb): every buffer is batch-major, so a chunk is an offset
@@ -241,19 +255,35 @@ static void gating_attention_impl(Tensor &input, int64_t batch, int64_t seq_len,
         } else {
             const dev::ElemType et = dt == kFP32 ? dev::kElemF32 : dev::kElemBF16;
             char *v_c = wv_ + b0 * row_bytes;
-            ok = dev::launch_gemm_generic(stream, et, x_c, C, d_wq.dev, C, nullptr, 0.f, q_c, C, Mc, C, C);
-            ok = ok && dev::launch_gemm_generic(stream, et, x_c, C, d_wk.dev, C, nullptr, 0.f, k_c, C, Mc, C, C);
-            ok = ok && dev::launch_gemm_generic(stream, et, x_c, C, d_wv.dev, C, nullptr, 0.f, v_c, C, Mc, C, C);
-            ok = ok && dev::launch_gemm_generic(stream, et, x_c, C, d_wg.dev, C, (const float *)d_bg.dev, 0.f, g_c, C,
-                                                Mc, C, C);
+            char *as_c = f32_tc_ok ? a_split + 2 * b0 * row_bytes : nullptr;
+            bool projected = false;
+            if (f32_tc_ok) {
+                // fp32: all four projections in one pass of the tensor-memory GEMM over the split activations
+                const float *pb[4] = {nullptr, nullptr, nullptr, (const float *)d_bg.dev};
+                void *po[4] = {q_c, k_c, v_c, g_c};
+                projected = dev::launch_split_tf32(stream, x_c, C, as_c, Mc, (int)C) &&
+                            dev::tcgen05_gemm_tf32x3(stream, as_c, w_split, pb, po, C, Mc, (int)C, (int)C, 4);
+            }
+            ok = projected || dev::launch_gemm_generic(stream, et, x_c, C, d_wq.dev, C, nullptr, 0.f, q_c, C, Mc, C, C);
+            ok = ok && (projected || dev::launch_gemm_generic(stream, et, x_c, C, d_wk.dev, C, nullptr, 0.f, k_c, C, Mc, C, C));
+            ok = ok && (projected || dev::launch_gemm_generic(stream, et, x_c, C, d_wv.dev, C, nullptr, 0.f, v_c, C, Mc, C, C));
+            ok = ok && (projected || dev::launch_gemm_generic(stream, et, x_c, C, d_wg.dev, C, (const float *)d_bg.dev, 0.f,
+                                                              g_c, C, Mc, C, C));
             ok = ok && ((dt == kFP32 && dev::launch_attn_f32(stream, q_c, k_c, v_c, g_c, bias_c, bias_s0,
                                                               has_nb ? d_nb.dev : nullptr, nb_s0, nb_s1, a_c, (int)nbr,
                                                               (int)S, (int)H, (int)D, scale)) ||
                         dev::launch_attn_generic(stream, et, q_c, k_c, v_c, g_c, bias_c, bias_s0,
                                                  has_nb ? d_nb.dev : nullptr, nb_s0, nb_s1, a_c, (int)nbr, (int)S, (int)H,
                                                  (int)D, scale));
-            ok = ok && dev::launch_gemm_generic(stream, et, a_c, C, d_wo.dev, C, (const float *)d_bo.dev, 0.f, out_c,
-                                                out_rs, Mc, C, C);
+            bool out_done = false;
+            if (ok && f32_tc_ok) {
+                const float *pb[1] = {(const float *)d_bo.dev};
+                void *po[1] = {out_c};
+                out_done = dev::launch_split_tf32(stream, a_c, C, as_c, Mc, (int)C) &&
+                           dev::tcgen05_gemm_tf32x3(stream, as_c, &w_split[4], pb, po, out_rs, Mc, (int)C, (int)C, 1);
+            }
+            ok = ok && (out_done || dev::launch_gemm_generic(stream, et, a_c, C, d_wo.dev, C, (const float *)d_bo.dev, 0.f,
+                                                             out_c, out_rs, Mc, C, C));
         }
         return ok;
     };

@@ -49,6 +49,14 @@ bool tcgen05_batched_nt_bf16(cudaStream_t stream, const void *a, int64_t a_row_s
                              const void *w, int64_t w_row_stride, int64_t w_batch_stride, void *out,
                              int64_t out_row_stride, int64_t out_batch_stride, int B, int M, int N, int K);
 
+// fp32 GEMM on tcgen05 (gemm_tf32_tcgen05.cu): operands pre-split into tf32 head and tail, stored as rows
+// [hi(0..K) | lo(0..K)] by launch_split_tf32 (src [rows, K] fp32 with row stride src_ld; dst [rows, 2K] dense).
+// out_i[m, :] = a[m, :] . w_i^T (+ bias_i) for up to four weight matrices [N, K] in one pass over a; out row stride
+// ldo. Needs N % 128 == 0, K % 32 == 0, 16-byte aligned pointers. False when the shape is not covered.
+bool launch_split_tf32(cudaStream_t stream, const void *src, int64_t src_ld, void *dst, int64_t rows, int K);
+bool tcgen05_gemm_tf32x3(cudaStream_t stream, const void *a_split, const void *const *w_split, const float *const *bias,
+                         void *const *out, int64_t ldo, int64_t M, int N, int K, int nseg);
+
 // ---- triangle multiplication: element-wise steps and fallbacks (tm_kernels.cu) ------------------------
 // proj[c, b, i] = bf16((f32(proj) * f32(mask[b, i])) * sigmoid(f32(gate[c, b, i]))) in place; strides in elements.
 bool launch_tm_mask_gate(cudaStream_t stream, void *proj, const void *gate, const void *mask, int64_t c_i, int64_t n_res,

@@ -52,6 +52,27 @@ bool make_tensor_map_bf16_3d(CUtensorMap *map, const void *base, uint64_t d0, ui
     return r == CUDA_SUCCESS;
 }
 
+bool make_tensor_map_2d(CUtensorMap *map, const void *base, int elem_bytes, uint64_t d0, uint64_t d1, uint64_t stride1,
+                        uint32_t box0, uint32_t box1, int swizzle_bytes)
+{
+    EncodeTiledFn fn = encode_fn();
+    if (!fn || (elem_bytes != 2 && elem_bytes != 4)) return false;
+    cuuint64_t dims[2] = {d0, d1};
+    cuuint64_t strides[1] = {stride1 * (cuuint64_t)elem_bytes};
+    cuuint32_t box[2] = {box0, box1};
+    cuuint32_t estr[2] = {1, 1};
+    CUtensorMapSwizzle sw = swizzle_bytes == 128  ? CU_TENSOR_MAP_SWIZZLE_128B
+                            : swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
+                            : swizzle_bytes == 32 ? CU_TENSOR_MAP_SWIZZLE_32B
+                                                  : CU_TENSOR_MAP_SWIZZLE_NONE;
+    CUresult r = fn(map, elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                    const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    KUTACC_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with ", (int)r, " dims ", d0, "x", d1, " stride ", stride1,
+                 " box ", box0, "x", box1, " element bytes ", elem_bytes);
+    return r == CUDA_SUCCESS;
+}
+
 KernelErrorWord &kernel_error_word()
 {
     static KernelErrorWord w;

@@ -16,6 +16,10 @@ bool make_tensor_map_bf16_3d(CUtensorMap *map, const void *base, uint64_t d0, ui
                              uint64_t stride1, uint64_t stride2, uint32_t box0, uint32_t box1, int swizzle_bytes,
                              uint32_t box2 = 1);
 
+// rank-2 tensor [d1][d0] of 2-byte (bf16) or 4-byte (fp32, raw bits) elements, row stride in ELEMENTS, box [box1][box0]
+bool make_tensor_map_2d(CUtensorMap *map, const void *base, int elem_bytes, uint64_t d0, uint64_t d1, uint64_t stride1,
+                        uint32_t box0, uint32_t box1, int swizzle_bytes);
+
 // Host-visible error word written by kernels whose bounded waits ran out (0 = none). The pointer is a
 // device-accessible alias of pinned host memory; the host reads *host after synchronising.
 struct KernelErrorWord {

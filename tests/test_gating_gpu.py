@@ -56,6 +56,24 @@ def test_fp32_matches_exact_oracle(kutacc_lib, B, S, H, D, with_nb):
     assert helpers.rel_err(got, helpers.oracle_exact(w)) <= helpers.FP32_TOL
 
 
+@pytest.mark.parametrize("B,S,H,D", [(3, 70, 4, 32), (2, 129, 8, 32), (1, 300, 8, 16)])
+def test_fp32_projections_run_on_the_tensor_memory_gemm(kutacc_lib, B, S, H, D):
+    """fp32 with nchannels a multiple of 128: the projections and the output projection go through the tcgen05 tf32
+    GEMM on operands split into head and tail (three products per multiply), which must stay at fp32 accuracy; the
+    row count B * S is not a multiple of the 128-row tile."""
+    w = W.random_gating_case(seed=400 + S, B=B, S=S, H=H, D=D, dtype="fp32", with_nb=True, full_mask_rows=0)
+    case = runner.DeviceCase(w)
+    api.set_profile(True)
+    api.profile_read()
+    got = runner.out_to_f32(case.run())
+    names = [k for k, _ in api.profile_read()]
+    api.set_profile(False)
+    assert names.count("gemm_tf32x3_tc") == 2 and "gemm_tf32x3" not in names
+    assert helpers.rel_err(got, helpers.oracle_exact(w)) <= helpers.FP32_TOL
+    # the host-buffer call takes the same kernels chunk by chunk
+    assert np.array_equal(_run(w, device=False), got)
+
+
 def test_fully_masked_row_is_uniform(kutacc_lib):
     # every key of batch row 0 carries -1e9: the softmax must be uniform, not NaN or zero
     w = W.random_gating_case(seed=5, B=2, S=128, H=2, D=32, with_nb=True, full_mask_rows=1)
