@@ -75,6 +75,7 @@ struct GemmParams {
     int relu;               // non-zero: max(0, .) after the bias, before the bf16 rounding
     const float2 *ln_stats; // F_LN: (mean, rstd) of every row of X, [B * S]
     const float *ln_s[4];   // F_LN: rounding residue of the folded weight rows, per segment
+    int rotate;             // non-zero: column tile of tile t is rotated by t / gridDim.x (see tile_of)
     int sigmoid_mask;       // bit i set: segment i stores bf16(sigmoid(bf16(y))) (the gate of the attention, whose
                             // reference rounds the gate to bf16 before the sigmoid: gating_attention.cpp:62-66,134-147)
     int *err;
@@ -127,6 +128,16 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p)
     const int n_tiles = n_tiles_seg * p.nseg;
     const int num_tiles = p.B * s_tiles * n_tiles;
     const int nk = (p.K + BK - 1) / BK;                 // columns past K are zero-filled by TMA
+    // Tile t covers row tile t / n_tiles and column tile t % n_tiles. A CTA walks t = blockIdx.x + k * gridDim.x, so
+    // when the grid size is a multiple of n_tiles it would meet the same column tile, i.e. the same segment, every
+    // time, and the CTAs that only get the gate segment (a sigmoid per element) would finish long after the others.
+    // With `rotate` the column tile is shifted by k, which is constant over the n_tiles tiles of a row tile (they
+    // lie in one block of gridDim.x consecutive t), so the map stays one to one and every CTA meets every segment.
+    auto tile_of = [&](int tile, int &m_tile, int &n_tile) {
+        m_tile = tile / n_tiles;
+        n_tile = tile % n_tiles;
+        if (p.rotate) n_tile = (n_tile + tile / (int)gridDim.x) % n_tiles;
+    };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < NSTAGE; ++s) {
@@ -156,7 +167,8 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p)
             int it = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-                const int m_tile = tile / n_tiles, n_tile = tile % n_tiles;
+                int m_tile, n_tile;
+                tile_of(tile, m_tile, n_tile);
                 const int b = m_tile / s_tiles, s0 = (m_tile % s_tiles) * BM;
                 const int seg = n_tile / n_tiles_seg, n0 = (n_tile % n_tiles_seg) * BN;
                 const CUtensorMap *wmap = &maps.w[seg];
@@ -215,7 +227,8 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p)
         int tcount = 0, nstore = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
-            const int m_tile = tile / n_tiles, n_tile = tile % n_tiles;
+            int m_tile, n_tile;
+            tile_of(tile, m_tile, n_tile);
             const int b = m_tile / s_tiles, s0 = (m_tile % s_tiles) * BM;
             const int seg = n_tile / n_tiles_seg, n0 = (n_tile % n_tiles_seg) * BN;
             const int a = tcount % ACC_STAGES;
@@ -383,8 +396,11 @@ bool launch(cudaStream_t stream, const GemmMaps &maps, const GemmParams &p, cons
     const int s_tiles = (p.S + BM - 1) / BM;
     const int64_t tiles = (int64_t)p.B * s_tiles * ((p.seg_n + BN - 1) / BN) * p.nseg;
     const unsigned grid = (unsigned)std::min<int64_t>(tiles, 2 * std::max(1, sm_count() - runtime().sm_margin));
+    GemmParams q = p;
+    const int n_tiles = ((p.seg_n + BN - 1) / BN) * p.nseg;
+    q.rotate = (n_tiles > 1 && grid % (unsigned)n_tiles == 0) ? 1 : 0;
     KernelTimer timer__(name, stream);
-    gemm_tcgen05_kernel<FEAT><<<grid, THREADS, SMEM_BYTES, stream>>>(maps, p);
+    gemm_tcgen05_kernel<FEAT><<<grid, THREADS, SMEM_BYTES, stream>>>(maps, q);
     count_launch();
     return true;
 }
