@@ -83,6 +83,29 @@ def test_fully_masked_row_is_uniform(kutacc_lib):
     assert helpers.rel_err(got[0], ref[0]) <= helpers.BF16_TOL
 
 
+def test_running_max_that_grows_late_in_the_key_sequence(kutacc_lib):
+    """The kernel forms probabilities against a running max that it raises lazily. Rows whose first keys are masked
+    (-1e9) and whose later keys are not make the max grow by far more than the 2^8 slack at a later tile: in the
+    first or in the second group of 16 keys of a thread's half of the tile (the second group also rescales the
+    probabilities the first one has already stored), and large pair-bias steps do the same without any mask."""
+    w = W.random_gating_case(seed=21, B=6, S=320, H=4, D=32, with_nb=True, mask_frac=0.0)
+    A = w.arrays
+    mask = np.ones((w.B, w.S), np.float32)
+    mask[0, :80] = 0.0           # tile 1: keys 64..79 masked, 80.. open -> growth in the second group of half 0
+    mask[1, :96] = 0.0           # tile 1: half 0 masked whole, growth in the first group of half 1
+    mask[2, :200] = 0.0          # growth in tile 3
+    mask[3, 10:300] = 0.0        # open keys first, a long masked stretch, open again
+    mask[4, :] = 0.0             # fully masked
+    A["mask"] = mask
+    A["bias"] = np.ascontiguousarray(1e9 * (mask - 1.0), np.float32)
+    nb = A["nb"].copy()
+    nb[:, :, 150:170] += 40.0    # a step of 40 in the logits late in the sequence (row 5 has no mask at all)
+    A["nb"] = W.as_f32(W.bf16_bits(nb))
+    got = _run(w)
+    assert np.isfinite(got).all()
+    assert helpers.rel_err(got, helpers.oracle_faithful(w)) <= helpers.BF16_TOL
+
+
 def test_host_pointers_give_the_same_bits_as_device_pointers(kutacc_lib):
     w = W.random_gating_case(seed=7, B=3, S=96, H=4, D=32, with_nb=True)
     dev = _run(w, device=True)
