@@ -56,6 +56,21 @@ extern "C" void kutacc_af2_linear(kutacc_tensor_h act_h, kutacc_tensor_h weight_
                                            (int)k);
         if (kutacc_check_err_set) return;
     }
+    if (dt == kFP32 && beta == 0 && a16 && k % 32 == 0 && n % 128 == 0 && lda % 4 == 0 && ldw % 4 == 0 && k <= INT32_MAX / 2 &&
+        n <= INT32_MAX && (((uintptr_t)d_r.dev | (uintptr_t)d_b.dev) & 15u) == 0) {
+        // fp32 on the tensor-memory GEMM: both operands split into tf32 head and tail in the workspace
+        const size_t as_bytes = (size_t)m * 2 * k * 4, ws_bytes = (size_t)n * 2 * k * 4;
+        if (rt.reserve_workspace(as_bytes + ws_bytes + 512)) {
+            void *a_split = rt.take_workspace(as_bytes), *w_split = rt.take_workspace(ws_bytes);
+            const void *wp[1] = {w_split};
+            const float *bp[1] = {(const float *)d_b.dev};
+            void *op[1] = {d_r.dev};
+            ok = a_split && w_split && dev::launch_split_tf32(stream, d_a.dev, lda, a_split, m, (int)k) &&
+                 dev::launch_split_tf32(stream, d_w.dev, ldw, w_split, n, (int)k) &&
+                 dev::tcgen05_gemm_tf32x3(stream, a_split, wp, bp, op, n, m, (int)n, (int)k, 1);
+        }
+        if (kutacc_check_err_set) return;
+    }
     if (!ok && dt == kBF16 && beta == 0 && a16 && k % 64 == 0 && n % 64 == 0 && lda % 8 == 0 && ldw == k) {
         ok = dev::launch_linear_bias_bf16(stream, d_a.dev, lda, d_w.dev, (const float *)d_b.dev, d_r.dev, n, m, (int)n,
                                           (int)k);

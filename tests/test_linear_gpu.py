@@ -43,6 +43,30 @@ def test_linear_fp32(kutacc_lib):
     assert helpers.rel_err(tr.cpu().numpy(), O.linear_exact(a, w, b)) <= helpers.FP32_TOL
 
 
+@pytest.mark.parametrize("M,N,K,bias", [(300, 128, 96, True), (1000, 384, 256, False), (77, 256, 32, True)])
+def test_linear_fp32_on_the_tensor_memory_gemm(kutacc_lib, M, N, K, bias):
+    # fp32 with n % 128 == 0 and k % 32 == 0: tcgen05 kind::tf32 on operands split into head and tail; large values
+    # next to small ones in one row show a dropped tail at once
+    rng = np.random.default_rng(M + N)
+    a = (rng.standard_normal((M, K)) * rng.choice([1e-3, 1.0, 300.0], (M, K))).astype(np.float32)
+    w = (rng.standard_normal((N, K)) / np.sqrt(K)).astype(np.float32)
+    b = rng.standard_normal(N).astype(np.float32) if bias else None
+    ta, tw = torch.from_numpy(a).to(DEV), torch.from_numpy(w).to(DEV)
+    tb = torch.from_numpy(b).to(DEV) if bias else None
+    tr = torch.full((M, N), 7.0, dtype=torch.float32, device=DEV)
+    api.set_profile(True)
+    api.profile_read()
+    api.linear(api.tensor(ta), api.tensor(tw), tb.data_ptr() if bias else None, api.tensor(tr), 0)
+    names = [k for k, _ in api.profile_read()]
+    api.set_profile(False)
+    assert "gemm_tf32x3_tc" in names
+    ref = O.linear_exact(a, w, b)
+    got = tr.cpu().numpy()
+    # against the magnitude of the terms of each dot product, not of the (possibly cancelling) result
+    scale = (np.abs(a).astype(np.float64) @ np.abs(w).astype(np.float64).T).max()
+    assert np.abs(got.astype(np.float64) - ref).max() <= 5e-6 * scale          # a dropped tail term would cost 2^-11
+
+
 @pytest.mark.parametrize("R,Nk,Cz,H", [(8, 384, 128, 4), (5, 100, 128, 8), (3, 33, 64, 4), (2, 50, 40, 3)])
 def test_pair_bias_matches_linear_then_permute(kutacc_lib, R, Nk, Cz, H):
     rng = np.random.default_rng(R * Nk)
