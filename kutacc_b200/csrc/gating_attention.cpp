@@ -194,8 +194,7 @@ static void gating_attention_impl(Tensor &input, int64_t batch, int64_t seq_len,
     bool f32_tc_ok = f32_tc && aligned16(d_x.dev) && aligned16(d_out.dev);
     if (f32_tc_ok) {
         const void *w_in[5] = {d_wq.dev, d_wk.dev, d_wv.dev, d_wg.dev, d_wo.dev};
-        for (int i = 0; i < 5 && f32_tc_ok; ++i)
-            f32_tc_ok = dev::launch_split_tf32(stream, w_in[i], C, w_split[i], C, (int)C);
+        f32_tc_ok = dev::launch_split_tf32_many(stream, 5, w_in, C, w_split, C, (int)C);
     }
 
     // kernel sequence for batch rows [b0, b0 + nb): every buffer is batch-major, so a chunk is an offset

@@ -233,10 +233,17 @@ __global__ void __launch_bounds__(THREADS, 2) gemm_tf32x3_tc_kernel(const __grid
     }
 }
 
+// up to eight matrices of the same shape per launch (blockIdx.y picks one): the five weights of an attention call
+struct SplitArgs {
+    const float *src[8];
+    float *dst[8];
+};
+
 // dst[r, 0..K) = tf32 head of src[r, :], dst[r, K..2K) = src - head (fp32, at most 12 significant bits)
-__global__ void __launch_bounds__(256) split_tf32_kernel(const float *__restrict__ src, int64_t src_ld, float *__restrict__ dst,
-                                                         int64_t rows, int K)
+__global__ void __launch_bounds__(256) split_tf32_kernel(const SplitArgs args, int64_t src_ld, int64_t rows, int K)
 {
+    const float *__restrict__ src = args.src[blockIdx.y];
+    float *__restrict__ dst = args.dst[blockIdx.y];
     const int kv = K / 4;
     const int64_t total = rows * kv;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
@@ -275,15 +282,28 @@ int sm_count_tf32()
 
 }  // namespace
 
-bool launch_split_tf32(cudaStream_t stream, const void *src, int64_t src_ld, void *dst, int64_t rows, int K)
+bool launch_split_tf32_many(cudaStream_t stream, int count, const void *const *src, int64_t src_ld, void *const *dst,
+                            int64_t rows, int K)
 {
-    if (rows <= 0 || K <= 0 || K % 4 != 0 || src_ld % 4 != 0 || ((((uintptr_t)src | (uintptr_t)dst) & 15u) != 0)) return false;
+    if (count < 1 || count > 8 || rows <= 0 || K <= 0 || K % 4 != 0 || src_ld % 4 != 0) return false;
+    SplitArgs a;
+    for (int i = 0; i < 8; ++i) {
+        const int j = i < count ? i : 0;
+        if ((((uintptr_t)src[j] | (uintptr_t)dst[j]) & 15u) != 0) return false;
+        a.src[i] = (const float *)src[j];
+        a.dst[i] = (float *)dst[j];
+    }
     const int64_t total = rows * (K / 4);
-    const unsigned grid = (unsigned)std::min<int64_t>((total + 255) / 256, (int64_t)sm_count_tf32() * 16);
+    const unsigned gx = (unsigned)std::min<int64_t>((total + 255) / 256, (int64_t)sm_count_tf32() * 16);
     KernelTimer timer__("split_tf32", stream);
-    split_tf32_kernel<<<grid, 256, 0, stream>>>((const float *)src, src_ld, (float *)dst, rows, K);
+    split_tf32_kernel<<<dim3(gx, (unsigned)count), 256, 0, stream>>>(a, src_ld, rows, K);
     count_launch();
     return true;
+}
+
+bool launch_split_tf32(cudaStream_t stream, const void *src, int64_t src_ld, void *dst, int64_t rows, int K)
+{
+    return launch_split_tf32_many(stream, 1, &src, src_ld, &dst, rows, K);
 }
 
 bool tcgen05_gemm_tf32x3(cudaStream_t stream, const void *a_split, const void *const *w_split, const float *const *bias,

@@ -54,6 +54,9 @@ bool tcgen05_batched_nt_bf16(cudaStream_t stream, const void *a, int64_t a_row_s
 // out_i[m, :] = a[m, :] . w_i^T (+ bias_i) for up to four weight matrices [N, K] in one pass over a; out row stride
 // ldo. Needs N % 128 == 0, K % 32 == 0, 16-byte aligned pointers. False when the shape is not covered.
 bool launch_split_tf32(cudaStream_t stream, const void *src, int64_t src_ld, void *dst, int64_t rows, int K);
+// the same for up to eight matrices of one shape in a single launch
+bool launch_split_tf32_many(cudaStream_t stream, int count, const void *const *src, int64_t src_ld, void *const *dst,
+                            int64_t rows, int K);
 bool tcgen05_gemm_tf32x3(cudaStream_t stream, const void *a_split, const void *const *w_split, const float *const *bias,
                          void *const *out, int64_t ldo, int64_t M, int N, int K, int nseg);
 
