@@ -534,11 +534,14 @@ bool launch_one(cudaStream_t stream, const CUtensorMap &tq, const CUtensorMap &t
         configured = true;
     }
     const unsigned grid = (unsigned)std::min<int64_t>(p.n_items, 2 * std::max(1, sm_count_attn() - runtime().sm_margin));
-    // one pair of counters per launch, out of a small ring so that launches in flight on different streams do not
-    // share one; zeroed when allocated and by every launch's last CTA
+    // One pair of counters per STREAM: launches on one stream run one after another, so they can share a pair (the
+    // last CTA of a launch zeroes it again), while launches on different streams may overlap and must not. Up to 63
+    // streams per device get a pair of their own; further streams share the last pair, which is only safe while they
+    // do not run attention kernels at the same time.
     constexpr int kCounters = 64;
     static int *counters[64] = {};                       // per device
-    static unsigned next_counter = 0;
+    static cudaStream_t owner[64][kCounters] = {};
+    static int owners[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64) return false;
@@ -549,8 +552,22 @@ bool launch_one(cudaStream_t stream, const CUtensorMap &tq, const CUtensorMap &t
         KUTACC_CUDA(cudaMemset(c, 0, 2 * kCounters * sizeof(int)));
         counters[dev] = c;
     }
+    int slot = -1;
+    for (int i = 0; i < owners[dev]; ++i)
+        if (owner[dev][i] == stream) {
+            slot = i;
+            break;
+        }
+    if (slot < 0) {
+        if (owners[dev] < kCounters - 1) {
+            slot = owners[dev]++;
+            owner[dev][slot] = stream;
+        } else {
+            slot = kCounters - 1;
+        }
+    }
     AttnParams q = p;
-    q.counter = counters[dev] + 2 * (next_counter++ % kCounters);
+    q.counter = counters[dev] + 2 * slot;
     KernelTimer timer__("attn_core", stream);
     attn_tc_kernel<HAS_NB><<<grid, THREADS, SMEM_BYTES, stream>>>(tq, tk, tvt, tnb, q);
     count_launch();
