@@ -53,7 +53,7 @@ __global__ void __launch_bounds__(256) ln_stats_vec_kernel(const __nv_bfloat16 *
     const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int64_t step = (int64_t)gridDim.x * (blockDim.x >> 5) * R;
     const int nvec = size / 8;
-    const float n = (float)size;
+    const float inv_n = 1.0f / (float)size;
     const uint4 zero = make_uint4(0, 0, 0, 0);
     // a warp's lanes stay together (the shuffles below are warp-wide): the loop runs while ANY group has a row
     for (int64_t base = warp * R; base < rows; base += NR * step) {
@@ -93,8 +93,12 @@ __global__ void __launch_bounds__(256) ln_stats_vec_kernel(const __nv_bfloat16 *
         if (l == 0) {
 #pragma unroll
             for (int r = 0; r < NR; ++r)
-                if (row[r] < rows)
-                    stats[row[r]] = make_float2(s[r] / n + d[r], 1.0f / sqrtf(fmaxf((q[r] - s[r] * s[r] / n) / n, 0.f) + eps));
+                if (row[r] < rows) {
+                    // a reciprocal of n taken once and the hardware reciprocal square root (2 ulp): IEEE divisions
+                    // and a square root per row made this kernel instruction-bound at twice its memory time
+                    const float var = fmaxf((q[r] - s[r] * s[r] * inv_n) * inv_n, 0.f);
+                    stats[row[r]] = make_float2(fmaf(s[r], inv_n, d[r]), rsqrtf(var + eps));
+                }
         }
     }
 }
