@@ -259,7 +259,10 @@ KUTACC_B200_API void kutacc_b200_clear_error(void);
 
 /* Device selection (default: current CUDA device) and stream (default: the legacy default
  * stream). Operators are synchronous unless kutacc_b200_set_async(1) was called, in which case
- * calls with device-resident tensors only enqueue work on the stream.
+ * calls only enqueue work on the stream. A result in HOST memory is then complete after
+ * kutacc_b200_synchronize(): kutacc_af2_gating_attention with a large host `out` downloads its rows chunk by chunk
+ * on a copy stream of the library and returns while those downloads run, so that the kernels of a following call
+ * start beside them (the library orders every later use of its staging pool after them).
  * The library has ONE workspace and ONE staging pool, handed out from their start on every call; only the
  * order of work on a stream protects them. In enqueue-only mode a caller that switches streams between calls
  * must therefore order the streams itself (an event from the old stream that the new one waits for) unless the
