@@ -276,6 +276,11 @@ KUTACC_B200_API void kutacc_b200_set_async(int enabled);
  * slab is computed) can ask them to leave `sms` SMs free, 0..64, so that the collective's CTAs find room
  * at once instead of waiting for the persistent CTAs to finish. Default 0. */
 KUTACC_B200_API void kutacc_b200_set_sm_margin(int sms);
+/* The pair bias of the NEXT kutacc_af2_gating_attention call (or its LayerNorm-fused form) is still being produced on
+ * another stream, an all-gather of its row blocks for instance: `cuda_event` (a cudaEvent_t recorded there) is what
+ * the call waits for, on the runtime stream, between its projections and its attention kernel, so the projections
+ * run beside that work. The event is used by one call and then forgotten; pass NULL to clear it. */
+KUTACC_B200_API void kutacc_b200_set_pair_bias_event(void *cuda_event);
 KUTACC_B200_API void kutacc_b200_synchronize(void);
 
 /* Device memory helpers for callers without a CUDA runtime of their own. */

@@ -30,7 +30,7 @@ EXPORTS = [
     "kutacc_af2_triangle_multiplication_gate_and_out_linear", "kutacc_af2_triangle_multiplication_last",
     # part 2: additions
     "kutacc_b200_tensor_create", "kutacc_b200_tensor_destroy", "kutacc_b200_error_set", "kutacc_b200_last_error",
-    "kutacc_b200_clear_error", "kutacc_b200_set_stream", "kutacc_b200_set_async", "kutacc_b200_set_sm_margin", "kutacc_b200_synchronize",
+    "kutacc_b200_clear_error", "kutacc_b200_set_stream", "kutacc_b200_set_async", "kutacc_b200_set_sm_margin", "kutacc_b200_set_pair_bias_event", "kutacc_b200_synchronize",
     "kutacc_b200_device_malloc", "kutacc_b200_device_free", "kutacc_b200_memcpy_h2d", "kutacc_b200_memcpy_d2h",
     "kutacc_b200_workspace_bytes", "kutacc_b200_release_workspace", "kutacc_b200_launch_count",
     "kutacc_b200_set_profile", "kutacc_b200_profile_read", "kutacc_b200_comm_unique_id", "kutacc_b200_comm_init_with_id", "kutacc_b200_pair_bias",
@@ -150,6 +150,8 @@ def lib() -> C.CDLL:
     L.kutacc_b200_set_async.restype = None
     L.kutacc_b200_set_sm_margin.argtypes = [C.c_int]
     L.kutacc_b200_set_sm_margin.restype = None
+    L.kutacc_b200_set_pair_bias_event.argtypes = [C.c_void_p]
+    L.kutacc_b200_set_pair_bias_event.restype = None
     L.kutacc_b200_synchronize.restype = None
     L.kutacc_b200_device_malloc.argtypes = [C.c_size_t]
     L.kutacc_b200_device_malloc.restype = vp
@@ -244,6 +246,12 @@ def set_async(enabled: bool) -> None:
 
 def set_sm_margin(sms: int) -> None:
     lib().kutacc_b200_set_sm_margin(int(sms))
+
+
+def set_pair_bias_event(event) -> None:
+    """The next gated-attention call waits for `event` (a torch.cuda.Event recorded on the stream that still
+    produces its pair bias, or None) between its projections and its attention kernel."""
+    lib().kutacc_b200_set_pair_bias_event(C.c_void_p(event.cuda_event) if event is not None else None)
 
 
 def synchronize() -> None:

@@ -72,6 +72,7 @@ struct Runtime {
     void *stream = nullptr;   // cudaStream_t
     bool async = false;
     int sm_margin = 0;        // SMs the persistent kernels leave free (for a collective running beside them)
+    void *pair_bias_event = nullptr;   // cudaEvent_t the next gated-attention call waits for before its attention kernel
 
     char *ws_base = nullptr;
     size_t ws_cap = 0, ws_off = 0;

@@ -163,11 +163,22 @@ static void gating_attention_impl(Tensor &input, int64_t batch, int64_t seq_len,
                       aligned16(d_wg.dev) && aligned16(d_wo.dev) && (out_rs % 2 == 0) &&
                       (((uintptr_t)d_out.dev & 3u) == 0);
 
+    // The pair bias may still be on its way (kutacc_b200_set_pair_bias_event): everything that reads it waits for the
+    // event, once. The projections do not read it, so they are queued first where the pair bias is used as it lies.
+    void *nb_event = rt.pair_bias_event;
+    rt.pair_bias_event = nullptr;
+    auto wait_for_pair_bias = [&]() {
+        if (nb_event) KUTACC_CUDA(cudaStreamWaitEvent(stream, (cudaEvent_t)nb_event, 0));
+        nb_event = nullptr;
+    };
+    if (!has_nb || staged_bytes_needed(nonbatched_bias.data_ptr(), nb_bytes) != 0) nb_event = nullptr;   // nothing to wait for / host data
+
     // The TMA loads of the pair bias need 16-byte aligned rows. A pair bias whose strides are not
     // multiples of 8 elements is first copied into the workspace with padded rows.
     const void *nb_dev = has_nb ? d_nb.dev : nullptr;
     int64_t nb_sh = nb_s0, nb_sq = nb_s1;
     if (fast && has_nb && ((nb_s0 % 8) || (nb_s1 % 8) || !aligned16(d_nb.dev))) {
+        wait_for_pair_bias();                         // the re-pitching copy reads it
         KUTACC_CUDA(cudaMemcpy2DAsync(nb_pad, (size_t)s_pad8 * 2, d_nb.dev, (size_t)nb_s1 * 2, (size_t)S * 2,
                                       (size_t)(nb_s0 == S * nb_s1 ? H * S : S), cudaMemcpyDeviceToDevice, stream));
         for (int64_t hh = 1; nb_s0 != S * nb_s1 && hh < H; ++hh)
@@ -241,6 +252,7 @@ static void gating_attention_impl(Tensor &input, int64_t batch, int64_t seq_len,
                      dev::launch_proj_qkvg_bf16(stream, x_c, d_wq.dev, d_wk.dev, d_wv.dev, d_wg.dev,
                                                 (const float *)d_bg.dev, q_c, k_c, v_c, g_c, (int)nbr, (int)S, (int)H,
                                                 (int)D, 1.0f);
+            wait_for_pair_bias();
             if (ok && v_key_major)
                 ok = dev::tcgen05_attn_core_bf16(stream, q_c, k_c, v_km, s_pad8, g_c, bias_c, bias_s0, nb_dev, nb_sh,
                                                  nb_sq, a_c, (int)nbr, (int)S, (int)H, (int)D, scale, /*gate_is_sigmoid=*/true);
@@ -268,6 +280,7 @@ static void gating_attention_impl(Tensor &input, int64_t batch, int64_t seq_len,
             ok = ok && (projected || dev::launch_gemm_generic(stream, et, x_c, C, d_wv.dev, C, nullptr, 0.f, v_c, C, Mc, C, C));
             ok = ok && (projected || dev::launch_gemm_generic(stream, et, x_c, C, d_wg.dev, C, (const float *)d_bg.dev, 0.f,
                                                               g_c, C, Mc, C, C));
+            wait_for_pair_bias();
             ok = ok && ((dt == kFP32 && dev::launch_attn_f32(stream, q_c, k_c, v_c, g_c, bias_c, bias_s0,
                                                               has_nb ? d_nb.dev : nullptr, nb_s0, nb_s1, a_c, (int)nbr,
                                                               (int)S, (int)H, (int)D, scale)) ||

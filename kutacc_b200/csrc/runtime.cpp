@@ -229,6 +229,7 @@ extern "C" {
 void kutacc_b200_set_stream(void *cuda_stream) { kutacc::runtime().stream = cuda_stream; }
 void kutacc_b200_set_async(int enabled) { kutacc::runtime().async = enabled != 0; }
 void kutacc_b200_set_sm_margin(int sms) { kutacc::runtime().sm_margin = sms < 0 ? 0 : (sms > 64 ? 64 : sms); }
+void kutacc_b200_set_pair_bias_event(void *cuda_event) { kutacc::runtime().pair_bias_event = cuda_event; }
 void kutacc_b200_synchronize(void) { kutacc::sync_and_check(); }
 
 void *kutacc_b200_device_malloc(size_t bytes)

@@ -116,6 +116,7 @@ class ShardedTriangleAttention:
         self.compute = torch.cuda.current_stream(device)
         self.comm = torch.cuda.Stream(device=device)
         self.events = [torch.cuda.Event() for _ in self.parts]
+        self.bias_projected, self.bias_gathered = torch.cuda.Event(), torch.cuda.Event()
         # phase marks of the last step, all on the compute stream
         self.marks = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
 
@@ -138,7 +139,15 @@ class ShardedTriangleAttention:
                 api.pair_bias(p["t_z"], self.t_wb, p["t_nb_rows"])
             self.marks[1].record(self.compute)
             if self.world > 1:
+                # the bias strips travel on the collective's stream while the first slab's projections run: the
+                # attention call waits for the gather between its projections and its attention kernel
+                self.bias_projected.record(self.compute)
+                self.comm.wait_event(self.bias_projected)
+                api.set_stream(self.comm.cuda_stream)
                 api.all_gather(self.g_nb_src_all, self.g_nb_dst_all)        # every slab's strips in one grouped call
+                self.bias_gathered.record(self.comm)
+                api.set_stream(self.compute.cuda_stream)
+                api.set_pair_bias_event(self.bias_gathered)
             self.marks[2].record(self.compute)
             for p, ev in zip(self.parts, self.events):
                 api.set_stream(self.compute.cuda_stream)
@@ -220,6 +229,8 @@ class HostShardedTriangleAttention:
         self.g_nb_dst = api.Tensor(self.nb_full.data_ptr(), [H, N, S * esz], [S * S * esz, S * esz, 1], api.DTYPE_BF16,
                                    keep=self.nb_full)
         self.compute = torch.cuda.current_stream(device)
+        self.comm = torch.cuda.Stream(device)
+        self.bias_projected, self.bias_gathered = torch.cuda.Event(), torch.cuda.Event()
         self.upload = torch.cuda.Stream(device)
         self.uploaded = [torch.cuda.Event() for _ in range(2)]
         self.computed = [None, None]   # recorded after the kernels of the last step that read device buffer 0 / 1
@@ -267,7 +278,15 @@ class HostShardedTriangleAttention:
             self.compute.wait_event(self.uploaded[j])
             api.pair_bias(self.t_z[j], self.t_wb, self.t_nb_rows)
             if self.world > 1:
+                # the gather runs on its own stream beside the projections of the attention call (see
+                # ShardedTriangleAttention.step)
+                self.bias_projected.record(self.compute)
+                self.comm.wait_event(self.bias_projected)
+                api.set_stream(self.comm.cuda_stream)
                 api.all_gather(self.g_nb_src, self.g_nb_dst)
+                self.bias_gathered.record(self.comm)
+                api.set_stream(self.compute.cuda_stream)
+                api.set_pair_bias_event(self.bias_gathered)
             if prefetch:
                 self._send(i + 1)
             # enqueue-only: the library downloads the output rows chunk by chunk on its copy stream while the later

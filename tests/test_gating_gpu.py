@@ -279,6 +279,40 @@ def test_enqueue_only_call_with_host_out_is_complete_after_synchronize(kutacc_li
     assert np.array_equal(runner.out_to_f32(host_tiny.out), want_tiny)
 
 
+def test_pair_bias_still_on_its_way_is_waited_for(kutacc_lib):
+    """kutacc_b200_set_pair_bias_event: the pair bias is written by another stream long after the call has been
+    queued; the call's attention kernel (not its projections) waits for the event, once."""
+    w = W.random_gating_case(seed=31, B=4, S=200, H=4, D=32, with_nb=True)
+    case = runner.DeviceCase(w)
+    want = runner.out_to_f32(case.run()).copy()
+    nb_src = case.nb.clone()
+    # two streams of their own: the legacy default stream would wait for the side stream by itself
+    main, side = torch.cuda.Stream(), torch.cuda.Stream()
+    ev = torch.cuda.Event()
+    api.set_async(True)
+    api.set_stream(main.cuda_stream)
+    try:
+        for _ in range(2):                                   # the second call must not wait for anything
+            case.nb.zero_()
+            torch.cuda.synchronize()
+            with torch.cuda.stream(side):
+                torch.cuda._sleep(20_000_000)                # about 10 ms: the call below is queued long before the bias exists
+                case.nb.copy_(nb_src, non_blocking=True)
+                ev.record(side)
+            api.set_pair_bias_event(ev)
+            out = case.run()
+            main.synchronize()
+            assert np.array_equal(runner.out_to_f32(out), want)
+            torch.cuda.synchronize()
+            out = case.run()                                 # no event set: uses the bias as it lies
+            main.synchronize()
+            assert np.array_equal(runner.out_to_f32(out), want)
+    finally:
+        api.set_stream(0)
+        api.set_async(False)
+        api.set_pair_bias_event(None)
+
+
 def test_sm_margin_changes_the_grid_not_the_result(kutacc_lib):
     # the persistent kernels walk their work items with a stride of the grid size: leaving SMs free for a
     # collective must not change a single bit
