@@ -359,7 +359,8 @@ def run_strong_scaling(args, torch, dist, api, W, runner, dev, world, rank, loca
         dist.broadcast(uid, 0)
         api.comm_init(world, rank, 0, bytes(uid.cpu().tolist()))
     slabs = args.slabs if world > 1 else 1
-    op = sharding.ShardedTriangleAttention(w, rank, world, slabs, dev, sm_margin=args.sm_margin)
+    op = sharding.ShardedTriangleAttention(w, rank, world, slabs, dev, sm_margin=args.sm_margin,
+                                           bias_gather_beside=not args.bias_gather_inline)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     rows_per_rank = w.B // world
 
@@ -591,6 +592,8 @@ def main():
                          "which measured best on 2 GPUs: 1.99 ms against 2.07 ms with 16 CTAs and a margin of 16 SMs)")
     ap.add_argument("--leave-sharded", action="store_true",
                     help="strong scaling: skip the all-gather of the output rows in the headline figure too")
+    ap.add_argument("--bias-gather-inline", action="store_true",
+                    help="strong scaling: run the bias all-gather on the compute stream instead of beside the projections")
     ap.add_argument("--slabs", type=int, default=2, help="strong scaling: slabs the output gather is pipelined in")
     args = ap.parse_args()
     keep_stdout_for_the_result()

@@ -54,7 +54,7 @@ class ShardedTriangleAttention:
     leaves them). With world == 1 the gathers are skipped.
     """
 
-    def __init__(self, w, rank: int, world: int, nslab: int, device, sm_margin: int = 8):
+    def __init__(self, w, rank: int, world: int, nslab: int, device, sm_margin: int = 8, bias_gather_beside: bool = True):
         import numpy as np
         import torch
         from . import api
@@ -62,6 +62,7 @@ class ShardedTriangleAttention:
         assert w.kind == "gating" and "wb" in w.arrays and w.B == w.S, "needs a full triangle workload"
         self.w, self.rank, self.world, self.device = w, rank, world, device
         self.sm_margin = sm_margin if world > 1 else 0      # SMs left to the collective that runs beside the kernels
+        self.bias_gather_beside = bias_gather_beside        # bias gather on the collective's stream, beside the projections
         self.api = api
         N, S, C, H = w.B, w.S, w.C, w.H
         self.slabs = slab_plan(N, world, nslab)
@@ -138,7 +139,9 @@ class ShardedTriangleAttention:
             for p in self.parts:
                 api.pair_bias(p["t_z"], self.t_wb, p["t_nb_rows"])
             self.marks[1].record(self.compute)
-            if self.world > 1:
+            if self.world > 1 and not self.bias_gather_beside:
+                api.all_gather(self.g_nb_src_all, self.g_nb_dst_all)        # every slab's strips in one grouped call
+            elif self.world > 1:
                 # the bias strips travel on the collective's stream while the first slab's projections run: the
                 # attention call waits for the gather between its projections and its attention kernel
                 self.bias_projected.record(self.compute)
