@@ -268,11 +268,15 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p)
                         const float4 bv = __ldg(reinterpret_cast<const float4 *>(bias + n) + j4);
                         float y0, y1, y2, y3;
                         if (FEAT & F_LN) {
+                            // two outputs per instruction on the packed fp32 pipe: y = ln_a * acc + (ln_b * s + t)
                             const float4 sv = __ldg(reinterpret_cast<const float4 *>(p.ln_s[seg] + n) + j4);
-                            y0 = fmaf(ln_a, __uint_as_float(r[c][4 * j4]), fmaf(ln_b, sv.x, bv.x));
-                            y1 = fmaf(ln_a, __uint_as_float(r[c][4 * j4 + 1]), fmaf(ln_b, sv.y, bv.y));
-                            y2 = fmaf(ln_a, __uint_as_float(r[c][4 * j4 + 2]), fmaf(ln_b, sv.z, bv.z));
-                            y3 = fmaf(ln_a, __uint_as_float(r[c][4 * j4 + 3]), fmaf(ln_b, sv.w, bv.w));
+                            const uint64_t a2 = pack_f32x2(ln_a, ln_a), b2 = pack_f32x2(ln_b, ln_b);
+                            const uint64_t w01 = fma_f32x2(pack_f32x2(sv.x, sv.y), b2, pack_f32x2(bv.x, bv.y));
+                            const uint64_t w23 = fma_f32x2(pack_f32x2(sv.z, sv.w), b2, pack_f32x2(bv.z, bv.w));
+                            unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(r[c][4 * j4]), __uint_as_float(r[c][4 * j4 + 1])),
+                                                   a2, w01), y0, y1);
+                            unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(r[c][4 * j4 + 2]),
+                                                              __uint_as_float(r[c][4 * j4 + 3])), a2, w23), y2, y3);
                         } else {
                             y0 = __uint_as_float(r[c][4 * j4]) + bv.x;
                             y1 = __uint_as_float(r[c][4 * j4 + 1]) + bv.y;
