@@ -89,6 +89,8 @@ struct AttnParams {
     int n_qt;                         // query tiles per (b, h)
     int n_items;                      // B * H * n_qt
     int gate_is_sigmoid;              // gate already holds bf16(sigmoid(bf16(x.Wg + bg)))
+    int nb_head_inner;                // pair-bias tensor map has the dimensions (key, head, query): the heads of a
+                                      // query row lie closer together than the rows (a [S, H, S] storage)
     int *counter;                     // [0] next work item of this launch, [1] CTAs that have finished (both zero at
                                       // launch; the last CTA to finish zeroes them again)
     float scale;
@@ -228,7 +230,12 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     mbar_arrive_expect_tx(kv_full(s), K_BYTES + BN * D * 2 + (HAS_NB ? NB_BYTES : 0));
                     tma_load_3d(st, &tm_k, kv_full(s), 0, k0, bh);
                     tma_load_3d(st + K_BYTES, &tm_vt, kv_full(s), k0, 0, bh);
-                    if (HAS_NB) tma_load_3d(st + K_BYTES + VT_BYTES, &tm_nb, kv_full(s), k0, q0, h);
+                    if (HAS_NB) {
+                        if (p.nb_head_inner)
+                            tma_load_3d(st + K_BYTES + VT_BYTES, &tm_nb, kv_full(s), k0, h, q0);
+                        else
+                            tma_load_3d(st + K_BYTES + VT_BYTES, &tm_nb, kv_full(s), k0, q0, h);
+                    }
                 }
                 float *mb = reinterpret_cast<float *>(smem_gen + OFF_STAGE + s * STAGE_BYTES + K_BYTES + VT_BYTES + NB_BYTES);
 #pragma unroll
@@ -607,10 +614,19 @@ bool tcgen05_attn_core_bf16(cudaStream_t stream, const void *q, const void *k, c
     if (!make_tensor_map_bf16_3d(&tq, q, D, Su, BH, D, Su * D, D, BM, 64)) return false;
     if (!make_tensor_map_bf16_3d(&tk, k, D, Su, BH, D, Su * D, D, BN, 64)) return false;
     if (!make_tensor_map_bf16_3d(&tvt, vt, Su, D, BH, (uint64_t)vt_pitch, (uint64_t)D * vt_pitch, BN, D, 128)) return false;
+    p.nb_head_inner = 0;
     if (nb) {
-        if (!make_tensor_map_bf16_3d(&tnb, nb, Su, Su, (uint64_t)H, (uint64_t)nb_stride_q, (uint64_t)nb_stride_h, BN, BM,
-                                     128))
+        if (nb_stride_h < nb_stride_q) {
+            // heads closer together than query rows: dimensions in the order of their strides (key, head, query); the
+            // box takes one head, so the tile in shared memory is the same 128 rows x 64 keys
+            p.nb_head_inner = 1;
+            if (!make_tensor_map_bf16_3d(&tnb, nb, Su, (uint64_t)H, Su, (uint64_t)nb_stride_h, (uint64_t)nb_stride_q, BN, 1,
+                                         128, BM))
+                return false;
+        } else if (!make_tensor_map_bf16_3d(&tnb, nb, Su, Su, (uint64_t)H, (uint64_t)nb_stride_q, (uint64_t)nb_stride_h, BN,
+                                            BM, 128)) {
             return false;
+        }
         return launch_one<true>(stream, tq, tk, tvt, tnb, p);
     }
     tnb = tk;

@@ -364,6 +364,7 @@ bool launch_attn_core_bf16(cudaStream_t stream, const void *q, const void *k, co
 {
     if (B > 65535 || H > 65535) return false;
     if (nb && ((nb_stride_h % 8) || (nb_stride_q % 8) || ((uintptr_t)nb % 16))) return false;
+    if (nb && nb_stride_h < nb_stride_q) return false;     // heads inside rows: only the tcgen05 core and the generic kernel
     KernelErrorWord &ew = kernel_error_word();
     if (ew.device == nullptr) return false;
     AttnParams p;

@@ -396,7 +396,8 @@ __global__ void __launch_bounds__(256) pair_bias_mma_kernel(const __nv_bfloat16 
                                                             const __nv_bfloat16 *__restrict__ wb,
                                                             __nv_bfloat16 *__restrict__ nb, int64_t nb_head_stride,
                                                             int64_t total, int H, const float2 *__restrict__ stats,
-                                                            const float *__restrict__ ln_s, const float *__restrict__ ln_t)
+                                                            const float *__restrict__ ln_s, const float *__restrict__ ln_t,
+                                                            int64_t nk, int64_t nb_row_stride)
 {
     constexpr int ROWB = CZ * 2, CHUNKS = ROWB / 16, TP = 128, STAGES = 3, STAGE_BYTES = TP * ROWB;
     extern __shared__ __align__(128) unsigned char pb_smem[];
@@ -448,13 +449,17 @@ __global__ void __launch_bounds__(256) pair_bias_mma_kernel(const __nv_bfloat16 
             acc[2] = fmaf(st1.y, acc[2] - st1.x * s0, t0);
             acc[3] = fmaf(st1.y, acc[3] - st1.x * s1, t1);
         }
+        // position p = row * nk + key is stored at row * nb_row_stride + key (rows of the output may be further apart
+        // than nk: a layout with the heads of a row next to each other, [rows, H, keys], for instance)
+        const int64_t o0 = nb_row_stride == nk ? p0 : (p0 / nk) * nb_row_stride + p0 % nk;
+        const int64_t o1 = nb_row_stride == nk ? p1 : (p1 / nk) * nb_row_stride + p1 % nk;
         if (p0 < total) {
-            if (h0 < H) nb[h0 * nb_head_stride + p0] = __float2bfloat16_rn(acc[0]);
-            if (h1 < H) nb[h1 * nb_head_stride + p0] = __float2bfloat16_rn(acc[1]);
+            if (h0 < H) nb[h0 * nb_head_stride + o0] = __float2bfloat16_rn(acc[0]);
+            if (h1 < H) nb[h1 * nb_head_stride + o0] = __float2bfloat16_rn(acc[1]);
         }
         if (p1 < total) {
-            if (h0 < H) nb[h0 * nb_head_stride + p1] = __float2bfloat16_rn(acc[2]);
-            if (h1 < H) nb[h1 * nb_head_stride + p1] = __float2bfloat16_rn(acc[3]);
+            if (h0 < H) nb[h0 * nb_head_stride + o1] = __float2bfloat16_rn(acc[2]);
+            if (h1 < H) nb[h1 * nb_head_stride + o1] = __float2bfloat16_rn(acc[3]);
         }
     }
     cp_async_wait<0>();
@@ -463,7 +468,7 @@ __global__ void __launch_bounds__(256) pair_bias_mma_kernel(const __nv_bfloat16 
 template <int CZ, bool LN = false>
 bool launch_pair_bias_mma(cudaStream_t stream, const void *z, const void *wb, void *nb, int64_t nb_head_stride,
                           int64_t total, int H, const void *stats = nullptr, const float *ln_s = nullptr,
-                          const float *ln_t = nullptr)
+                          const float *ln_t = nullptr, int64_t nk = 1, int64_t nb_row_stride = 1)
 {
     constexpr int SMEM = 3 * 128 * CZ * 2;
     static bool configured = false;
@@ -478,7 +483,7 @@ bool launch_pair_bias_mma(cudaStream_t stream, const void *z, const void *wb, vo
     const unsigned grid = (unsigned)std::min<int64_t>(ntiles, 148 * 2);
     pair_bias_mma_kernel<CZ, LN><<<grid, 256, SMEM, stream>>>((const __nv_bfloat16 *)z, (const __nv_bfloat16 *)wb,
                                                               (__nv_bfloat16 *)nb, nb_head_stride, total, H,
-                                                              (const float2 *)stats, ln_s, ln_t);
+                                                              (const float2 *)stats, ln_s, ln_t, nk, nb_row_stride);
     return true;
 }
 
@@ -581,8 +586,9 @@ bool launch_pair_bias_ln(cudaStream_t stream, const void *z, const void *wb_fold
 }
 
 bool launch_pair_bias(cudaStream_t stream, ElemType t, const void *z, const void *wb, void *nb,
-                      int64_t nb_head_stride, int64_t pos_stride, int64_t R, int64_t Nk, int Cz, int H)
+                      int64_t nb_head_stride, int64_t pos_stride, int64_t R, int64_t Nk, int Cz, int H, int64_t nb_row_stride)
 {
+    if (nb_row_stride <= 0) nb_row_stride = Nk;
     if (H > 16 || (size_t)H * Cz * 4 > 48 * 1024) return false;
     KernelTimer timer__("pair_bias", stream);
     const int64_t pos = R * Nk;
@@ -592,13 +598,16 @@ bool launch_pair_bias(cudaStream_t stream, ElemType t, const void *z, const void
     const bool pow2 = lanes > 0 && (lanes & (lanes - 1)) == 0 && lanes <= 32 && Cz % 8 == 0;
     if (t == kElemBF16 && H <= 8 && pos_stride == 1 && ((uintptr_t)z % 16) == 0 && ((uintptr_t)wb % 4) == 0 &&
         (Cz == 128 || Cz == 64)) {
-        const bool ok = Cz == 128 ? launch_pair_bias_mma<128>(stream, z, wb, nb, nb_head_stride, pos, H)
-                                  : launch_pair_bias_mma<64>(stream, z, wb, nb, nb_head_stride, pos, H);
+        const bool ok = Cz == 128 ? launch_pair_bias_mma<128>(stream, z, wb, nb, nb_head_stride, pos, H, nullptr, nullptr,
+                                                              nullptr, Nk, nb_row_stride)
+                                  : launch_pair_bias_mma<64>(stream, z, wb, nb, nb_head_stride, pos, H, nullptr, nullptr,
+                                                             nullptr, Nk, nb_row_stride);
         if (ok) {
             count_launch();
             return true;
         }
     }
+    if (nb_row_stride != Nk) return false;                   // only the tensor-core kernel writes rows that are apart
     if (t == kElemBF16 && pow2 && H <= 8 && ((uintptr_t)z % 16) == 0) {
         const int64_t ppb = 256 / lanes;
         const unsigned gridv = (unsigned)std::min<int64_t>((pos + ppb - 1) / ppb, 148 * 32);

@@ -111,8 +111,11 @@ bool launch_attn_generic(cudaStream_t stream, ElemType t, const void *q, const v
 // ---- pair-bias projection --------------------------------------------------------------------------
 // y[h * head_stride + (r * Nk + k) * pos_stride] = z[r, k, :] . wb[h, :], z [R, Nk, Cz] contiguous.
 // (head_stride = R*Nk, pos_stride = 1) writes [H, R, Nk]; (1, H) writes [R*Nk, H]. H <= 16.
+// nb_row_stride (elements, 0 = Nk): distance between the output rows of one head when they are not dense, e.g.
+// H * Nk for a [R, H, Nk] layout with head stride Nk (bf16, c_z 64 or 128, pos_stride 1 only).
 bool launch_pair_bias(cudaStream_t stream, ElemType t, const void *z, const void *wb, void *nb,
-                      int64_t nb_head_stride, int64_t pos_stride, int64_t R, int64_t Nk, int Cz, int H);
+                      int64_t nb_head_stride, int64_t pos_stride, int64_t R, int64_t Nk, int Cz, int H,
+                      int64_t nb_row_stride = 0);
 // The same projection of LayerNorm(z) with folded weights (launch_ln_fold) and per-position statistics: only the
 // tensor-core kernel (bf16, c_z 64 or 128, up to 8 heads, [H, R, Nk] output); false otherwise.
 bool launch_pair_bias_ln(cudaStream_t stream, const void *z, const void *wb_folded, const void *stats, const float *ln_s,

@@ -137,14 +137,14 @@ extern "C" void kutacc_b200_pair_bias(kutacc_tensor_h z_h, kutacc_tensor_h wb_h,
     const DType dt = z.dtype();
     KUTACC_CHECK((dt == kBF16 || dt == kFP32) && wb.sizes()[1] == Cz && nb.sizes()[0] == H && nb.sizes()[1] == R &&
                      nb.sizes()[2] == Nk && z.strides()[2] == 1 && z.strides()[1] == Cz && z.strides()[0] == Nk * Cz &&
-                     nb.strides()[2] == 1 && nb.strides()[1] == Nk && wb.strides()[1] == 1 && wb.strides()[0] == Cz &&
+                     nb.strides()[2] == 1 && nb.strides()[1] >= Nk && wb.strides()[1] == 1 && wb.strides()[0] == Cz &&
                      R > 0 && Nk > 0 && Cz > 0 && H > 0 && H <= 16 && Cz <= 4096,
                  "kutacc_b200_pair_bias: shape/stride invalid");
     if (kutacc_check_err_set) return;
     const size_t es = dtype_size(dt);
-    const int64_t hs = nb.strides()[0];
+    const int64_t hs = nb.strides()[0], rs = nb.strides()[1];   // rs > Nk: rows apart, e.g. [rows, nheads, keys] storage
     const size_t z_bytes = (size_t)R * Nk * Cz * es, w_bytes = (size_t)H * Cz * es,
-                 nb_bytes = (size_t)((H - 1) * hs + R * Nk) * es;
+                 nb_bytes = (size_t)((H - 1) * hs + (R - 1) * rs + Nk) * es;
     Runtime &rt = runtime();
     const size_t stage = staged_bytes_needed(z.data_ptr(), z_bytes) + staged_bytes_needed(wb.data_ptr(), w_bytes) +
                          staged_bytes_needed(nb.data_ptr(), nb_bytes);
@@ -153,8 +153,8 @@ extern "C" void kutacc_b200_pair_bias(kutacc_tensor_h z_h, kutacc_tensor_h wb_h,
               d_n = resolve_out(nb.data_ptr(), nb_bytes);
     if (kutacc_check_err_set) return;
     const bool ok = dev::launch_pair_bias((cudaStream_t)rt.stream, dt == kFP32 ? dev::kElemF32 : dev::kElemBF16,
-                                          d_z.dev, d_w.dev, d_n.dev, hs, 1, R, Nk, (int)Cz, (int)H);
-    KUTACC_CHECK(ok, "kutacc_b200_pair_bias: no device kernel for nheads=", H, " c_z=", Cz);
+                                          d_z.dev, d_w.dev, d_n.dev, hs, 1, R, Nk, (int)Cz, (int)H, rs);
+    KUTACC_CHECK(ok, "kutacc_b200_pair_bias: no device kernel for nheads=", H, " c_z=", Cz, " row stride ", rs);
     finish_out(d_n);
     end_of_call();
 }

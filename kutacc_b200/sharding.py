@@ -79,41 +79,45 @@ class ShardedTriangleAttention:
         self.bg, self.bo = f32(A["bg"]), f32(A["bo"])
         self.wb = f(np.ascontiguousarray(A["wb"].T))                                   # [H, c_z]
         tdt = torch.bfloat16 if w.dtype == "bf16" else torch.float32
-        self.nb_full = torch.zeros((H, S, S), dtype=tdt, device=device)
+        # The pair bias is stored with the heads of a query row next to each other, [S, H, S]: the rows a rank
+        # projects are then one dense block per slab, so a slab's share of the bias is gathered in place by ONE
+        # collective (with [H, S, S] storage every (head, slab) strip needed a call of its own, and queueing those
+        # calls cost more host time than the gather takes). The operators see it as [H, S, S] through strides.
+        self.nb_full = torch.zeros((S, H, S), dtype=tdt, device=device)
         self.out_full = torch.zeros((N, S, C), dtype=tdt, device=device)
         self.weights = api.make_weights(C, H, w.D, self.wq, self.wk, self.wv, self.wg, self.bg, self.wo, self.bo)
         self.t_wb = api.tensor(self.wb)
-        self.t_nb = api.tensor(self.nb_full)
+        self.t_nb = api.Tensor(self.nb_full.data_ptr(), [H, S, S], [S, H * S, 1], dt, keep=self.nb_full)
         self.parts = []
         for (r0, n), (s0, srows, blk), x, bias in zip(self.mine, self.slabs, self.x, self.bias):
-            nb_rows = self.nb_full[:, r0:r0 + n, :]
+            nb_rows = self.nb_full[r0:r0 + n]
             out_rows = self.out_full[r0:r0 + n]
             part = {
                 "inputs": api.make_inputs(n, S),
                 "t_x": api.tensor(x, sizes=[n * S, C], strides=[C, 1]),
                 "t_z": api.tensor(x),                                                   # z[q, k, :] = x[q, k, :]
                 "t_bias": api.tensor(bias),
-                "t_nb_rows": api.Tensor(nb_rows.data_ptr(), [H, n, S], [S * S, S, 1], dt, keep=self.nb_full),
+                "t_nb_rows": api.Tensor(nb_rows.data_ptr(), [H, n, S], [S, H * S, 1], dt, keep=self.nb_full),
                 "t_out_rows": api.Tensor(out_rows.data_ptr(), [n, S, C], [S * C, C, 1], dt, keep=self.out_full),
                 # byte views for the collectives: [m, n, len]
-                "g_nb_src": api.Tensor(nb_rows.data_ptr(), [H, n, S * esz], [S * S * esz, S * esz, 1], api.DTYPE_BF16,
-                                       keep=self.nb_full),
-                "g_nb_dst": api.Tensor(self.nb_full[:, s0:s0 + srows, :].data_ptr(), [H, srows, S * esz],
-                                       [S * S * esz, S * esz, 1], api.DTYPE_BF16, keep=self.nb_full),
+                "g_nb_src": api.Tensor(nb_rows.data_ptr(), [n, 1, H * S * esz], [H * S * esz, H * S * esz, 1],
+                                       api.DTYPE_BF16, keep=self.nb_full),
+                "g_nb_dst": api.Tensor(self.nb_full[s0:s0 + srows].data_ptr(), [srows, 1, H * S * esz],
+                                       [H * S * esz, H * S * esz, 1], api.DTYPE_BF16, keep=self.nb_full),
                 "g_out_src": api.Tensor(out_rows.data_ptr(), [n, S, C * esz], [S * C * esz, C * esz, 1], api.DTYPE_BF16,
                                         keep=self.out_full),
                 "g_out_dst": api.Tensor(self.out_full[s0:s0 + srows].data_ptr(), [srows, S, C * esz],
                                         [S * C * esz, C * esz, 1], api.DTYPE_BF16, keep=self.out_full),
             }
             self.parts.append(part)
-        # The bias of all slabs in ONE gather: [H, N, S] with N = nslab * srows is also [H * nslab, srows, S] with a
-        # uniform stride between the (head, slab) strips, and inside every strip rank r owns block r.
+        # Every slab's share in ONE call: [S, H, S] with S = nslab * srows rows is also [nslab, srows, H * S], and inside
+        # every slab rank r owns block r (the library gathers such strips in place, as one group of collectives).
         srows, blk = self.slabs[0][1], self.slabs[0][2]
-        strides = [srows * S * esz, S * esz, 1]
-        self.g_nb_src_all = api.Tensor(self.nb_full.data_ptr() + rank * blk * S * esz, [H * nslab, blk, S * esz], strides,
+        row = H * S * esz
+        self.g_nb_src_all = api.Tensor(self.nb_full.data_ptr() + rank * blk * row, [nslab, blk, row], [srows * row, row, 1],
                                        api.DTYPE_BF16, keep=self.nb_full)
-        self.g_nb_dst_all = api.Tensor(self.nb_full.data_ptr(), [H * nslab, srows, S * esz], strides, api.DTYPE_BF16,
-                                       keep=self.nb_full)
+        self.g_nb_dst_all = api.Tensor(self.nb_full.data_ptr(), [nslab, srows, row], [srows * row, row, 1],
+                                       api.DTYPE_BF16, keep=self.nb_full)
         self.compute = torch.cuda.current_stream(device)
         self.comm = torch.cuda.Stream(device=device)
         self.events = [torch.cuda.Event() for _ in self.parts]
@@ -140,14 +144,14 @@ class ShardedTriangleAttention:
                 api.pair_bias(p["t_z"], self.t_wb, p["t_nb_rows"])
             self.marks[1].record(self.compute)
             if self.world > 1 and not self.bias_gather_beside:
-                api.all_gather(self.g_nb_src_all, self.g_nb_dst_all)        # every slab's strips in one grouped call
+                api.all_gather(self.g_nb_src_all, self.g_nb_dst_all)        # one in-place gather per slab, one group
             elif self.world > 1:
                 # the bias strips travel on the collective's stream while the first slab's projections run: the
                 # attention call waits for the gather between its projections and its attention kernel
                 self.bias_projected.record(self.compute)
                 self.comm.wait_event(self.bias_projected)
                 api.set_stream(self.comm.cuda_stream)
-                api.all_gather(self.g_nb_src_all, self.g_nb_dst_all)        # every slab's strips in one grouped call
+                api.all_gather(self.g_nb_src_all, self.g_nb_dst_all)        # one in-place gather per slab, one group
                 self.bias_gathered.record(self.comm)
                 api.set_stream(self.compute.cuda_stream)
                 api.set_pair_bias_event(self.bias_gathered)
@@ -216,21 +220,22 @@ class HostShardedTriangleAttention:
         self.wq, self.wk, self.wv, self.wg, self.wo = (f(A[k]) for k in ("wq", "wk", "wv", "wg", "wo"))
         self.bg, self.bo = f32(A["bg"]), f32(A["bo"])
         self.wb = f(np.ascontiguousarray(A["wb"].T))
-        self.nb_full = torch.zeros((H, S, S), dtype=tdt, device=device)
+        # [S, H, S] storage (see ShardedTriangleAttention): this rank's rows are one dense block, gathered in place
+        self.nb_full = torch.zeros((S, H, S), dtype=tdt, device=device)
         self.weights = api.make_weights(C, H, w.D, self.wq, self.wk, self.wv, self.wg, self.bg, self.wo, self.bo)
         self.inputs = api.make_inputs(n, S)
         self.t_wb = api.tensor(self.wb)
-        self.t_nb = api.tensor(self.nb_full)
+        self.t_nb = api.Tensor(self.nb_full.data_ptr(), [H, S, S], [S, H * S, 1], dt, keep=self.nb_full)
         self.t_x = [api.tensor(x, sizes=[n * S, C], strides=[C, 1]) for x in self.xs]
         self.t_z = [api.tensor(x) for x in self.xs]
         self.t_bias = [api.tensor(b) for b in self.biases]
         self.t_out = api.tensor(self.hout)
-        nb_rows = self.nb_full[:, r0:r0 + n, :]
-        self.t_nb_rows = api.Tensor(nb_rows.data_ptr(), [H, n, S], [S * S, S, 1], dt, keep=self.nb_full)
-        self.g_nb_src = api.Tensor(nb_rows.data_ptr(), [H, n, S * esz], [S * S * esz, S * esz, 1], api.DTYPE_BF16,
+        nb_rows = self.nb_full[r0:r0 + n]
+        self.t_nb_rows = api.Tensor(nb_rows.data_ptr(), [H, n, S], [S, H * S, 1], dt, keep=self.nb_full)
+        self.g_nb_src = api.Tensor(nb_rows.data_ptr(), [n, 1, H * S * esz], [H * S * esz, H * S * esz, 1], api.DTYPE_BF16,
                                    keep=self.nb_full)
-        self.g_nb_dst = api.Tensor(self.nb_full.data_ptr(), [H, N, S * esz], [S * S * esz, S * esz, 1], api.DTYPE_BF16,
-                                   keep=self.nb_full)
+        self.g_nb_dst = api.Tensor(self.nb_full.data_ptr(), [N, 1, H * S * esz], [H * S * esz, H * S * esz, 1],
+                                   api.DTYPE_BF16, keep=self.nb_full)
         self.compute = torch.cuda.current_stream(device)
         self.comm = torch.cuda.Stream(device)
         self.bias_projected, self.bias_gathered = torch.cuda.Event(), torch.cuda.Event()

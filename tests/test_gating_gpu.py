@@ -279,6 +279,23 @@ def test_enqueue_only_call_with_host_out_is_complete_after_synchronize(kutacc_li
     assert np.array_equal(runner.out_to_f32(host_tiny.out), want_tiny)
 
 
+@pytest.mark.parametrize("B,S,H,D", [(3, 200, 4, 32), (2, 129, 4, 32), (2, 70, 2, 16)])
+def test_pair_bias_stored_with_the_heads_inside_the_rows(kutacc_lib, B, S, H, D):
+    """The pair bias handed over as [H, S, S] through strides over a [S, H, S] storage (what the sharded flow
+    gathers in place): the same bits as with the dense [H, S, S] tensor (head size 32: the tcgen05 core with the
+    tensor-map dimensions in stride order; head size 16: the generic kernel)."""
+    w = W.random_gating_case(seed=60 + S, B=B, S=S, H=H, D=D, with_nb=True, full_mask_rows=1 if B > 2 else 0)
+    case = runner.DeviceCase(w)
+    want = runner.out_to_f32(case.run()).copy()
+    sp = (S + 7) // 8 * 8                                   # rows of 16-byte multiples for the TMA path
+    store = torch.zeros((S, H, sp), dtype=case.nb.dtype, device="cuda:0")
+    store[:, :, :S] = case.nb.permute(1, 0, 2)
+    t_nb = api.Tensor(store.data_ptr(), [H, S, S], [sp, H * sp, 1], api.DTYPE_BF16, keep=store)
+    api.gating_attention(case.t_x, case.inputs, case.t_bias, t_nb, case.weights, case.t_out)
+    torch.cuda.synchronize()
+    assert np.array_equal(runner.out_to_f32(case.out), want)
+
+
 def test_pair_bias_still_on_its_way_is_waited_for(kutacc_lib):
     """kutacc_b200_set_pair_bias_event: the pair bias is written by another stream long after the call has been
     queued; the call's attention kernel (not its projections) waits for the event, once."""

@@ -102,3 +102,21 @@ def test_all_gather_single_rank_copies_with_byte_strides(kutacc_lib):
     out = np.zeros((4, 5, 1), dtype=np.uint8)
     api.all_gather(api.tensor(grid), api.tensor(out))
     assert np.array_equal(out, grid)
+
+
+@pytest.mark.parametrize("R,Nk,Cz,H", [(8, 384, 128, 4), (5, 100, 64, 8)])
+def test_pair_bias_written_with_the_heads_inside_the_rows(kutacc_lib, R, Nk, Cz, H):
+    # nb [H, R, Nk] as a strided view of a [R, H, Nk] storage: the same values as the dense output, nothing else touched
+    rng = np.random.default_rng(R + Nk)
+    z = W.as_f32(W.bf16_bits(rng.standard_normal((R, Nk, Cz)).astype(np.float32)))
+    wb = W.as_f32(W.bf16_bits((rng.standard_normal((H, Cz)) / np.sqrt(Cz)).astype(np.float32)))
+    tz = torch.from_numpy(W.bf16_bits(z).view(np.int16)).view(torch.bfloat16).to(DEV)
+    tw = torch.from_numpy(W.bf16_bits(wb).view(np.int16)).view(torch.bfloat16).to(DEV)
+    dense = torch.zeros((H, R, Nk), dtype=torch.bfloat16, device=DEV)
+    api.pair_bias(api.tensor(tz), api.tensor(tw), api.tensor(dense))
+    store = torch.full((R, H + 1, Nk), 7.0, dtype=torch.bfloat16, device=DEV)       # one spare "head" of padding per row
+    view = api.Tensor(store.data_ptr(), [H, R, Nk], [Nk, (H + 1) * Nk, 1], api.DTYPE_BF16, keep=store)
+    api.pair_bias(api.tensor(tz), api.tensor(tw), view)
+    torch.cuda.synchronize()
+    assert torch.equal(store[:, :H, :].permute(1, 0, 2), dense)
+    assert (store[:, H, :] == 7.0).all()
