@@ -336,7 +336,10 @@ KUTACC_B200_API int kutacc_b200_selftest_wait_timeout(int64_t limit_microseconds
 /* Pair-bias projection written directly in the layout the attention operator consumes:
  * nb[h, q, k] = z[q, k, :] . wb[h, :]   with z [rows, n_k, c_z], wb [nheads, c_z], nb
  * [nheads, rows, n_k] (row stride of head h = nb_head_stride elements). Same arithmetic as
- * kutacc_af2_linear on z viewed [rows*n_k, c_z] followed by the caller's permute. dtype bf16/fp32. */
+ * kutacc_af2_linear on z viewed [rows*n_k, c_z] followed by the caller's permute. dtype bf16/fp32.
+ * nb's strides may place the heads of a row next to each other (a [rows, nheads, n_k] storage seen as
+ * [nheads, rows, n_k]: strides {n_k, nheads * n_k, 1}; bf16, c_z 64 or 128): the rows one rank projects are then one
+ * dense block, which kutacc_af2_all_gather gathers in place. kutacc_af2_gating_attention takes such a pair bias too. */
 KUTACC_B200_API void kutacc_b200_pair_bias(kutacc_tensor_h z, kutacc_tensor_h wb, kutacc_tensor_h nb);
 
 /* LayerNorm fused in front of the two projections of the attention path (no counterpart in the reference, whose
