@@ -57,7 +57,7 @@ __global__ void __launch_bounds__(A_THREADS, 2) attn_f32_kernel(const float *__r
                                                              const float *__restrict__ bias, int64_t bias_stride0,
                                                              const float *__restrict__ nb, int64_t nb_stride_h,
                                                              int64_t nb_stride_q, float *__restrict__ avg, int S, int H,
-                                                             int n_qt, float scale)
+                                                             int n_qt, float scale, float *__restrict__ avg_split)
 {
     __shared__ F32Smem sm;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
@@ -230,6 +230,18 @@ __global__ void __launch_bounds__(A_THREADS, 2) attn_f32_kernel(const float *__r
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
     const float i0 = 1.0f / l0, i1 = 1.0f / l1;
+    // With avg_split the gated average goes out as the operand of the output projection's tensor-memory GEMM: rows
+    // of 2C floats, [tf32 head | tail] (what launch_split_tf32 would make of avg), and avg itself is not written.
+    auto store_result = [&](int64_t off, int64_t row, int ch, float2 res) {
+        if (avg_split == nullptr) {
+            *reinterpret_cast<float2 *>(avg + off) = res;
+            return;
+        }
+        const float hx = __uint_as_float(tf32_hi(res.x)), hy = __uint_as_float(tf32_hi(res.y));
+        float *dst = avg_split + row * 2 * C + ch;
+        *reinterpret_cast<float2 *>(dst) = make_float2(hx, hy);
+        *reinterpret_cast<float2 *>(dst + C) = make_float2(res.x - hx, res.y - hy);
+    };
 #pragma unroll
     for (int ct = 0; ct < 4; ++ct) {
         const int ch = h * AD + ct * 8 + 2 * t;
@@ -239,7 +251,7 @@ __global__ void __launch_bounds__(A_THREADS, 2) attn_f32_kernel(const float *__r
             float2 res;
             res.x = o[ct][0] * i0 * (1.0f / (1.0f + __expf(-gv.x)));
             res.y = o[ct][1] * i0 * (1.0f / (1.0f + __expf(-gv.y)));
-            *reinterpret_cast<float2 *>(avg + off) = res;
+            store_result(off, ((int64_t)b * S + r0), ch, res);
         }
         if (r1 < S) {
             const int64_t off = ((int64_t)b * S + r1) * C + ch;
@@ -247,7 +259,7 @@ __global__ void __launch_bounds__(A_THREADS, 2) attn_f32_kernel(const float *__r
             float2 res;
             res.x = o[ct][2] * i1 * (1.0f / (1.0f + __expf(-gv.x)));
             res.y = o[ct][3] * i1 * (1.0f / (1.0f + __expf(-gv.y)));
-            *reinterpret_cast<float2 *>(avg + off) = res;
+            store_result(off, ((int64_t)b * S + r1), ch, res);
         }
     }
 }
@@ -257,17 +269,17 @@ __global__ void __launch_bounds__(A_THREADS, 2) attn_f32_kernel(const float *__r
 // fp32, head size 32 only; returns false for anything else (the caller falls back to the generic kernel).
 bool launch_attn_f32(cudaStream_t stream, const void *q, const void *k, const void *v, const void *gate, const void *bias,
                      int64_t bias_stride0, const void *nb, int64_t nb_stride_h, int64_t nb_stride_q, void *avg, int B,
-                     int S, int H, int D, float scale)
+                     int S, int H, int D, float scale, void *avg_split)
 {
     if (D != AD || B < 1 || S < 1 || H < 1) return false;
-    if ((((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)gate | (uintptr_t)avg) & 15u) != 0) return false;
+    if ((((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)gate | (uintptr_t)avg | (uintptr_t)avg_split) & 15u) != 0) return false;
     const int n_qt = (S + AQ - 1) / AQ;
     const int64_t items = (int64_t)B * H * n_qt;
     if (items > 0x7fffffff) return false;
     KernelTimer timer__("attn_f32", stream);
     attn_f32_kernel<<<(unsigned)items, A_THREADS, 0, stream>>>(
         (const float *)q, (const float *)k, (const float *)v, (const float *)gate, (const float *)bias, bias_stride0,
-        (const float *)nb, nb_stride_h, nb_stride_q, (float *)avg, S, H, n_qt, scale);
+        (const float *)nb, nb_stride_h, nb_stride_q, (float *)avg, S, H, n_qt, scale, (float *)avg_split);
     count_launch();
     return true;
 }

@@ -281,7 +281,14 @@ static void gating_attention_impl(Tensor &input, int64_t batch, int64_t seq_len,
             ok = ok && (projected || dev::launch_gemm_generic(stream, et, x_c, C, d_wg.dev, C, (const float *)d_bg.dev, 0.f,
                                                               g_c, C, Mc, C, C));
             wait_for_pair_bias();
-            ok = ok && ((dt == kFP32 && dev::launch_attn_f32(stream, q_c, k_c, v_c, g_c, bias_c, bias_s0,
+            // fp32 with the tensor-memory GEMM after it: the attention core writes its result already split into
+            // tf32 head and tail, in the rows of the output projection's operand
+            bool avg_is_split = false;
+            if (ok && dt == kFP32 && f32_tc_ok)
+                avg_is_split = dev::launch_attn_f32(stream, q_c, k_c, v_c, g_c, bias_c, bias_s0, has_nb ? d_nb.dev : nullptr,
+                                                    nb_s0, nb_s1, a_c, (int)nbr, (int)S, (int)H, (int)D, scale, as_c);
+            ok = ok && (avg_is_split ||
+                        (dt == kFP32 && dev::launch_attn_f32(stream, q_c, k_c, v_c, g_c, bias_c, bias_s0,
                                                               has_nb ? d_nb.dev : nullptr, nb_s0, nb_s1, a_c, (int)nbr,
                                                               (int)S, (int)H, (int)D, scale)) ||
                         dev::launch_attn_generic(stream, et, q_c, k_c, v_c, g_c, bias_c, bias_s0,
@@ -291,11 +298,13 @@ static void gating_attention_impl(Tensor &input, int64_t batch, int64_t seq_len,
             if (ok && f32_tc_ok) {
                 const float *pb[1] = {(const float *)d_bo.dev};
                 void *po[1] = {out_c};
-                out_done = dev::launch_split_tf32(stream, a_c, C, as_c, Mc, (int)C) &&
+                out_done = (avg_is_split || dev::launch_split_tf32(stream, a_c, C, as_c, Mc, (int)C)) &&
                            dev::tcgen05_gemm_tf32x3(stream, as_c, &w_split[4], pb, po, out_rs, Mc, (int)C, (int)C, 1);
             }
-            ok = ok && (out_done || dev::launch_gemm_generic(stream, et, a_c, C, d_wo.dev, C, (const float *)d_bo.dev, 0.f,
-                                                             out_c, out_rs, Mc, C, C));
+            // (when the average exists only in split form, the tensor-memory GEMM is the only kernel that can read it)
+            ok = ok && (out_done || (!avg_is_split && dev::launch_gemm_generic(stream, et, a_c, C, d_wo.dev, C,
+                                                                               (const float *)d_bo.dev, 0.f, out_c, out_rs,
+                                                                               Mc, C, C)));
         }
         return ok;
     };

@@ -124,9 +124,11 @@ bool launch_pair_bias_ln(cudaStream_t stream, const void *z, const void *wb_fold
 // ---- global attention (bf16, C = 64) ---------------------------------------------------------------
 // scratch: qk [B, H, 64] fp32-sized slots and wa [B, 64]; see global_attention.cu
 // fp32 attention core on tensor cores (error-compensated tf32), head size 32; false for other shapes.
+// With avg_split the result is written as rows [tf32 head | tail] of 2 * H * D floats (the operand layout of
+// tcgen05_gemm_tf32x3) instead of into avg.
 bool launch_attn_f32(cudaStream_t stream, const void *q, const void *k, const void *v, const void *gate, const void *bias,
                      int64_t bias_stride0, const void *nb, int64_t nb_stride_h, int64_t nb_stride_q, void *avg, int B,
-                     int S, int H, int D, float scale);
+                     int S, int H, int D, float scale, void *avg_split = nullptr);
 
 // LayerNorm folded into the projection that follows (ln_fold.cu): per-row (mean, rstd) pairs as float2, and
 // for up to four [N, K] weight matrices the folded, centred bf16 weights with the epilogue terms s and t
